@@ -1,0 +1,96 @@
+/* C ABI of the B200 (sm_100a) NVFP4 paged MLA decode library, libnvfp4_mla_b200.so.
+ *
+ * Every entry point takes plain device pointers and sizes plus a CUDA stream handle (cudaStream_t passed as void*;
+ * NULL = the legacy default stream), launches asynchronously on that stream and never synchronises the device,
+ * allocates nothing and keeps no reference to its arguments. Functions returning int return 0 on success; on
+ * failure nothing was launched and nvfp4_mla_last_error() describes why (thread-local, valid until the thread's
+ * next call). All pointers must belong to the device that is current when the call is made.
+ *
+ * Each function names the interface of the reference project (elwhyjay/nvfp4-mla) that it replaces, by the file's
+ * path inside that project.
+ */
+#ifndef NVFP4_MLA_B200_H_
+#define NVFP4_MLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NVFP4_MLA_API __attribute__((visibility("default")))
+#else
+#define NVFP4_MLA_API
+#endif
+
+#define NVFP4_MLA_PRECISION_BF16 0 /* exact FP16 K/V operands, FP16 P, fp32 accumulation */
+#define NVFP4_MLA_PRECISION_FP8 1  /* E4M3 query rows, K, V and P, fp32 accumulation */
+
+/* Library version as major * 10000 + minor * 100 + patch. */
+NVFP4_MLA_API int nvfp4_mla_version(void);
+
+/* Message of the calling thread's most recent failed call ("" if none). */
+NVFP4_MLA_API const char* nvfp4_mla_last_error(void);
+
+/* Bytes of scratch nvfp4_mla_decode needs for this problem on the current device. `num_splits` as in the decode
+ * call. Replaces the torch::empty of o_part / lse_part inside the reference launcher
+ * (nvfp4_mla/csrc/mla_decode.cu:1042-1047). Returns -1 on invalid arguments. */
+NVFP4_MLA_API int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits);
+
+/* Absorbed-MLA decode, one query token per request, over the NVFP4 paged latent-KV cache.
+ * Replaces the pybind `decode` of the reference (nvfp4_mla/csrc/mla_decode.cu:1063-1085, launcher :984-1061), which
+ * nvfp4_mla.decode calls (nvfp4_mla/__init__.py:47-81).
+ *
+ *   q_nope       [batch, heads, 512] bfloat16, contiguous        q_pe  [batch, heads, 64] bfloat16, contiguous
+ *   ckv_cache    [num_pages, page_size, 256] uint8   packed E2M1, low nibble = even channel
+ *   ckv_sf_cache [num_pages, page_size, 32]  E4M3    one scale per 16 channels
+ *   kpe_cache    [num_pages, page_size, 64]  E4M3
+ *   page_table   [batch, page_table_stride] int32 page ids (only the first ceil(kv_len / page_size) are read)
+ *   kv_lens      [batch] int32; read on the device, never on the host
+ *   heads        a multiple of 16;  page_size a power of two;  ckv_scale, kpe_scale > 0
+ *   max_kv_len   upper bound of kv_lens: with num_splits it fixes the launch shape, so the same call can be
+ *                captured in a CUDA graph and replayed with other kv_lens below the bound
+ *   num_splits   0 = one KV range per request (work is still balanced over all SMs tile by tile);
+ *                n > 0 = cut every request at multiples of round_up(ceil(max_kv_len / n), 128) tokens as well
+ *   precision    NVFP4_MLA_PRECISION_*
+ *   out          [batch, heads, 512] bfloat16 or NULL
+ *   out_f32      [batch, heads, 512] float or NULL: the same result unrounded (for merging across GPUs)
+ *   lse          [batch, heads] float or NULL: log2-domain log-sum-exp of the scaled scores, i.e.
+ *                log2(sum_t exp(score_t)), -inf for kv_len 0 (the unit of the reference's split partials,
+ *                nvfp4_mla/csrc/mla_decode.cu:478-492)
+ *   workspace    at least nvfp4_mla_decode_workspace_bytes() bytes, 256-byte aligned; its first int32 is a sticky
+ *                device-side status word that the caller zeroes once (see nvfp4_mla_workspace_status)
+ */
+NVFP4_MLA_API int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
+                     const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
+                     int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale,
+                     float ckv_scale, float kpe_scale, int max_kv_len, int num_splits, int precision, void* out,
+                     float* out_f32, float* lse, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Synchronises `stream` and returns the status word of a decode workspace: 0 = every kernel ran to completion,
+ * 1 = a bounded wait inside the decode kernel gave up (results invalid), 2 = batch * num_splits too large for the
+ * schedule kernel; negative = CUDA error (see nvfp4_mla_last_error). No counterpart in the reference, whose kernels
+ * have no bounded waits. */
+NVFP4_MLA_API int nvfp4_mla_workspace_status(const void* workspace, void* stream);
+
+/* Whole-cache dequantisation: ckv = e2m1 * block_scale * ckv_scale, kpe = e4m3 * kpe_scale, in that multiply
+ * order, to float (out_bf16 = 0) or bfloat16 (out_bf16 = 1). num_tokens = num_pages * page_size.
+ * Replaces the pybind `dequantize` (nvfp4_mla/csrc/mla_decode.cu:1113-1132; nvfp4_mla/__init__.py:84-92). */
+NVFP4_MLA_API int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache, const uint8_t* kpe_cache,
+                         int64_t num_tokens, float ckv_scale, float kpe_scale, int out_bf16, void* ckv_out,
+                         void* kpe_out, void* stream);
+
+/* Log-sum-exp merge of `parts` partial results: o_part [parts, rows, 512] float (each normalised by its own
+ * softmax sum), lse_part [parts, rows] float in log2 units (-inf = empty partial, weight 0). Any of out
+ * (bfloat16 [rows, 512]), out_f32 (float [rows, 512]) and lse (float [rows]) may be NULL.
+ * Replaces the pybind `combine` (nvfp4_mla/csrc/mla_decode.cu:1281-1294, kernel :933-966); also the merge step of
+ * sequence-sharded decode across GPUs. */
+NVFP4_MLA_API int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32,
+                      float* lse, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_MLA_B200_H_ */

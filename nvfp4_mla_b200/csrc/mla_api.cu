@@ -1,0 +1,243 @@
+// C ABI of libnvfp4_mla_b200.so: argument validation, the TMA descriptor of the cache, and kernel launches.
+// Declarations and their documentation: include/nvfp4_mla_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/nvfp4_mla_b200.h"
+#include "mla_common.cuh"
+#include "mla_decode_sm100.cuh"
+#include "mla_dequant.cuh"
+#include "mla_schedule.cuh"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return 1;
+}
+#define MLA_CHECK(cond, ...) \
+  do {                       \
+    if (!(cond)) return fail(__VA_ARGS__); \
+  } while (0)
+#define MLA_CUDA(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess) return fail("%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+};
+std::mutex g_mutex;
+DeviceInfo g_devices[kMaxDevices];
+
+using DecodeKernel = void (*)(const CUtensorMap, const mla::DecodeParams);
+constexpr int kHeadsPerCta = 16;
+constexpr int kRawSlots = 3;
+DecodeKernel decode_kernel() { return mla::mla_decode_kernel<kHeadsPerCta, kRawSlots>; }
+constexpr size_t kDecodeSmem = mla::decode_smem_bytes<kHeadsPerCta, kRawSlots>();
+
+// Per-device one-time setup (SM count, opt-in shared memory). Must first run outside stream capture.
+int device_info(DeviceInfo** out) {
+  int dev = 0;
+  MLA_CUDA(cudaGetDevice(&dev));
+  MLA_CHECK(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_devices[dev];
+  if (!d.ready) {
+    int major = 0;
+    MLA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    MLA_CHECK(major == 10, "nvfp4_mla_b200 needs an sm_100a GPU (B200), found compute capability %d.x", major);
+    MLA_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    MLA_CUDA(cudaFuncSetAttribute(decode_kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSmem)));
+    d.ready = true;
+  }
+  *out = &d;
+  return 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MLA_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    MLA_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  *out = fn;
+  return 0;
+}
+
+// ckv_cache as a 2-D byte tensor [num_pages * page_size, 256]; a box is min(page_size, 64) token rows by 128 bytes,
+// written to shared memory with the 128-byte swizzle that makes thread-per-token reads conflict free.
+int make_ckv_map(const uint8_t* ckv, int64_t rows, int page_size, CUtensorMap* map) {
+  EncodeTiledFn encode;
+  if (encode_fn(&encode)) return 1;
+  const cuuint64_t dims[2] = {256, cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {256};
+  const cuuint32_t box[2] = {128, cuuint32_t(page_size < mla::HALF ? page_size : mla::HALF)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(ckv), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MLA_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return 0;
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, mla::Problem* pb) {
+  MLA_CHECK(batch >= 0, "batch must be non-negative");
+  MLA_CHECK(heads > 0 && heads % 16 == 0, "heads must be a multiple of 16, got %d", heads);
+  MLA_CHECK(num_splits >= 0, "num_splits must be non-negative");
+  const int splits = num_splits > 0 ? num_splits : 1;
+  const long long len = max_kv_len > 1 ? max_kv_len : 1;
+  const long long chunk = ((len + splits - 1) / splits + mla::TILE - 1) / mla::TILE * mla::TILE;
+  pb->batch = batch, pb->heads = heads, pb->heads_per_cta = kHeadsPerCta, pb->head_groups = heads / kHeadsPerCta;
+  pb->splits = splits, pb->chunk = int(chunk), pb->n_cta = n_cta;
+  MLA_CHECK((long long)batch * splits <= mla::kSchedMaxBZ, "batch * num_splits = %lld exceeds %d", (long long)batch * splits,
+            mla::kSchedMaxBZ);
+  MLA_CHECK(splits + n_cta <= 512, "num_splits %d too large (at most %d)", splits, 512 - n_cta);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_mla_version(void) { return 100; }
+
+const char* nvfp4_mla_last_error(void) { return g_error; }
+
+int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
+  DeviceInfo* d;
+  if (device_info(&d)) return -1;
+  mla::Problem pb;
+  if (problem_of(batch, heads, 1, num_splits, d->sm_count, &pb)) return -1;
+  return int64_t(mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total);
+}
+
+int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
+                     const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
+                     int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale, float ckv_scale,
+                     float kpe_scale, int max_kv_len, int num_splits, int precision, void* out, float* out_f32, float* lse,
+                     void* workspace, int64_t workspace_bytes, void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16 || precision == NVFP4_MLA_PRECISION_FP8,
+            "precision must be 0 (bf16) or 1 (fp8), got %d", precision);
+  MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16, "precision fp8 is not built into this library yet");
+  MLA_CHECK(page_size > 0 && (page_size & (page_size - 1)) == 0, "page_size must be a power of two, got %d", page_size);
+  MLA_CHECK(num_pages > 0 && num_pages * page_size < (int64_t(1) << 31), "num_pages * page_size must be in [1, 2^31)");
+  MLA_CHECK(ckv_scale > 0.f && kpe_scale > 0.f, "ckv_scale and kpe_scale must be positive");
+  MLA_CHECK(q_nope && q_pe && ckv_cache && ckv_sf_cache && kpe_cache && page_table && kv_lens && workspace, "null pointer argument");
+  MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
+  MLA_CHECK(aligned(q_nope, 16) && aligned(q_pe, 16) && aligned(ckv_cache, 16) && aligned(ckv_sf_cache, 16) &&
+                aligned(kpe_cache, 16) && aligned(workspace, 256) && aligned(out, 16) && aligned(out_f32, 16),
+            "q, caches and outputs must be 16-byte aligned and the workspace 256-byte aligned");
+  MLA_CHECK(page_table_stride >= 0, "page_table_stride must be non-negative");
+  DeviceInfo* d;
+  if (device_info(&d)) return 1;
+  mla::Problem pb;
+  if (problem_of(batch, heads, max_kv_len, num_splits, d->sm_count, &pb)) return 1;
+  if (batch == 0) return 0;
+  const mla::WsLayout L = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta);
+  MLA_CHECK(workspace_bytes >= int64_t(L.total), "workspace too small: %lld bytes given, %lld needed", (long long)workspace_bytes,
+            (long long)L.total);
+
+  CUtensorMap ckv_map;
+  if (make_ckv_map(ckv_cache, num_pages * page_size, page_size, &ckv_map)) return 1;
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* header = reinterpret_cast<int*>(ws + L.header);
+  int2* cta_range = reinterpret_cast<int2*>(ws + L.cta_range);
+  int2* item_range = reinterpret_cast<int2*>(ws + L.item_range);
+  mla::Seg* segs = reinterpret_cast<mla::Seg*>(ws + L.segs);
+  float* lse_part = reinterpret_cast<float*>(ws + L.lse_part);
+  float* o_part = reinterpret_cast<float*>(ws + L.o_part);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  mla::mla_schedule_kernel<<<1, mla::kSchedThreads, 0, st>>>(kv_lens, pb, header, cta_range, item_range, segs);
+  MLA_CUDA(cudaGetLastError());
+
+  mla::DecodeParams P;
+  P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
+  P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
+  P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads;
+  P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
+  P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
+  decode_kernel()<<<pb.n_cta, mla::kDecodeThreads, kDecodeSmem, st>>>(ckv_map, P);
+  MLA_CUDA(cudaGetLastError());
+
+  mla::mla_combine_sched_kernel<<<unsigned(batch) * unsigned(heads), mla::kCombineThreads, 0, st>>>(pb, item_range, lse_part, o_part,
+                                                                                                out, out_f32, lse);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_mla_workspace_status(const void* workspace, void* stream) {
+  g_error[0] = 0;
+  if (!workspace) return -fail("null workspace");
+  int status = 0;
+  cudaError_t e = cudaMemcpyAsync(&status, workspace, sizeof status, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return -fail("reading the workspace status failed: %s", cudaGetErrorString(e));
+  return status;
+}
+
+int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache, const uint8_t* kpe_cache, int64_t num_tokens,
+                         float ckv_scale, float kpe_scale, int out_bf16, void* ckv_out, void* kpe_out, void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(num_tokens >= 0, "num_tokens must be non-negative");
+  if (num_tokens == 0) return 0;
+  MLA_CHECK(ckv_cache && ckv_sf_cache && kpe_cache && ckv_out && kpe_out, "null pointer argument");
+  MLA_CHECK(aligned(ckv_cache, 2) && aligned(kpe_cache, 2) && aligned(ckv_out, 16) && aligned(kpe_out, 8),
+            "caches must be 2-byte aligned, ckv_out 16-byte and kpe_out 8-byte aligned");
+  DeviceInfo* d;
+  if (device_info(&d)) return 1;
+  const long long warps_per_block = mla::kDequantThreads / 32;
+  long long blocks = (num_tokens + warps_per_block - 1) / warps_per_block;
+  const long long cap = (long long)d->sm_count * 32;  // grid-stride beyond 32 CTAs per SM
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_bf16)
+    mla::mla_dequant_kernel<__nv_bfloat16><<<unsigned(blocks), mla::kDequantThreads, 0, st>>>(
+        ckv_cache, ckv_sf_cache, kpe_cache, ckv_scale, kpe_scale, static_cast<__nv_bfloat16*>(ckv_out),
+        static_cast<__nv_bfloat16*>(kpe_out), num_tokens);
+  else
+    mla::mla_dequant_kernel<float><<<unsigned(blocks), mla::kDequantThreads, 0, st>>>(
+        ckv_cache, ckv_sf_cache, kpe_cache, ckv_scale, kpe_scale, static_cast<float*>(ckv_out), static_cast<float*>(kpe_out),
+        num_tokens);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32, float* lse,
+                      void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(parts > 0 && rows >= 0, "parts must be positive and rows non-negative");
+  if (rows == 0) return 0;
+  MLA_CHECK(o_part && lse_part, "null pointer argument");
+  MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
+  MLA_CHECK(aligned(o_part, 16) && aligned(out, 8) && aligned(out_f32, 16), "o_part and out_f32 must be 16-byte, out 8-byte aligned");
+  MLA_CHECK(rows < (int64_t(1) << 31), "rows must be below 2^31");
+  mla::mla_combine_dense_kernel<<<unsigned(rows), mla::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      o_part, lse_part, parts, rows, out, out_f32, lse);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,562 @@
+// Weight-absorbed MLA decode over the NVFP4 paged latent-KV cache for sm_100a.
+//
+// Data path (one CTA per SM, persistent over the work the schedule kernel assigned to it):
+//
+//   HBM --TMA--> raw ring (smem) --convert warps--> K as FP16 in TENSOR MEMORY (tokens = lanes)  --QK^T--> S^T (TMEM)
+//                                              \--> V as FP16 in smem, [token][channel]           --PV----> O^T (TMEM)
+//
+// Tokens are the M dimension of both MMAs (128 per tile); the heads of the CTA are N (16 or 32), so 16 heads are
+// never padded to the MMA's minimum M.
+//   QK^T : S^T[token, head] = K[token, 576] . Q^T          A = K from tensor memory, B = Q^T from smem (K-major)
+//   PV   : O^T[chan, head] += V^T[chan, token] . P^T       A = V from smem read MN-major (the [token][channel] tile
+//          IS V^T with M contiguous), B = P^T from smem (K-major), 4 blocks of 128 channels
+// One dequantisation (thread = token, registers = channels) feeds both: the FP16 values go to tensor memory with
+// tcgen05.st and to the swizzled V tile with st.shared. FP16 holds e2m1 x e4m3 exactly (6 significant bits,
+// 2^-10 .. 2688), so K and V are the cache's values bit for bit; the query is converted to FP16 after an exact
+// per-row power-of-two scaling that the score scale undoes.
+//
+// Warp roles (512 threads): 0-3 softmax + epilogue (thread = token row of S^T / channel row of O^T),
+// 4-11 dequantise (warp%4 = TMEM lane quadrant, two warps per quadrant split the channel panels), 12 MMA issue,
+// 13 TMA producer. Softmax keeps one running max per head shared by all 128 token rows and rescales O^T in
+// tensor memory only when some score outgrows it by 2^8 (a CTA-wide vote per tile), so the common tile has no
+// cross-thread traffic except that vote.
+//
+// Every wait is bounded (ptx::mbar_wait): a protocol error sets an abort flag, every role leaves its loop, the CTA
+// frees its tensor memory and the kernel reports kWaitTimeout in the workspace header.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "mla_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace mla {
+
+constexpr int kDecodeThreads = 512;
+constexpr int kSegBatch = 32;
+constexpr int kRawSlotBytes = HALF * TOKEN_BYTES;  // 22528: ckv lo | ckv hi | sf | kpe
+constexpr int kRawCkvHi = HALF * 128, kRawSf = 2 * HALF * 128, kRawKpe = kRawSf + HALF * 32;
+constexpr int kVPanelBytes = TILE * 128;  // one 64-channel panel of the FP16 V tile
+constexpr int kTmemCols = 512;
+
+struct DecodeParams {
+  const __nv_bfloat16* q_nope;
+  const __nv_bfloat16* q_pe;
+  const uint8_t* sf;
+  const uint8_t* kpe;
+  const int* page_table;
+  long long pt_stride;
+  int page_shift;  // log2(page_size)
+  int heads;
+  float sm_scale_log2, ckv_scale, kpe_scale;
+  const int2* cta_range;
+  const Seg* segs;
+  float* lse_part;
+  float* o_part;
+  int* header;
+};
+
+template <int N, int RAW_SLOTS>
+struct DecodeSmem {
+  alignas(1024) uint8_t v16[8][kVPanelBytes];       // V tile: panel p = channels [64p, 64p+64), row = token, 128-B swizzle
+  alignas(1024) uint8_t q[9][N * 128];              // Q^T: panel p = channels [64p, +64) (panel 8 = rope), row = head
+  alignas(1024) uint8_t p[2][N * 128];              // P^T: panel = 64 tokens, row = head
+  alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
+  Seg segs[kSegBatch];
+  float qa[2][N], qb[2][N];                         // per-head score scales (latent / rope part), by segment parity
+  float red[4][N];                                  // softmax group: per-warp partial reductions
+  unsigned int qamax[N];
+  alignas(8) uint64_t raw_full[RAW_SLOTS];
+  uint64_t raw_empty[RAW_SLOTS];
+  uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {2g, 2g+1}, chunk 4 = rope
+  uint64_t v_free[4];                               // PV finished reading V panels {2mb, 2mb+1}
+  uint64_t s_full, p_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int N, int RAW_SLOTS>
+constexpr size_t decode_smem_bytes() { return sizeof(DecodeSmem<N, RAW_SLOTS>) + 1024; }
+
+// tensor-memory columns
+template <int N> struct Cols {
+  static constexpr uint32_t K = 0, KROPE = 256, SN = 288, SP = 288 + N, O = 288 + 2 * N;
+  static_assert(O + 4 * N <= kTmemCols, "tensor memory overflow");
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: TMA producer (one warp; lane 0 issues, all lanes help with page ids)
+// ---------------------------------------------------------------------------------------------------------------
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+                                              int n_segs, uint32_t& hcount) {
+  const int lane = ptx::lane_id();
+  const int ps = 1 << P.page_shift;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    const int* pt = P.page_table + (long long)seg.b * P.pt_stride;
+    for (int hk = 0; hk < 2 * seg.ntiles; ++hk, ++hcount) {
+      const int slot = hcount % RAW_SLOTS;
+      const uint32_t use = hcount / RAW_SLOTS;
+      bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
+      if (!__all_sync(~0u, ok)) return;
+      const int tok = seg.tok0 + hk * HALF;
+      int nvalid = seg.tok_end - tok;
+      nvalid = nvalid < 0 ? 0 : (nvalid > HALF ? HALF : nvalid);
+      uint8_t* dst = s.raw[slot];
+      uint64_t* bar = &s.raw_full[slot];
+      if (nvalid == 0) {
+        if (lane == 0) ptx::mbar_arrive(bar);
+      } else if (ps >= HALF) {
+        if (lane == 0) {
+          const int page = pt[tok >> P.page_shift];
+          const int row = (page << P.page_shift) + (tok & (ps - 1));
+          ptx::mbar_arrive_expect_tx(bar, HALF * TOKEN_BYTES);
+          ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kRawCkvHi, ckv_map, 128, row, bar);
+          ptx::bulk_load(dst + kRawSf, P.sf + (long long)row * 32, HALF * 32, bar);
+          ptx::bulk_load(dst + kRawKpe, P.kpe + (long long)row * 64, HALF * 64, bar);
+          // L2 prefetch a few slots ahead (the ring itself is too shallow to cover HBM latency)
+          const int tok_pf = tok + 6 * HALF;
+          if (tok_pf < seg.tok_end) {
+            const int page2 = pt[tok_pf >> P.page_shift];
+            const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
+            ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
+            ptx::bulk_prefetch_l2(P.sf + (long long)row2 * 32, HALF * 32);
+            ptx::bulk_prefetch_l2(P.kpe + (long long)row2 * 64, HALF * 64);
+          }
+        }
+      } else {
+        // small pages: one box per page that holds a valid token, lanes share the pages
+        const int npages = (nvalid + ps - 1) >> P.page_shift;
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(npages) * ps * TOKEN_BYTES);
+        __syncwarp();
+        for (int pi = lane; pi < npages; pi += 32) {
+          const int page = pt[(tok >> P.page_shift) + pi];
+          const int row = page << P.page_shift, r0 = pi << P.page_shift;
+          ptx::tma_load_2d(dst + r0 * 128, ckv_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kRawCkvHi + r0 * 128, ckv_map, 128, row, bar);
+          ptx::bulk_load(dst + kRawSf + r0 * 32, P.sf + (long long)row * 32, ps * 32, bar);
+          ptx::bulk_load(dst + kRawKpe + r0 * 64, P.kpe + (long long)row * 64, ps * 64, bar);
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: dequantise (8 warps). cw = warp - 4: quadrant = cw % 4 (tensor-memory lanes), hf = cw / 4 (panel parity).
+// ---------------------------------------------------------------------------------------------------------------
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int ct, int par) {
+  // ct = 0..255. Pass 1: per-row amax (positive floats compare as unsigned ints). Pass 2: scale by 2^(14 - e) so the
+  // row's largest magnitude lies in [2^14, 2^15), convert to FP16, store swizzled; the score scale undoes it.
+  if (ct < N) s.qamax[ct] = 0;
+  ptx::bar_sync(2, 256);
+  const long long row0 = (long long)seg.b * P.heads + (long long)seg.hg * N;
+  constexpr int CH = (CKV + KPE) / 8;  // 72 chunks of 8 channels per row
+  for (int i = ct; i < N * CH; i += 256) {
+    const int n = i / CH, c = i % CH;
+    const uint4 v = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
+                           : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    unsigned int m = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned int lo = (w[j] << 16) & 0x7FFFFFFFu, hi = w[j] & 0x7FFF0000u;
+      m = max(m, max(lo, hi));
+    }
+    if (m < 0x7F800000u) atomicMax(&s.qamax[n], m);  // ignore inf / nan for the scale
+  }
+  ptx::bar_sync(2, 256);
+  for (int i = ct; i < N * CH; i += 256) {
+    const int n = i / CH, c = i % CH;
+    int e = int(s.qamax[n] >> 23) - 127;       // floor(log2(amax)); -127 for 0 / subnormal rows
+    e = e < -100 ? -100 : e;
+    const float up = __uint_as_float(uint32_t(14 - e + 127) << 23);  // 2^(14 - e), exact
+    const uint4 v = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
+                           : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      h[j] = ptx::f32x2_to_f16x2(__uint_as_float(w[j] << 16) * up, __uint_as_float(w[j] & 0xFFFF0000u) * up);
+    const int panel = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(s.q[panel] + n * 128 + ((cc ^ (n & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+    if (c == 0) {
+      const float down = __uint_as_float(uint32_t(e - 14 + 127) << 23);  // 2^(e - 14)
+      s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * down;
+      s.qb[par][n] = P.sm_scale_log2 * P.kpe_scale * down;
+    }
+  }
+  ptx::fence_proxy_async_smem();
+}
+
+// One tile of one convert thread; false = a wait gave up.
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const Seg& seg, int t, uint32_t it, int lane, int quad,
+                                             int hf) {
+  const int r = quad * 32 + lane;  // token row of the tile = tensor-memory lane
+  const int half = r >> 6, rr = r & 63;
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
+  const uint32_t hidx = 2 * it + half;
+  const int slot = hidx % RAW_SLOTS;
+  bool ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
+  if (!__all_sync(~0u, ok)) return false;
+  const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
+
+  // ---- this thread's share of the token row, to registers; then the raw slot can be refilled
+  const uint8_t* raw = s.raw[slot];
+  uint4 nope[4][2];
+  uint32_t sfw[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int p = 2 * g + hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row
+    const uint8_t* base = raw + (p >> 2) * kRawCkvHi + rr * 128;
+    const int c0 = 2 * (p & 3);
+    nope[g][0] = *reinterpret_cast<const uint4*>(base + (((c0) ^ (rr & 7)) << 4));
+    nope[g][1] = *reinterpret_cast<const uint4*>(base + (((c0 + 1) ^ (rr & 7)) << 4));
+    sfw[g] = *reinterpret_cast<const uint32_t*>(raw + kRawSf + rr * 32 + 4 * p);
+  }
+  const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
+  const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+
+  const uint32_t prev = (it - 1) & 1;  // parity of the previous tile's phase on the per-tile barriers
+  // ---- rope chunk first: it needs no room in the V tile, so it overlaps the previous tile's PV
+  {
+    ok = it == 0 || ptx::mbar_wait(&s.k_free[4], prev, &s.abort_flag);
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tc_fence_after_sync();
+    const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
+    uint32_t h[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
+      h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
+    }
+    ptx::tmem_st16(tm_lane + Cols<N>::KROPE + 16 * hf, h);
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[4]);
+  }
+  // ---- latent panels
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int p = 2 * g + hf;
+    ok = it == 0 || (ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag) && ptx::mbar_wait(&s.v_free[g], prev, &s.abort_flag));
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tc_fence_after_sync();
+    // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
+    const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] >> 16));
+    const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
+                            __byte_perm(s23, s23, 0x3232)};
+    const uint32_t wds[8] = {nope[g][0].x, nope[g][0].y, nope[g][0].z, nope[g][0].w,
+                             nope[g][1].x, nope[g][1].y, nope[g][1].z, nope[g][1].w};
+    uint32_t h[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
+      uint32_t e[4];
+      ptx::e2m1x8_to_f16x8(wds[j], e);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+    }
+    ptx::tmem_st32(tm_lane + Cols<N>::K + 32 * p, h);
+    uint8_t* vrow = s.v16[p] + r * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<uint4*>(vrow + ((c ^ (r & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+    ptx::tmem_wait_st();
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[g]);
+  }
+  return true;
+}
+
+// A warp whose wait gave up does not leave at once: the 256 convert threads meet at a named barrier at the start of
+// every segment, so it carries on (skipping the work) to the next such barrier, where the failure is OR-reduced and
+// all eight warps leave together.
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it,
+                                             uint32_t& seg_count) {
+  const int lane = ptx::lane_id();
+  const int cw = (threadIdx.x >> 5) - 4, quad = cw & 3, hf = cw >> 2;
+  bool dead = false;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
+    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[3], (it - 1) & 1, &s.abort_flag));
+    if (ptx::bar_red_or(2, 256, !ok)) return;
+    load_query<N, RAW_SLOTS>(s, P, seg, cw * 32 + lane, seg_count & 1);
+    ++seg_count;
+    for (int t = 0; t < seg.ntiles; ++t, ++it) {
+      if (!convert_tile<N, RAW_SLOTS>(s, seg, t, it, lane, quad, hf)) {
+        dead = true;
+        break;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: MMA issue (one thread)
+// ---------------------------------------------------------------------------------------------------------------
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs, uint32_t& it) {
+  const uint32_t tm = s.tmem_base;
+  const uint32_t idesc_qk = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, false, false);
+  const uint32_t idesc_pv = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
+  const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q[0]), 16, 1024);
+  const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[0]), 16, 1024);
+  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), kVPanelBytes, 1024);  // MN-major: LBO = next 64 channels
+  for (int si = 0; si < n_segs; ++si) {
+    const int ntiles = s.segs[si].ntiles;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t par = it & 1;
+      // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
+      if (!ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag)) return;
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        ptx::mma_f16_ts(tm + Cols<N>::SP, tm + Cols<N>::KROPE + 8 * ks, q_desc + ((8 * N * 128 + ks * 32) >> 4), idesc_qk, ks > 0);
+      ptx::mma_commit(&s.k_free[4]);
+#pragma unroll 1
+      for (int g = 0; g < 4; ++g) {
+        if (!ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag)) return;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int p = 2 * g + (j >> 2), ks = j & 3;
+          ptx::mma_f16_ts(tm + Cols<N>::SN, tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc_qk,
+                          (g | j) != 0);
+        }
+        ptx::mma_commit(&s.k_free[g]);
+      }
+      ptx::mma_commit(&s.s_full);
+      // ---- O^T += V^T . P^T
+      if (!ptx::mbar_wait(&s.p_full, par, &s.abort_flag)) return;
+      ptx::tc_fence_after_sync();
+#pragma unroll 1
+      for (int mb = 0; mb < 4; ++mb) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((2 * mb * kVPanelBytes + ks * 2048) >> 4),
+                          p_desc + (((ks >> 2) * N * 128 + (ks & 3) * 32) >> 4), idesc_pv, (t | ks) != 0);
+        ptx::mma_commit(&s.v_free[mb]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: softmax + epilogue (4 warps; thread r = token row of S^T and channel row of O^T)
+// ---------------------------------------------------------------------------------------------------------------
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it,
+                                             uint32_t& seg_count) {
+  const int lane = ptx::lane_id(), warp = threadIdx.x >> 5;
+  const int r = threadIdx.x;  // 0..127
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(warp * 32) << 16);
+  constexpr float kGrow = 8.f;  // rescale only when a score exceeds the running max by 2^8 (P stays <= 256)
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    const int par_q = seg_count & 1;
+    ++seg_count;
+    float m[N], lsum[N];
+#pragma unroll
+    for (int h = 0; h < N; ++h) m[h] = -INFINITY, lsum[h] = 0.f;
+
+    for (int t = 0; t < seg.ntiles; ++t, ++it) {
+      bool ok = ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag);
+      ptx::tc_fence_after_sync();
+      float x[N];
+      if (ok) {
+        const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
+#pragma unroll
+        for (int c0 = 0; c0 < N; c0 += 16) {
+          uint32_t sn[16], sp[16];
+          ptx::tmem_ld16(tm_lane + Cols<N>::SN + c0, sn);
+          ptx::tmem_ld16(tm_lane + Cols<N>::SP + c0, sp);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float(sn[j]) * s.qa[par_q][c0 + j] + __uint_as_float(sp[j]) * s.qb[par_q][c0 + j];
+            x[c0 + j] = valid ? v : -INFINITY;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < N; ++h) x[h] = -INFINITY;
+      }
+      bool need = !ok;
+#pragma unroll
+      for (int h = 0; h < N; ++h) need |= x[h] > m[h] + kGrow;
+      if (ptx::bar_red_or(1, 128, need)) {
+        if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
+        // new running max per head over the 128 token rows
+        float tm_[N];
+#pragma unroll
+        for (int h = 0; h < N; ++h) {
+          float v = x[h];
+#pragma unroll
+          for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(~0u, v, o));
+          tm_[h] = v;
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int h = 0; h < N; ++h) s.red[warp][h] = tm_[h];
+        }
+        ptx::bar_sync(1, 128);
+        float corr[N];
+        bool any_scale = false;
+#pragma unroll
+        for (int h = 0; h < N; ++h) {
+          const float mx = fmaxf(fmaxf(s.red[0][h], s.red[1][h]), fmaxf(s.red[2][h], s.red[3][h]));
+          const float mn = fmaxf(m[h], mx);
+          corr[h] = (m[h] == -INFINITY) ? 0.f : ptx::ex2(m[h] - mn);  // mn = -inf only if m = -inf
+          any_scale |= corr[h] != 1.f;
+          lsum[h] *= corr[h];
+          m[h] = mn;
+        }
+        // O^T *= corr per head (column). s_full of this tile was committed after the previous tile's PV, so O^T is
+        // quiescent here; the next PV is not issued before this thread arrives on p_full.
+        if (t > 0 && any_scale) {
+#pragma unroll 1
+          for (int mb = 0; mb < 4; ++mb) {
+#pragma unroll
+            for (int c0 = 0; c0 < N; c0 += 16) {
+              uint32_t o[16];
+              ptx::tmem_ld16(tm_lane + Cols<N>::O + mb * N + c0, o);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr[c0 + j]);
+              ptx::tmem_st16(tm_lane + Cols<N>::O + mb * N + c0, o);
+            }
+          }
+          ptx::tmem_wait_st();
+        }
+      }
+      // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
+#pragma unroll
+      for (int h = 0; h < N; ++h) {
+        const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
+        lsum[h] += pv;
+        const __half ph = __float2half_rn(pv);
+        const uint32_t off = h * 128 + ((((r & 63) >> 3) ^ (h & 7)) << 4) + (r & 7) * 2;
+        *reinterpret_cast<__half*>(s.p[r >> 6] + off) = ph;
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&s.p_full);
+    }
+
+    // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
+    bool ok = ptx::mbar_wait(&s.v_free[3], (it - 1) & 1, &s.abort_flag);
+    if (ptx::bar_red_or(1, 128, !ok)) return;
+    ptx::tc_fence_after_sync();
+#pragma unroll
+    for (int h = 0; h < N; ++h) {
+      float v = lsum[h];
+#pragma unroll
+      for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
+      lsum[h] = v;
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int h = 0; h < N; ++h) s.red[warp][h] = lsum[h];
+    }
+    ptx::bar_sync(1, 128);
+    float inv[N];
+#pragma unroll
+    for (int h = 0; h < N; ++h) {
+      const float l = (s.red[0][h] + s.red[1][h]) + (s.red[2][h] + s.red[3][h]);
+      inv[h] = l > 0.f ? P.ckv_scale / l : 0.f;
+      lsum[h] = l;
+    }
+    const long long slot = (long long)seg.cta + seg.w;
+    float* obase = P.o_part + slot * N * CKV;
+#pragma unroll 1
+    for (int mb = 0; mb < 4; ++mb) {
+#pragma unroll
+      for (int c0 = 0; c0 < N; c0 += 16) {
+        uint32_t o[16];
+        ptx::tmem_ld16(tm_lane + Cols<N>::O + mb * N + c0, o);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) obase[(long long)(c0 + j) * CKV + mb * 128 + r] = __uint_as_float(o[j]) * inv[c0 + j];
+      }
+    }
+    if (r < N) {
+      float l = 0.f, mm = 0.f;
+#pragma unroll
+      for (int h = 0; h < N; ++h)
+        if (h == r) l = lsum[h], mm = m[h];
+      P.lse_part[slot * N + r] = l > 0.f ? mm + log2f(l) : -INFINITY;
+    }
+    ptx::tc_fence_before_sync();
+    ptx::bar_sync(1, 128);  // s.red is reused by the next segment
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------------------------
+template <int N, int RAW_SLOTS>
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = DecodeSmem<N, RAW_SLOTS>;
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
+    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8), ptx::mbar_init(&s.k_free[i], 1);
+    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_free[i], 1);
+    ptx::mbar_init(&s.s_full, 1);
+    ptx::mbar_init(&s.p_full, 128);
+    s.abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&ckv_map);
+  }
+  if (warp == 12) {
+    ptx::tmem_alloc(&s.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+
+  const int2 range = P.cta_range[blockIdx.x];
+  uint32_t it = 0, seg_count = 0, hcount = 0;  // each role advances its own copies identically
+  for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
+    const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
+    if (threadIdx.x < n_segs) {
+      Seg g = P.segs[(long long)blockIdx.x + w0 + threadIdx.x];
+      if (g.cta != int(blockIdx.x) || g.w != w0 + int(threadIdx.x)) g.ntiles = 0;  // empty item or foreign slot
+      s.segs[threadIdx.x] = g;
+    }
+    __syncthreads();
+    if (warp < 4) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
+    else if (warp < 12) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
+    else if (warp == 12) { if (lane == 0) mma_role<N, RAW_SLOTS>(s, n_segs, it); }
+    else if (warp == 13) producer_role<N, RAW_SLOTS>(s, P, &ckv_map, n_segs, hcount);
+    __syncthreads();
+    if (s.abort_flag) break;
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
+}
+
+}  // namespace mla

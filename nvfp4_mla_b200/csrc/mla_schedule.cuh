@@ -1,0 +1,240 @@
+// Split-KV schedule, computed on the device from kv_lens so that the launch shape of the decode kernel never
+// depends on host-visible lengths (no host sync, CUDA-graph safe).
+//
+// The (request, split, head-group) items are laid end to end in units of 128-token tiles and the flattened tile
+// range is cut into n_cta equal pieces, one per decode CTA: every SM streams the same number of tiles whatever the
+// mix of request lengths. A CTA whose piece spans several items produces one partial (o, lse) per item it touches;
+// the partial of (cta, item w) lives in slot cta + w, which is unique because both indices only grow along the cut.
+#pragma once
+#include "mla_common.cuh"
+
+namespace mla {
+
+constexpr int kSchedThreads = 1024;
+constexpr int kSchedMaxBZ = 8192;  // batch * splits the single-block scan holds in shared memory
+
+__global__ void __launch_bounds__(kSchedThreads, 1)
+mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, int2* cta_range, int2* item_range, Seg* segs) {
+  __shared__ int tiles[kSchedMaxBZ];      // tiles of (b, z), then its exclusive prefix
+  __shared__ int warp_sums[kSchedThreads / 32];
+  __shared__ int total_bz;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int BZ = pb.batch * pb.splits;
+  if (BZ > kSchedMaxBZ) {
+    if (tid == 0) header[0] = kBadSchedule;
+    return;
+  }
+  const int HG = pb.head_groups;
+
+  // ---- tiles per (b, z) and their exclusive prefix (block scan, kSchedMaxBZ / kSchedThreads entries per thread)
+  constexpr int PER = kSchedMaxBZ / kSchedThreads;
+  int local[PER], sum = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int bz = tid * PER + j;
+    int t = 0;
+    if (bz < BZ) {
+      const int b = bz / pb.splits, z = bz % pb.splits;
+      const int len = kv_lens[b];
+      const long long lo = (long long)z * pb.chunk;
+      long long n = (long long)len - lo;
+      n = n < 0 ? 0 : (n > pb.chunk ? pb.chunk : n);
+      t = int((n + TILE - 1) / TILE);
+    }
+    local[j] = sum;
+    sum += t;
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(~0u, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int v = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(~0u, v, o);
+      if (lane >= o) v += u;
+    }
+    warp_sums[lane] = v;  // inclusive over warps
+    if (lane == 31) total_bz = v;
+  }
+  __syncthreads();
+  const int base = incl - sum + (warp ? warp_sums[warp - 1] : 0);
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int bz = tid * PER + j;
+    if (bz < BZ) tiles[bz] = base + local[j];  // exclusive prefix of tiles over (b, z)
+  }
+  __syncthreads();
+  const long long T = (long long)total_bz * HG;
+  const int q = int(T > 0 ? (T + pb.n_cta - 1) / pb.n_cta : 1);
+  if (tid == 0) header[1] = int(T), header[2] = q;
+  auto prefix = [&](int bz) { return bz < BZ ? tiles[bz] : total_bz; };  // exclusive prefix, in (b, z) tiles
+  auto tiles_of = [&](int bz) { return prefix(bz + 1) - prefix(bz); };
+
+  // ---- invalidate every slot, then fill the live ones
+  const long long W = pb.items();
+  for (long long i = tid; i < W + pb.n_cta; i += kSchedThreads) segs[i].cta = -1, segs[i].ntiles = 0;
+  __syncthreads();
+
+  // ---- per CTA: the items its tile range [c * q, (c + 1) * q) touches
+  for (int c = tid; c < pb.n_cta; c += kSchedThreads) {
+    const long long g0 = (long long)c * q, g1 = (g0 + q < T ? g0 + q : T);
+    int2 r = make_int2(0, 0);
+    if (g0 < g1) {
+      auto item_of = [&](long long g) {  // item containing flat tile g
+        int lo = 0, hi = BZ - 1;         // last bz with HG * prefix(bz) <= g
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if ((long long)HG * prefix(mid) <= g) lo = mid; else hi = mid - 1;
+        }
+        const int t = tiles_of(lo);
+        const int hg = t > 0 ? int((g - (long long)HG * prefix(lo)) / t) : 0;
+        return lo * HG + hg;
+      };
+      r = make_int2(item_of(g0), item_of(g1 - 1) + 1);
+    }
+    cta_range[c] = r;
+  }
+
+  // ---- per item: the CTAs that hold a piece of it, and one Seg per piece
+  for (long long w = tid; w < W; w += kSchedThreads) {
+    const int bz = int(w / HG), hg = int(w % HG);
+    const int t = tiles_of(bz);
+    if (t == 0) {
+      item_range[w] = make_int2(0, -1);
+      continue;
+    }
+    const int b = bz / pb.splits, z = bz % pb.splits;
+    const long long P = (long long)HG * prefix(bz) + (long long)hg * t;
+    const int c0 = int(P / q), c1 = int((P + t - 1) / q);
+    item_range[w] = make_int2(c0, c1);
+    const int len = kv_lens[b];
+    const long long end = (long long)(z + 1) * pb.chunk;
+    for (int c = c0; c <= c1; ++c) {
+      const long long lo = ((long long)c * q > P ? (long long)c * q : P) - P;
+      const long long hi = ((long long)(c + 1) * q < P + t ? (long long)(c + 1) * q : P + t) - P;
+      Seg s;
+      s.b = b, s.hg = hg, s.tok0 = z * pb.chunk + int(lo) * TILE, s.ntiles = int(hi - lo);
+      s.tok_end = int(end < len ? end : len), s.w = int(w), s.cta = c, s.pad = 0;
+      segs[c + w] = s;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Merge of the partials of one output row (b, h): out = sum_i 2^(lse_i - M) o_i / sum_i 2^(lse_i - M).
+// One CTA of 128 threads per row; each thread owns 4 channels. Log-sum-exp weights are computed by the lanes of a
+// warp in parallel (one partial per lane) and reduced with shuffles; every warp repeats that small reduction so the
+// four warps never have to meet.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kCombineThreads = 128;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(~0u, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
+  return v;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// Shared tail: `n_parts` partials whose (lse, o-row) addresses are produced by `lse_of(i)` / `o_of(i)`.
+template <class LseOf, class OOf>
+__device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, long long row, void* out_bf16,
+                                          float* out_f32, float* lse_out) {
+  const int lane = threadIdx.x & 31;
+  float M = -INFINITY;
+  for (int i = lane; i < n_parts; i += 32) M = fmaxf(M, lse_of(i));
+  M = warp_max(M);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  if (M > -INFINITY) {
+    for (int i0 = 0; i0 < n_parts; i0 += 32) {
+      const int i = i0 + lane;
+      const float wl = i < n_parts ? exp2f(lse_of(i) - M) : 0.f;  // lse = -inf (empty partial) gives weight 0
+      den += wl;
+      const int cnt = n_parts - i0 < 32 ? n_parts - i0 : 32;
+      for (int j = 0; j < cnt; ++j) {
+        const float wj = __shfl_sync(~0u, wl, j);
+        if (wj != 0.f) {
+          const float4 v = reinterpret_cast<const float4*>(o_of(i0 + j))[threadIdx.x];
+          acc.x += wj * v.x, acc.y += wj * v.y, acc.z += wj * v.z, acc.w += wj * v.w;
+        }
+      }
+    }
+    den = warp_sum(den);
+  }
+  const float s = den > 0.f ? 1.f / den : 0.f;
+  acc.x *= s, acc.y *= s, acc.z *= s, acc.w *= s;
+  if (out_bf16)
+    reinterpret_cast<uint2*>(out_bf16)[row * (CKV / 4) + threadIdx.x] =
+        make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+  if (out_f32) reinterpret_cast<float4*>(out_f32)[row * (CKV / 4) + threadIdx.x] = acc;
+  if (lse_out && threadIdx.x == 0) lse_out[row] = den > 0.f ? M + log2f(den) : -INFINITY;
+}
+
+// Partials addressed through the schedule (what the decode kernel wrote).
+__global__ void __launch_bounds__(kCombineThreads)
+mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const float* __restrict__ lse_part,
+                         const float* __restrict__ o_part, void* out_bf16, float* out_f32, float* lse_out) {
+  __shared__ int slots[512];
+  __shared__ int n_parts_s;
+  const long long row = blockIdx.x;
+  const int b = int(row / pb.heads), h = int(row % pb.heads);
+  const int N = pb.heads_per_cta, hg = h / N, n = h % N;
+  if (threadIdx.x < 32) {  // enumerate the row's partial slots: splits z, CTAs c0..c1 of item (b, z, hg)
+    int count = 0;
+    for (int z0 = 0; z0 < pb.splits; z0 += 32) {
+      const int z = z0 + threadIdx.x;
+      int c0 = 0, c1 = -1;
+      long long w = 0;
+      if (z < pb.splits) {
+        w = ((long long)b * pb.splits + z) * pb.head_groups + hg;
+        const int2 r = item_range[w];
+        c0 = r.x, c1 = r.y;
+      }
+      const int mine = c1 >= c0 ? c1 - c0 + 1 : 0;
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(~0u, incl, o);
+        if (int(threadIdx.x) >= o) incl += v;
+      }
+      int pos = count + incl - mine;
+      for (int c = c0; c <= c1; ++c, ++pos)
+        if (pos < 512) slots[pos] = int(c + w);
+      count += __shfl_sync(~0u, incl, 31);
+    }
+    if (threadIdx.x == 0) n_parts_s = count < 512 ? count : 512;
+  }
+  __syncthreads();
+  const int n_parts = n_parts_s;
+  merge_row(
+      n_parts, [&](int i) { return lse_part[(long long)slots[i] * N + n]; },
+      [&](int i) { return o_part + ((long long)slots[i] * N + n) * CKV; }, row, out_bf16, out_f32, lse_out);
+}
+
+// Dense partials [parts, rows, 512] / [parts, rows]: the merge a caller runs on (o, lse) pairs gathered from
+// several GPUs or produced by its own splits.
+__global__ void __launch_bounds__(kCombineThreads)
+mla_combine_dense_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, int parts, long long rows,
+                         void* out_bf16, float* out_f32, float* lse_out) {
+  const long long row = blockIdx.x;
+  merge_row(
+      parts, [&](int i) { return lse_part[(long long)i * rows + row]; },
+      [&](int i) { return o_part + ((long long)i * rows + row) * CKV; }, row, out_bf16, out_f32, lse_out);
+}
+
+}  // namespace mla
