@@ -75,6 +75,15 @@ NVFP4_MLA_API int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const u
  * have no bounded waits. */
 NVFP4_MLA_API int nvfp4_mla_workspace_status(const void* workspace, void* stream);
 
+/* Measurement aid: between nvfp4_mla_profile_begin(capacity) and nvfp4_mla_profile_end, every nvfp4_mla_decode call
+ * made by this thread (up to `capacity` of them) brackets its main decode kernel, and only that kernel, with a pair
+ * of CUDA events on the call's stream. profile_end waits for them, writes the kernel durations in milliseconds to
+ * ms[0 .. min(calls, capacity)) and returns how many it wrote (negative on error). The only entry points that create
+ * CUDA objects; not meant for stream capture. Stands where the reference times kernels with CUPTI
+ * (benchmarks/baselines.py:168-187). */
+NVFP4_MLA_API int nvfp4_mla_profile_begin(int capacity);
+NVFP4_MLA_API int nvfp4_mla_profile_end(float* ms, int capacity);
+
 /* Whole-cache dequantisation: ckv = e2m1 * block_scale * ckv_scale, kpe = e4m3 * kpe_scale, in that multiply
  * order, to float (out_bf16 = 0) or bfloat16 (out_bf16 = 1). num_tokens = num_pages * page_size.
  * Replaces the pybind `dequantize` (nvfp4_mla/csrc/mla_decode.cu:1113-1132; nvfp4_mla/__init__.py:84-92). */

@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/nvfp4_mla_b200.h"
 #include "mla_common.cuh"
@@ -98,6 +99,13 @@ int make_ckv_map(const uint8_t* ckv, int64_t rows, int page_size, CUtensorMap* m
   return 0;
 }
 
+// Optional per-call timing of the decode kernel alone (see nvfp4_mla_profile_begin).
+struct Profile {
+  std::vector<cudaEvent_t> start, stop;
+  int used = 0;
+};
+thread_local Profile* g_profile = nullptr;
+
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, mla::Problem* pb) {
@@ -116,6 +124,11 @@ int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, 
 }
 
 }  // namespace
+
+#ifdef MLA_TRACE
+namespace { long long* g_trace = nullptr; }
+extern "C" NVFP4_MLA_API void nvfp4_mla_set_trace(long long* device_buffer) { g_trace = device_buffer; }
+#endif
 
 extern "C" {
 
@@ -179,13 +192,49 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
+#ifdef MLA_TRACE
+  P.trace = g_trace;
+#endif
+  Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
+  if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
   decode_kernel()<<<pb.n_cta, mla::kDecodeThreads, kDecodeSmem, st>>>(ckv_map, P);
   MLA_CUDA(cudaGetLastError());
+  if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
   mla::mla_combine_sched_kernel<<<unsigned(batch) * unsigned(heads), mla::kCombineThreads, 0, st>>>(pb, item_range, lse_part, o_part,
                                                                                                 out, out_f32, lse);
   MLA_CUDA(cudaGetLastError());
   return 0;
+}
+
+int nvfp4_mla_profile_begin(int capacity) {
+  g_error[0] = 0;
+  MLA_CHECK(capacity > 0 && capacity <= (1 << 20), "capacity must be in [1, 2^20]");
+  MLA_CHECK(g_profile == nullptr, "a profile is already open on this thread");
+  Profile* p = new Profile;
+  p->start.resize(capacity), p->stop.resize(capacity);
+  for (int i = 0; i < capacity; ++i) {
+    MLA_CUDA(cudaEventCreate(&p->start[i]));
+    MLA_CUDA(cudaEventCreate(&p->stop[i]));
+  }
+  g_profile = p;
+  return 0;
+}
+
+int nvfp4_mla_profile_end(float* ms, int capacity) {
+  g_error[0] = 0;
+  Profile* p = g_profile;
+  if (!p) return -fail("no profile is open on this thread");
+  g_profile = nullptr;
+  int n = p->used < capacity ? p->used : capacity, rc = n;
+  for (int i = 0; i < p->used; ++i) {
+    cudaError_t e = cudaEventSynchronize(p->stop[i]);
+    if (e == cudaSuccess && i < n) e = cudaEventElapsedTime(&ms[i], p->start[i], p->stop[i]);
+    if (e != cudaSuccess) rc = -fail("reading kernel timings failed: %s", cudaGetErrorString(e));
+  }
+  for (size_t i = 0; i < p->start.size(); ++i) cudaEventDestroy(p->start[i]), cudaEventDestroy(p->stop[i]);
+  delete p;
+  return rc;
 }
 
 int nvfp4_mla_workspace_status(const void* workspace, void* stream) {

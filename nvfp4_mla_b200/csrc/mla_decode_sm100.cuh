@@ -38,6 +38,18 @@ constexpr int kRawCkvHi = HALF * 128, kRawSf = 2 * HALF * 128, kRawKpe = kRawSf 
 constexpr int kVPanelBytes = TILE * 128;  // one 64-channel panel of the FP16 V tile
 constexpr int kTmemCols = 512;
 
+// Optional timeline tracing (compiled in with -DMLA_TRACE): CTA 0 records clock64() at pipeline events of its first
+// kTraceTiles tiles into trace[event][tile].
+#ifdef MLA_TRACE
+constexpr int kTraceTiles = 64, kTraceEvents = 32;
+#define MLA_TRACE_AT(P, ev, tile)                                                             \
+  do {                                                                                        \
+    if ((P).trace && blockIdx.x == 0 && (tile) < mla::kTraceTiles) (P).trace[(ev) * mla::kTraceTiles + (tile)] = clock64(); \
+  } while (0)
+#else
+#define MLA_TRACE_AT(P, ev, tile) do {} while (0)
+#endif
+
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
   const __nv_bfloat16* q_pe;
@@ -53,6 +65,9 @@ struct DecodeParams {
   float* lse_part;
   float* o_part;
   int* header;
+#ifdef MLA_TRACE
+  long long* trace;
+#endif
 };
 
 template <int N, int RAW_SLOTS>
@@ -100,6 +115,7 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS>& s, const
       const uint32_t use = hcount / RAW_SLOTS;
       bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
+      if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 24, hcount >> 1);
       const int tok = seg.tok0 + hk * HALF;
       int nvalid = seg.tok_end - tok;
       nvalid = nvalid < 0 ? 0 : (nvalid > HALF ? HALF : nvalid);
@@ -196,8 +212,9 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const De
 
 // One tile of one convert thread; false = a wait gave up.
 template <int N, int RAW_SLOTS>
-__device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const Seg& seg, int t, uint32_t it, int lane, int quad,
-                                             int hf) {
+__device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
+                                             int lane, int quad, int hf) {
+  const bool tr = (threadIdx.x == 128);  // first convert thread
   const int r = quad * 32 + lane;  // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
@@ -205,6 +222,7 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
   const int slot = hidx % RAW_SLOTS;
   bool ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
   if (!__all_sync(~0u, ok)) return false;
+  if (tr) MLA_TRACE_AT(P, 0, it);
   const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
 
   // ---- this thread's share of the token row, to registers; then the raw slot can be refilled
@@ -224,6 +242,7 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
   const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
   __syncwarp();
   if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+  if (tr) MLA_TRACE_AT(P, 1, it);
 
   const uint32_t prev = (it - 1) & 1;  // parity of the previous tile's phase on the per-tile barriers
   // ---- rope chunk first: it needs no room in the V tile, so it overlaps the previous tile's PV
@@ -243,6 +262,7 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.k_full[4]);
+    if (tr) MLA_TRACE_AT(P, 2, it);
   }
   // ---- latent panels
 #pragma unroll
@@ -250,6 +270,7 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
     const int p = 2 * g + hf;
     ok = it == 0 || (ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag) && ptx::mbar_wait(&s.v_free[g], prev, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
+    if (tr) MLA_TRACE_AT(P, 3 + 2 * g, it);
     ptx::tc_fence_after_sync();
     // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
     const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] >> 16));
@@ -275,6 +296,7 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.k_full[g]);
+    if (tr) MLA_TRACE_AT(P, 4 + 2 * g, it);
   }
   return true;
 }
@@ -297,7 +319,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     load_query<N, RAW_SLOTS>(s, P, seg, cw * 32 + lane, seg_count & 1);
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
-      if (!convert_tile<N, RAW_SLOTS>(s, seg, t, it, lane, quad, hf)) {
+      if (!convert_tile<N, RAW_SLOTS>(s, P, seg, t, it, lane, quad, hf)) {
         dead = true;
         break;
       }
@@ -309,7 +331,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 // role: MMA issue (one thread)
 // ---------------------------------------------------------------------------------------------------------------
 template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs, uint32_t& it) {
+__device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const uint32_t tm = s.tmem_base;
   const uint32_t idesc_qk = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, false, false);
   const uint32_t idesc_pv = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
@@ -322,6 +344,7 @@ __device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs
       const uint32_t par = it & 1;
       // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
       if (!ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag)) return;
+      MLA_TRACE_AT(P, 12, it);
       ptx::tc_fence_after_sync();
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
@@ -330,6 +353,7 @@ __device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs
 #pragma unroll 1
       for (int g = 0; g < 4; ++g) {
         if (!ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag)) return;
+        MLA_TRACE_AT(P, 13 + g, it);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -340,8 +364,10 @@ __device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs
         ptx::mma_commit(&s.k_free[g]);
       }
       ptx::mma_commit(&s.s_full);
+      MLA_TRACE_AT(P, 17, it);
       // ---- O^T += V^T . P^T
       if (!ptx::mbar_wait(&s.p_full, par, &s.abort_flag)) return;
+      MLA_TRACE_AT(P, 18, it);
       ptx::tc_fence_after_sync();
 #pragma unroll 1
       for (int mb = 0; mb < 4; ++mb) {
@@ -351,6 +377,7 @@ __device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, int n_segs
                           p_desc + (((ks >> 2) * N * 128 + (ks & 3) * 32) >> 4), idesc_pv, (t | ks) != 0);
         ptx::mma_commit(&s.v_free[mb]);
       }
+      MLA_TRACE_AT(P, 19, it);
     }
   }
 }
@@ -376,6 +403,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       bool ok = ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag);
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       float x[N];
       if (ok) {
@@ -444,6 +472,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
           ptx::tmem_wait_st();
         }
       }
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
       // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
 #pragma unroll
       for (int h = 0; h < N; ++h) {
@@ -456,6 +485,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s.p_full);
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
@@ -547,7 +577,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     __syncthreads();
     if (warp < 4) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
     else if (warp < 12) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    else if (warp == 12) { if (lane == 0) mma_role<N, RAW_SLOTS>(s, n_segs, it); }
+    else if (warp == 12) { if (lane == 0) mma_role<N, RAW_SLOTS>(s, P, n_segs, it); }
     else if (warp == 13) producer_role<N, RAW_SLOTS>(s, P, &ckv_map, n_segs, hcount);
     __syncthreads();
     if (s.abort_flag) break;

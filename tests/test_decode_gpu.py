@@ -150,7 +150,7 @@ def test_max_kv_len_is_an_upper_bound():
 
 def test_cuda_graph_replay_with_new_lengths():
     """The launch shape depends on max_kv_len only: a captured decode replays correctly after kv_lens change."""
-    big = SyntheticCache([1000, 700, 300], 64, 16, 0.5, 2.0, seed=21).to("cuda")
+    big = SyntheticCache([1024, 1024, 1024], 64, 16, 0.5, 2.0, seed=21).to("cuda")  # every replayed length is written
     args = list(big.args())
     kv = big.kv_lens.clone()
     args[6] = kv
