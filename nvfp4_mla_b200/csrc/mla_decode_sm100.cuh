@@ -10,14 +10,18 @@
 //   QK^T : S^T[token, head] = K[token, 576] . Q^T          A = K from tensor memory, B = Q^T from smem (K-major)
 //   PV   : O^T[chan, head] += V^T[chan, token] . P^T       A = V from smem read MN-major (the [token][channel] tile
 //          IS V^T with M contiguous), B = P^T from smem (K-major), 4 blocks of 128 channels
-// One dequantisation (thread = token, registers = channels) feeds both: the FP16 values go to tensor memory with
-// tcgen05.st and to the swizzled V tile with st.shared. FP16 holds e2m1 x e4m3 exactly (6 significant bits,
-// 2^-10 .. 2688), so K and V are the cache's values bit for bit; the query is converted to FP16 after an exact
-// per-row power-of-two scaling that the score scale undoes.
+// One dequantisation (thread = token, registers = channels) feeds both. Phase A of a tile converts the token row
+// to FP16 and writes it to tensor memory with tcgen05.st, chunk by chunk, so QK^T chases the conversion. Phase B,
+// once the previous tile's PV has released the V tile, copies the same FP16 values from tensor memory to the
+// swizzled V tile (tcgen05.ld + st.shared): the expensive arithmetic never waits for the V buffer.
+// FP16 holds e2m1 x e4m3 exactly (6 significant bits, 2^-10 .. 2688), so K and V are the cache's values bit for
+// bit; the query is converted to FP16 after an exact per-row power-of-two scaling that the score scale undoes.
 //
 // Warp roles (512 threads): 0-3 softmax + epilogue (thread = token row of S^T / channel row of O^T),
-// 4-11 dequantise (warp%4 = TMEM lane quadrant, two warps per quadrant split the channel panels), 12 MMA issue,
-// 13 TMA producer. Softmax keeps one running max per head shared by all 128 token rows and rescales O^T in
+// 4-11 dequantise (warp%4 = TMEM lane quadrant, two warps per quadrant split the channel panels), 12 QK^T issue,
+// 13 TMA producer, 14 PV issue. QK^T and PV have their own issuing warps so that the tensor pipe interleaves
+// QK^T of tile j+1 (as its chunks are converted) with PV of tile j (as softmax and the V copy finish); S^T and P^T
+// are double buffered. Softmax keeps one running max per head shared by all 128 token rows and rescales O^T in
 // tensor memory only when some score outgrows it by 2^8 (a CTA-wide vote per tile), so the common tile has no
 // cross-thread traffic except that vote.
 //
@@ -74,17 +78,20 @@ template <int N, int RAW_SLOTS>
 struct DecodeSmem {
   alignas(1024) uint8_t v16[8][kVPanelBytes];       // V tile: panel p = channels [64p, 64p+64), row = token, 128-B swizzle
   alignas(1024) uint8_t q[9][N * 128];              // Q^T: panel p = channels [64p, +64) (panel 8 = rope), row = head
-  alignas(1024) uint8_t p[2][N * 128];              // P^T: panel = 64 tokens, row = head
+  alignas(1024) uint8_t p[2][2][N * 128];           // P^T, double buffered: [buffer][panel of 64 tokens], row = head
   alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
   Seg segs[kSegBatch];
-  float qa[2][N], qb[2][N];                         // per-head score scales (latent / rope part), by segment parity
+  float qa[4][N];                                   // per-head score scale, ring indexed by segment count
   float red[4][N];                                  // softmax group: per-warp partial reductions
   unsigned int qamax[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
   uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {2g, 2g+1}, chunk 4 = rope
-  uint64_t v_free[4];                               // PV finished reading V panels {2mb, 2mb+1}
-  uint64_t s_full, p_full;
+  uint64_t v_full[4], v_free[4];                    // V panels {2mb, 2mb+1}: written / PV finished reading them
+  // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
+  // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
+  uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
+  uint64_t p_full[2], p_free[2];                    // P^T written by softmax / read by PV (= PV of that tile complete)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -94,7 +101,9 @@ constexpr size_t decode_smem_bytes() { return sizeof(DecodeSmem<N, RAW_SLOTS>) +
 
 // tensor-memory columns
 template <int N> struct Cols {
-  static constexpr uint32_t K = 0, KROPE = 256, SN = 288, SP = 288 + N, O = 288 + 2 * N;
+  static constexpr uint32_t K = 0, KROPE = 256, O = 288 + 4 * N;
+  __host__ __device__ static constexpr uint32_t sn(uint32_t buf) { return 288 + buf * 2 * N; }      // latent part of the scores
+  __host__ __device__ static constexpr uint32_t sp(uint32_t buf) { return 288 + buf * 2 * N + N; }  // rope part
   static_assert(O + 4 * N <= kTmemCols, "tensor memory overflow");
 };
 
@@ -204,18 +213,20 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const De
     if (c == 0) {
       const float down = __uint_as_float(uint32_t(e - 14 + 127) << 23);  // 2^(e - 14)
       s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * down;
-      s.qb[par][n] = P.sm_scale_log2 * P.kpe_scale * down;
     }
   }
   ptx::fence_proxy_async_smem();
 }
 
-// One tile of one convert thread; false = a wait gave up.
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
-                                             int lane, int quad, int hf) {
-  const bool tr = (threadIdx.x == 128);  // first convert thread
-  const int r = quad * 32 + lane;  // token row of the tile = tensor-memory lane
+// Phase A of one tile for one convert thread: dequantise this thread's share of the token row into tensor memory.
+// FULL = every row of the tile is a live token (no masking). Returns false if a wait gave up.
+// The publish of a chunk is deferred until the next chunk's values have been computed, so the latency of the
+// tensor-memory store hides behind arithmetic.
+template <int N, int RAW_SLOTS, bool FULL>
+__device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t,
+                                               uint32_t it, int lane, int quad, int hf) {
+  const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
+  const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
   const uint32_t hidx = 2 * it + half;
@@ -223,30 +234,15 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
   bool ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
   if (!__all_sync(~0u, ok)) return false;
   if (tr) MLA_TRACE_AT(P, 0, it);
-  const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
-
-  // ---- this thread's share of the token row, to registers; then the raw slot can be refilled
+  const bool valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
   const uint8_t* raw = s.raw[slot];
-  uint4 nope[4][2];
-  uint32_t sfw[4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const int p = 2 * g + hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row
-    const uint8_t* base = raw + (p >> 2) * kRawCkvHi + rr * 128;
-    const int c0 = 2 * (p & 3);
-    nope[g][0] = *reinterpret_cast<const uint4*>(base + (((c0) ^ (rr & 7)) << 4));
-    nope[g][1] = *reinterpret_cast<const uint4*>(base + (((c0 + 1) ^ (rr & 7)) << 4));
-    sfw[g] = *reinterpret_cast<const uint32_t*>(raw + kRawSf + rr * 32 + 4 * p);
-  }
-  const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
-  const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
-  __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
-  if (tr) MLA_TRACE_AT(P, 1, it);
-
   const uint32_t prev = (it - 1) & 1;  // parity of the previous tile's phase on the per-tile barriers
-  // ---- rope chunk first: it needs no room in the V tile, so it overlaps the previous tile's PV
+  const uint32_t swz = uint32_t(rr & 7) << 4;
+
+  // ---- rope chunk: 32 channels of this thread's half
   {
+    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
+    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
     ok = it == 0 || ptx::mbar_wait(&s.k_free[4], prev, &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
@@ -258,26 +254,26 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
       h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
     }
     ptx::tmem_st16(tm_lane + Cols<N>::KROPE + 16 * hf, h);
-    ptx::tmem_wait_st();
-    ptx::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[4]);
-    if (tr) MLA_TRACE_AT(P, 2, it);
   }
-  // ---- latent panels
+  if (tr) MLA_TRACE_AT(P, 2, it);
+  // ---- latent panels; chunk g publishes chunk g - 1 (rope = 4 for g = 0)
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const int p = 2 * g + hf;
-    ok = it == 0 || (ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag) && ptx::mbar_wait(&s.v_free[g], prev, &s.abort_flag));
-    if (!__all_sync(~0u, ok)) return false;
-    if (tr) MLA_TRACE_AT(P, 3 + 2 * g, it);
-    ptx::tc_fence_after_sync();
+    const int p = 2 * g + hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row
+    const uint8_t* base = raw + (p >> 2) * kRawCkvHi + rr * 128;
+    const uint32_t c0 = uint32_t(2 * (p & 3)) << 4;
+    const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
+    const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
+    const uint32_t sfw = *reinterpret_cast<const uint32_t*>(raw + kRawSf + rr * 32 + 4 * p);
+    if (g == 3) {  // last read of the raw slot by this thread
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+    }
     // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
-    const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw[g] >> 16));
+    const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
     const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
                             __byte_perm(s23, s23, 0x3232)};
-    const uint32_t wds[8] = {nope[g][0].x, nope[g][0].y, nope[g][0].z, nope[g][0].w,
-                             nope[g][1].x, nope[g][1].y, nope[g][1].z, nope[g][1].w};
+    const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
     uint32_t h[32];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
@@ -286,17 +282,56 @@ __device__ __forceinline__ bool convert_tile(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
       for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
     }
+    // publish the previous chunk (its store has been in flight during the arithmetic above)
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+    // these columns are free once the previous tile's QK^T chunk has read them
+    ok = it == 0 || ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag);
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tc_fence_after_sync();
     ptx::tmem_st32(tm_lane + Cols<N>::K + 32 * p, h);
+    if (tr) MLA_TRACE_AT(P, 3 + g, it);
+  }
+  ptx::tmem_wait_st();
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
+  if (tr) MLA_TRACE_AT(P, 7, it);
+  return true;
+}
+
+// Phase B: copy this thread's FP16 row from tensor memory into the V tile, panel by panel, as PV of the previous
+// tile releases the panels.
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ bool convert_tile_b(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, uint32_t it, int lane, int quad,
+                                               int hf) {
+  const bool tr = (threadIdx.x == 128);
+  const int r = quad * 32 + lane;
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
+  const uint32_t prev = (it - 1) & 1;
+  const uint32_t swz = uint32_t(r & 7) << 4;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int p = 2 * g + hf;
+    uint32_t h[32];
+    ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * p, h);
+    const bool ok = it == 0 || ptx::mbar_wait(&s.v_free[g], prev, &s.abort_flag);
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tmem_wait_ld();
+    if (tr && g == 0) MLA_TRACE_AT(P, 25, it);
     uint8_t* vrow = s.v16[p] + r * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c)
-      *reinterpret_cast<uint4*>(vrow + ((c ^ (r & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
-    ptx::tmem_wait_st();
+      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+    if (tr && g == 0) MLA_TRACE_AT(P, 26, it);
     ptx::fence_proxy_async_smem();
+    if (tr && g == 0) MLA_TRACE_AT(P, 27, it);
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[g]);
-    if (tr) MLA_TRACE_AT(P, 4 + 2 * g, it);
+    if (lane == 0) ptx::mbar_arrive(&s.v_full[g]);
+    if (tr) MLA_TRACE_AT(P, 8 + g, it);
   }
   return true;
 }
@@ -316,10 +351,13 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
     const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[3], (it - 1) & 1, &s.abort_flag));
     if (ptx::bar_red_or(2, 256, !ok)) return;
-    load_query<N, RAW_SLOTS>(s, P, seg, cw * 32 + lane, seg_count & 1);
+    load_query<N, RAW_SLOTS>(s, P, seg, cw * 32 + lane, seg_count & 3);
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
-      if (!convert_tile<N, RAW_SLOTS>(s, P, seg, t, it, lane, quad, hf)) {
+      const bool full = seg.tok0 + (t + 1) * TILE <= seg.tok_end;
+      const bool ok_a = full ? convert_tile_a<N, RAW_SLOTS, true>(s, P, seg, t, it, lane, quad, hf)
+                             : convert_tile_a<N, RAW_SLOTS, false>(s, P, seg, t, it, lane, quad, hf);
+      if (!ok_a || !convert_tile_b<N, RAW_SLOTS>(s, P, it, lane, quad, hf)) {
         dead = true;
         break;
       }
@@ -328,56 +366,82 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// role: MMA issue (one thread)
+// roles: MMA issue (one warp for QK^T, one for PV). The whole warp runs the loop so that every operand is
+// warp-uniform (descriptors then live in uniform registers and an MMA costs a couple of instructions); one elected
+// lane issues. A tcgen05.commit tracks only the MMAs of the thread that executes it, so each role's barriers speak
+// for its own MMAs.
 // ---------------------------------------------------------------------------------------------------------------
 template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void mma_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+__device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+  const bool leader = ptx::elect_one();
   const uint32_t tm = s.tmem_base;
-  const uint32_t idesc_qk = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, false, false);
-  const uint32_t idesc_pv = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
+  const uint32_t idesc = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, false, false);
   const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q[0]), 16, 1024);
-  const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[0]), 16, 1024);
+  for (int si = 0; si < n_segs; ++si) {
+    const int ntiles = s.segs[si].ntiles;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t par = it & 1, buf = it & 1;
+      // softmax of tile it - 2 must have read this S^T buffer
+      if (!__all_sync(~0u, it < 2 || ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag))) return;
+      // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag))) return;
+      if (leader) MLA_TRACE_AT(P, 12, it);
+      ptx::tc_fence_after_sync();
+      if (leader) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          ptx::mma_f16_ts(tm + Cols<N>::sp(buf), tm + Cols<N>::KROPE + 8 * ks, q_desc + ((8 * N * 128 + ks * 32) >> 4), idesc, ks > 0);
+        ptx::mma_commit(&s.k_free[4]);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag))) return;
+        if (leader) MLA_TRACE_AT(P, 13 + g, it);
+        ptx::tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int p = 2 * g + (j >> 2), ks = j & 3;
+            ptx::mma_f16_ts(tm + Cols<N>::sn(buf), tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc,
+                            (g | j) != 0);
+          }
+          ptx::mma_commit(&s.k_free[g]);
+          if (g == 3) ptx::mma_commit(&s.s_full[buf]);
+        }
+      }
+      if (leader) MLA_TRACE_AT(P, 17, it);
+    }
+  }
+}
+
+template <int N, int RAW_SLOTS>
+__device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+  const bool leader = ptx::elect_one();
+  const uint32_t tm = s.tmem_base;
+  const uint32_t idesc = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
   const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), kVPanelBytes, 1024);  // MN-major: LBO = next 64 channels
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
-      const uint32_t par = it & 1;
-      // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
-      if (!ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag)) return;
-      MLA_TRACE_AT(P, 12, it);
-      ptx::tc_fence_after_sync();
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        ptx::mma_f16_ts(tm + Cols<N>::SP, tm + Cols<N>::KROPE + 8 * ks, q_desc + ((8 * N * 128 + ks * 32) >> 4), idesc_qk, ks > 0);
-      ptx::mma_commit(&s.k_free[4]);
-#pragma unroll 1
-      for (int g = 0; g < 4; ++g) {
-        if (!ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag)) return;
-        MLA_TRACE_AT(P, 13 + g, it);
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int p = 2 * g + (j >> 2), ks = j & 3;
-          ptx::mma_f16_ts(tm + Cols<N>::SN, tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc_qk,
-                          (g | j) != 0);
-        }
-        ptx::mma_commit(&s.k_free[g]);
-      }
-      ptx::mma_commit(&s.s_full);
-      MLA_TRACE_AT(P, 17, it);
+      const uint32_t par = it & 1, buf = it & 1;
+      const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][0]), 16, 1024);
       // ---- O^T += V^T . P^T
-      if (!ptx::mbar_wait(&s.p_full, par, &s.abort_flag)) return;
-      MLA_TRACE_AT(P, 18, it);
-      ptx::tc_fence_after_sync();
-#pragma unroll 1
-      for (int mb = 0; mb < 4; ++mb) {
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
+      if (leader) MLA_TRACE_AT(P, 18, it);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((2 * mb * kVPanelBytes + ks * 2048) >> 4),
-                          p_desc + (((ks >> 2) * N * 128 + (ks & 3) * 32) >> 4), idesc_pv, (t | ks) != 0);
-        ptx::mma_commit(&s.v_free[mb]);
+      for (int mb = 0; mb < 4; ++mb) {
+        if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full[mb], par, &s.abort_flag))) return;
+        ptx::tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((2 * mb * kVPanelBytes + ks * 2048) >> 4),
+                            p_desc + (((ks >> 2) * N * 128 + (ks & 3) * 32) >> 4), idesc, (t | ks) != 0);
+          ptx::mma_commit(&s.v_free[mb]);
+          if (mb == 3) ptx::mma_commit(&s.p_free[buf]);
+        }
       }
-      MLA_TRACE_AT(P, 19, it);
+      if (leader) MLA_TRACE_AT(P, 19, it);
     }
   }
 }
@@ -392,17 +456,22 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
   const int r = threadIdx.x;  // 0..127
   const uint32_t tm_lane = s.tmem_base + (uint32_t(warp * 32) << 16);
   constexpr float kGrow = 8.f;  // rescale only when a score exceeds the running max by 2^8 (P stays <= 256)
+  const float ratio = P.kpe_scale / P.ckv_scale;
+  // P^T[head h][token r]: panel r / 64, row h (128 B), 16-byte chunk (r % 64) / 8 swizzled by h % 8
+  const uint32_t p_off = uint32_t(r >> 6) * (N * 128) + (r & 7) * 2;
+  const uint32_t p_chunk = uint32_t((r & 63) >> 3) << 4;
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
-    const int par_q = seg_count & 1;
+    const int par_q = seg_count & 3;
     ++seg_count;
     float m[N], lsum[N];
 #pragma unroll
     for (int h = 0; h < N; ++h) m[h] = -INFINITY, lsum[h] = 0.f;
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
-      bool ok = ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag);
+      const uint32_t buf = it & 1;
+      bool ok = ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag);
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       float x[N];
@@ -411,12 +480,12 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
         for (int c0 = 0; c0 < N; c0 += 16) {
           uint32_t sn[16], sp[16];
-          ptx::tmem_ld16(tm_lane + Cols<N>::SN + c0, sn);
-          ptx::tmem_ld16(tm_lane + Cols<N>::SP + c0, sp);
+          ptx::tmem_ld16(tm_lane + Cols<N>::sn(buf) + c0, sn);
+          ptx::tmem_ld16(tm_lane + Cols<N>::sp(buf) + c0, sp);
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = __uint_as_float(sn[j]) * s.qa[par_q][c0 + j] + __uint_as_float(sp[j]) * s.qb[par_q][c0 + j];
+            const float v = fmaf(ratio, __uint_as_float(sp[j]), __uint_as_float(sn[j])) * s.qa[par_q][c0 + j];
             x[c0 + j] = valid ? v : -INFINITY;
           }
         }
@@ -424,6 +493,9 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
         for (int h = 0; h < N; ++h) x[h] = -INFINITY;
       }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&s.s_free[buf]);  // QK^T of tile it + 2 may overwrite this S^T buffer
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       bool need = !ok;
 #pragma unroll
       for (int h = 0; h < N; ++h) need |= x[h] > m[h] + kGrow;
@@ -454,9 +526,12 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
           lsum[h] *= corr[h];
           m[h] = mn;
         }
-        // O^T *= corr per head (column). s_full of this tile was committed after the previous tile's PV, so O^T is
-        // quiescent here; the next PV is not issued before this thread arrives on p_full.
+        // O^T *= corr per head (column): after the previous tile's PV has finished; this tile's PV is not issued
+        // before this thread arrives on p_full.
         if (t > 0 && any_scale) {
+          const bool okv = ptx::mbar_wait(&s.p_free[buf ^ 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of tile it - 1
+          if (ptx::bar_red_or(1, 128, !okv)) return;
+          ptx::tc_fence_after_sync();
 #pragma unroll 1
           for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll
@@ -473,23 +548,28 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
         }
       }
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
+      // PV of tile it - 2 must have read this P^T buffer
+      // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
+      if (it >= 2) ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 28, it);
       // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
+      uint8_t* const p_base = s.p[buf][0] + p_off;
 #pragma unroll
       for (int h = 0; h < N; ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
-        const __half ph = __float2half_rn(pv);
-        const uint32_t off = h * 128 + ((((r & 63) >> 3) ^ (h & 7)) << 4) + (r & 7) * 2;
-        *reinterpret_cast<__half*>(s.p[r >> 6] + off) = ph;
+        *reinterpret_cast<__half*>(p_base + h * 128 + (p_chunk ^ (uint32_t(h & 7) << 4))) = __float2half_rn(pv);
       }
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
       ptx::fence_proxy_async_smem();
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&s.p_full);
+      ptx::mbar_arrive(&s.p_full[buf]);
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
-    bool ok = ptx::mbar_wait(&s.v_free[3], (it - 1) & 1, &s.abort_flag);
+    bool ok = ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of the last tile
     if (ptx::bar_red_or(1, 128, !ok)) return;
     ptx::tc_fence_after_sync();
 #pragma unroll
@@ -545,14 +625,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   extern __shared__ uint8_t smem_raw[];
   using Smem = DecodeSmem<N, RAW_SLOTS>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8), ptx::mbar_init(&s.k_free[i], 1);
-    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_free[i], 1);
-    ptx::mbar_init(&s.s_full, 1);
-    ptx::mbar_init(&s.p_full, 128);
+    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_full[i], 8), ptx::mbar_init(&s.v_free[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 128);
+      ptx::mbar_init(&s.p_full[i], 128), ptx::mbar_init(&s.p_free[i], 1);
+    }
     s.abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&ckv_map);
@@ -577,8 +659,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     __syncthreads();
     if (warp < 4) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
     else if (warp < 12) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    else if (warp == 12) { if (lane == 0) mma_role<N, RAW_SLOTS>(s, P, n_segs, it); }
+    else if (warp == 12) qk_role<N, RAW_SLOTS>(s, P, n_segs, it);
     else if (warp == 13) producer_role<N, RAW_SLOTS>(s, P, &ckv_map, n_segs, hcount);
+    else if (warp == 14) pv_role<N, RAW_SLOTS>(s, P, n_segs, it);
     __syncthreads();
     if (s.abort_flag) break;
   }
