@@ -35,6 +35,7 @@ WORKLOADS = {
     "c2_h16_b64_64k": (64, 16, 65536, 64, "bf16"),   # BASELINE config 2, the shape the metric is quoted on
     "c1_h16_b32_8k": (32, 16, 8192, 64, "bf16"),     # BASELINE config 1
     "h16_b64_16k": (64, 16, 16384, 64, "bf16"),
+    "h16_b8_64k": (8, 16, 65536, 64, "bf16"),        # small case for ncu captures (185 MB of KV, still larger than L2)
     "h128_b64_16k": (64, 128, 16384, 64, "bf16"),
 }
 TOKEN_BYTES = 352

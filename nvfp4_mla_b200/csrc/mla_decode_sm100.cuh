@@ -86,8 +86,8 @@ struct DecodeSmem {
   unsigned int qamax[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
-  uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {2g, 2g+1}, chunk 4 = rope
-  uint64_t v_full[4], v_free[4];                    // V panels {2mb, 2mb+1}: written / PV finished reading them
+  uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {g, g+4}, chunk 4 = rope
+  uint64_t v_full;                                  // the V tile is written (one phase per tile)
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -239,6 +239,8 @@ __device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, cons
   const uint32_t prev = (it - 1) & 1;  // parity of the previous tile's phase on the per-tile barriers
   const uint32_t swz = uint32_t(rr & 7) << 4;
 
+  // the 16 block scales of this thread's half row
+  const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);
   // ---- rope chunk: 32 channels of this thread's half
   {
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
@@ -259,12 +261,12 @@ __device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, cons
   // ---- latent panels; chunk g publishes chunk g - 1 (rope = 4 for g = 0)
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const int p = 2 * g + hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row
-    const uint8_t* base = raw + (p >> 2) * kRawCkvHi + rr * 128;
-    const uint32_t c0 = uint32_t(2 * (p & 3)) << 4;
+    const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
+    const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
+    const uint32_t c0 = uint32_t(2 * g) << 4;
     const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
     const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
-    const uint32_t sfw = *reinterpret_cast<const uint32_t*>(raw + kRawSf + rr * 32 + 4 * p);
+    const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
     if (g == 3) {  // last read of the raw slot by this thread
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
@@ -302,37 +304,38 @@ __device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, cons
   return true;
 }
 
-// Phase B: copy this thread's FP16 row from tensor memory into the V tile, panel by panel, as PV of the previous
-// tile releases the panels.
+// Phase B: once PV of the previous tile has finished with the V tile, copy this thread's FP16 row from tensor memory
+// into it (four 64-channel panels, the load of the next panel in flight while the current one is stored), then
+// publish the whole tile with a single proxy fence.
 template <int N, int RAW_SLOTS>
 __device__ __forceinline__ bool convert_tile_b(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, uint32_t it, int lane, int quad,
                                                int hf) {
   const bool tr = (threadIdx.x == 128);
   const int r = quad * 32 + lane;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
-  const uint32_t prev = (it - 1) & 1;
   const uint32_t swz = uint32_t(r & 7) << 4;
+  uint32_t h[2][32];
+  ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * (4 * hf), h[0]);
+  const bool ok = it == 0 || ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of tile it - 1
+  if (!__all_sync(~0u, ok)) return false;
+  if (tr) MLA_TRACE_AT(P, 8, it);
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const int p = 2 * g + hf;
-    uint32_t h[32];
-    ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * p, h);
-    const bool ok = it == 0 || ptx::mbar_wait(&s.v_free[g], prev, &s.abort_flag);
-    if (!__all_sync(~0u, ok)) return false;
+    const int p = g + 4 * hf;
     ptx::tmem_wait_ld();
-    if (tr && g == 0) MLA_TRACE_AT(P, 25, it);
+    if (g < 3) ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * (p + 1), h[(g + 1) & 1]);
     uint8_t* vrow = s.v16[p] + r * 128;
+    const uint32_t* v = h[g & 1];
 #pragma unroll
     for (int c = 0; c < 8; ++c)
-      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
-    if (tr && g == 0) MLA_TRACE_AT(P, 26, it);
-    ptx::fence_proxy_async_smem();
-    if (tr && g == 0) MLA_TRACE_AT(P, 27, it);
-    ptx::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.v_full[g]);
-    if (tr) MLA_TRACE_AT(P, 8 + g, it);
+      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
   }
+  if (tr) MLA_TRACE_AT(P, 9, it);
+  ptx::fence_proxy_async_smem();
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.v_full);
+  if (tr) MLA_TRACE_AT(P, 10, it);
   return true;
 }
 
@@ -393,17 +396,21 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
           ptx::mma_f16_ts(tm + Cols<N>::sp(buf), tm + Cols<N>::KROPE + 8 * ks, q_desc + ((8 * N * 128 + ks * 32) >> 4), idesc, ks > 0);
         ptx::mma_commit(&s.k_free[4]);
       }
-#pragma unroll
+      // rolled loops (4 MMAs per trip): fully unrolled, the 36 operand sets would occupy ~100 registers of a warp
+      // group that has given most of its registers away
+#pragma unroll 1
       for (int g = 0; g < 4; ++g) {
         if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag))) return;
         if (leader) MLA_TRACE_AT(P, 13 + g, it);
         ptx::tc_fence_after_sync();
         if (leader) {
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            const int p = g + 4 * half;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int p = 2 * g + (j >> 2), ks = j & 3;
-            ptx::mma_f16_ts(tm + Cols<N>::sn(buf), tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc,
-                            (g | j) != 0);
+            for (int ks = 0; ks < 4; ++ks)
+              ptx::mma_f16_ts(tm + Cols<N>::sn(buf), tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc,
+                              (g | half | ks) != 0);
           }
           ptx::mma_commit(&s.k_free[g]);
           if (g == 3) ptx::mma_commit(&s.s_full[buf]);
@@ -419,7 +426,8 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
   const bool leader = ptx::elect_one();
   const uint32_t tm = s.tmem_base;
   const uint32_t idesc = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
-  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), kVPanelBytes, 1024);  // MN-major: LBO = next 64 channels
+  // MN-major A: block mb = panels {mb, mb + 4} (channels [64mb, +64) and [256 + 64mb, +64)), so LBO = 4 panels
+  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), 4 * kVPanelBytes, 1024);
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
@@ -427,19 +435,21 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][0]), 16, 1024);
       // ---- O^T += V^T . P^T
       if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full, par, &s.abort_flag))) return;
       if (leader) MLA_TRACE_AT(P, 18, it);
+      ptx::tc_fence_after_sync();
+      if (leader) {
+#pragma unroll 1
+        for (int mb = 0; mb < 4; ++mb) {
+#pragma unroll 1
+          for (int kh = 0; kh < 2; ++kh) {  // 64 tokens = one P^T panel per trip
 #pragma unroll
-      for (int mb = 0; mb < 4; ++mb) {
-        if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full[mb], par, &s.abort_flag))) return;
-        ptx::tc_fence_after_sync();
-        if (leader) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((2 * mb * kVPanelBytes + ks * 2048) >> 4),
-                            p_desc + (((ks >> 2) * N * 128 + (ks & 3) * 32) >> 4), idesc, (t | ks) != 0);
-          ptx::mma_commit(&s.v_free[mb]);
-          if (mb == 3) ptx::mma_commit(&s.p_free[buf]);
+            for (int ks = 0; ks < 4; ++ks)
+              ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((mb * kVPanelBytes + (4 * kh + ks) * 2048) >> 4),
+                              p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
+          }
         }
+        ptx::mma_commit(&s.p_free[buf]);
       }
       if (leader) MLA_TRACE_AT(P, 19, it);
     }
@@ -601,7 +611,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
         ptx::tmem_ld16(tm_lane + Cols<N>::O + mb * N + c0, o);
         ptx::tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) obase[(long long)(c0 + j) * CKV + mb * 128 + r] = __uint_as_float(o[j]) * inv[c0 + j];
+        for (int j = 0; j < 16; ++j)  // lane r of block mb is channel 64mb + r (r < 64) or 256 + 64mb + r - 64
+          obase[(long long)(c0 + j) * CKV + 64 * mb + (r & 63) + 256 * (r >> 6)] = __uint_as_float(o[j]) * inv[c0 + j];
       }
     }
     if (r < N) {
@@ -613,6 +624,34 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     }
     ptx::tc_fence_before_sync();
     ptx::bar_sync(1, 128);  // s.red is reused by the next segment
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The CTA's segments are staged through shared memory in batches; every thread takes part in the two CTA-wide
+// barriers around a batch, whatever its role.
+// ---------------------------------------------------------------------------------------------------------------
+enum Role { kRoleSoftmax, kRoleConvert, kRoleQk, kRoleProducer, kRolePv, kRoleIdle };
+
+template <int N, int RAW_SLOTS, int ROLE>
+__device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map) {
+  const int2 range = P.cta_range[blockIdx.x];
+  uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
+  for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
+    const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
+    if (ROLE == kRoleSoftmax && int(threadIdx.x) < n_segs) {
+      Seg g = P.segs[(long long)blockIdx.x + w0 + threadIdx.x];
+      if (g.cta != int(blockIdx.x) || g.w != w0 + int(threadIdx.x)) g.ntiles = 0;  // empty item or foreign slot
+      s.segs[threadIdx.x] = g;
+    }
+    __syncthreads();
+    if (ROLE == kRoleSoftmax) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
+    if (ROLE == kRoleConvert) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
+    if (ROLE == kRoleQk) qk_role<N, RAW_SLOTS>(s, P, n_segs, it);
+    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS>(s, P, ckv_map, n_segs, hcount);
+    if (ROLE == kRolePv) pv_role<N, RAW_SLOTS>(s, P, n_segs, it);
+    __syncthreads();
+    if (s.abort_flag) break;
   }
 }
 
@@ -630,7 +669,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8), ptx::mbar_init(&s.k_free[i], 1);
-    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_full[i], 8), ptx::mbar_init(&s.v_free[i], 1);
+    ptx::mbar_init(&s.v_full, 8);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 128);
       ptx::mbar_init(&s.p_full[i], 128), ptx::mbar_init(&s.p_free[i], 1);
@@ -647,23 +686,21 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   __syncthreads();
   ptx::tc_fence_after_sync();
 
-  const int2 range = P.cta_range[blockIdx.x];
-  uint32_t it = 0, seg_count = 0, hcount = 0;  // each role advances its own copies identically
-  for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
-    const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
-    if (threadIdx.x < n_segs) {
-      Seg g = P.segs[(long long)blockIdx.x + w0 + threadIdx.x];
-      if (g.cta != int(blockIdx.x) || g.w != w0 + int(threadIdx.x)) g.ntiles = 0;  // empty item or foreign slot
-      s.segs[threadIdx.x] = g;
-    }
-    __syncthreads();
-    if (warp < 4) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    else if (warp < 12) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    else if (warp == 12) qk_role<N, RAW_SLOTS>(s, P, n_segs, it);
-    else if (warp == 13) producer_role<N, RAW_SLOTS>(s, P, &ckv_map, n_segs, hcount);
-    else if (warp == 14) pv_role<N, RAW_SLOTS>(s, P, n_segs, it);
-    __syncthreads();
-    if (s.abort_flag) break;
+  // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
+  // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
+  // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
+  if (warp < 4) {
+    ptx::reg_alloc<160>();
+    run_role<N, RAW_SLOTS, kRoleSoftmax>(s, P, &ckv_map);
+  } else if (warp < 12) {
+    ptx::reg_alloc<152>();
+    run_role<N, RAW_SLOTS, kRoleConvert>(s, P, &ckv_map);
+  } else {
+    ptx::reg_dealloc<48>();
+    if (warp == 12) run_role<N, RAW_SLOTS, kRoleQk>(s, P, &ckv_map);
+    else if (warp == 13) run_role<N, RAW_SLOTS, kRoleProducer>(s, P, &ckv_map);
+    else if (warp == 14) run_role<N, RAW_SLOTS, kRolePv>(s, P, &ckv_map);
+    else run_role<N, RAW_SLOTS, kRoleIdle>(s, P, &ckv_map);
   }
 
   ptx::tc_fence_before_sync();

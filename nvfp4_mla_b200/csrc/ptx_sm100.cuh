@@ -18,6 +18,11 @@ __device__ __forceinline__ bool elect_one() {
   return p != 0;
 }
 
+// Register budget of the calling warp group (all four warps of the group must execute it). The kernel must be
+// compiled with a fixed register count at entry (__launch_bounds__ with one CTA per SM) for these to take effect.
+template <int REGS> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
+template <int REGS> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
+
 // ---------------------------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------------------------
