@@ -88,6 +88,7 @@ struct DecodeSmem {
   uint64_t raw_empty[RAW_SLOTS];
   uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {g, g+4}, chunk 4 = rope
   uint64_t v_full;                                  // the V tile is written (one phase per tile)
+  uint64_t v_free[4];                               // PV has read block mb = panels {mb, mb + 4} of the V tile
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -218,31 +219,35 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const De
   ptx::fence_proxy_async_smem();
 }
 
-// Phase A of one tile for one convert thread: dequantise this thread's share of the token row into tensor memory.
-// FULL = every row of the tile is a live token (no masking). Returns false if a wait gave up.
-// The publish of a chunk is deferred until the next chunk's values have been computed, so the latency of the
-// tensor-memory store hides behind arithmetic.
-template <int N, int RAW_SLOTS, bool FULL>
-__device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t,
-                                               uint32_t it, int lane, int quad, int hf) {
+// One pipeline step of a convert thread: phase A of tile `it` (dequantise the thread's share of the token row into
+// tensor memory, chunk by chunk, so that QK^T chases the conversion) interleaved with phase B of tile `it - 1` (copy
+// that tile's FP16 values from tensor memory into the V tile as PV of tile `it - 2` releases it). The two phases use
+// different units (ALU + tensor-memory stores versus tensor-memory loads + shared-memory stores), so one instruction
+// stream keeps both busy. Per 64-channel panel p of this thread:
+//     load B's panel from tensor memory -> compute A's panel -> publish A's previous chunk -> (B's load has landed)
+//     -> store A's panel over it -> store B's panel to the V tile.
+// FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
+template <int N, int RAW_SLOTS, bool FULL, bool has_a, bool has_b>
+__device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
+                                             int lane, int quad, int hf) {
   const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
   const uint32_t hidx = 2 * it + half;
   const int slot = hidx % RAW_SLOTS;
-  bool ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
-  if (!__all_sync(~0u, ok)) return false;
-  if (tr) MLA_TRACE_AT(P, 0, it);
-  const bool valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
   const uint8_t* raw = s.raw[slot];
-  const uint32_t prev = (it - 1) & 1;  // parity of the previous tile's phase on the per-tile barriers
-  const uint32_t swz = uint32_t(rr & 7) << 4;
-
-  // the 16 block scales of this thread's half row
-  const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);
-  // ---- rope chunk: 32 channels of this thread's half
-  {
+  const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
+  const uint32_t swz = uint32_t(rr & 7) << 4, swz_v = uint32_t(r & 7) << 4;
+  bool ok, valid = true;
+  uint4 sf16 = make_uint4(0, 0, 0, 0);
+  if (has_a) {
+    ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
+    if (!__all_sync(~0u, ok)) return false;
+    if (tr) MLA_TRACE_AT(P, 0, it);
+    valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
+    sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);  // the 16 block scales of this half row
+    // ---- rope chunk: 32 channels of this thread's half
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
     ok = it == 0 || ptx::mbar_wait(&s.k_free[4], prev, &s.abort_flag);
@@ -256,86 +261,74 @@ __device__ __forceinline__ bool convert_tile_a(DecodeSmem<N, RAW_SLOTS>& s, cons
       h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
     }
     ptx::tmem_st16(tm_lane + Cols<N>::KROPE + 16 * hf, h);
+    if (tr) MLA_TRACE_AT(P, 2, it);
   }
-  if (tr) MLA_TRACE_AT(P, 2, it);
-  // ---- latent panels; chunk g publishes chunk g - 1 (rope = 4 for g = 0)
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
-    const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
-    const uint32_t c0 = uint32_t(2 * g) << 4;
-    const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
-    const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
-    const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
-    if (g == 3) {  // last read of the raw slot by this thread
+    uint32_t hb[32], h[32];
+    if (has_b) ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * p, hb);  // tile it - 1, on its way to the V tile
+    if (has_a) {
+      const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
+      const uint32_t c0 = uint32_t(2 * g) << 4;
+      const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
+      const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
+      const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
+      if (g == 3) {  // last read of the raw slot by this thread
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+      }
+      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
+      const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
+      const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
+                              __byte_perm(s23, s23, 0x3232)};
+      const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
+        uint32_t e[4];
+        ptx::e2m1x8_to_f16x8(wds[j], e);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+      }
+      // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+      if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
     }
-    // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
-    const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
-    const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
-                            __byte_perm(s23, s23, 0x3232)};
-    const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
-    uint32_t h[32];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
-      uint32_t e[4];
-      ptx::e2m1x8_to_f16x8(wds[j], e);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+    if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
+    if (has_a) {
+      // ... once the previous tile's QK^T chunk has read them
+      ok = it == 0 || ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag);
+      if (!__all_sync(~0u, ok)) return false;
+      ptx::tc_fence_after_sync();
+      ptx::tmem_st32(tm_lane + Cols<N>::K + 32 * p, h);
+      if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
-    // publish the previous chunk (its store has been in flight during the arithmetic above)
+    if (has_b) {
+      // PV of tile it - 2 must have finished with this block of the V tile
+      ok = it < 2 || ptx::mbar_wait(&s.v_free[g], it & 1, &s.abort_flag);
+      if (!__all_sync(~0u, ok)) return false;
+      uint8_t* vrow = s.v16[p] + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
+      if (tr) MLA_TRACE_AT(P, 8 + g, it);
+    }
+  }
+  if (has_a) {
     ptx::tmem_wait_st();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
-    // these columns are free once the previous tile's QK^T chunk has read them
-    ok = it == 0 || ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag);
-    if (!__all_sync(~0u, ok)) return false;
-    ptx::tc_fence_after_sync();
-    ptx::tmem_st32(tm_lane + Cols<N>::K + 32 * p, h);
-    if (tr) MLA_TRACE_AT(P, 3 + g, it);
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
+    if (tr) MLA_TRACE_AT(P, 7, it);
   }
-  ptx::tmem_wait_st();
-  ptx::tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
-  if (tr) MLA_TRACE_AT(P, 7, it);
-  return true;
-}
-
-// Phase B: once PV of the previous tile has finished with the V tile, copy this thread's FP16 row from tensor memory
-// into it (four 64-channel panels, the load of the next panel in flight while the current one is stored), then
-// publish the whole tile with a single proxy fence.
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ bool convert_tile_b(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, uint32_t it, int lane, int quad,
-                                               int hf) {
-  const bool tr = (threadIdx.x == 128);
-  const int r = quad * 32 + lane;
-  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
-  const uint32_t swz = uint32_t(r & 7) << 4;
-  uint32_t h[2][32];
-  ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * (4 * hf), h[0]);
-  const bool ok = it == 0 || ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of tile it - 1
-  if (!__all_sync(~0u, ok)) return false;
-  if (tr) MLA_TRACE_AT(P, 8, it);
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const int p = g + 4 * hf;
-    ptx::tmem_wait_ld();
-    if (g < 3) ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * (p + 1), h[(g + 1) & 1]);
-    uint8_t* vrow = s.v16[p] + r * 128;
-    const uint32_t* v = h[g & 1];
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  if (has_b) {
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.v_full);  // phase of tile it - 1
   }
-  if (tr) MLA_TRACE_AT(P, 9, it);
-  ptx::fence_proxy_async_smem();
-  ptx::tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.v_full);
-  if (tr) MLA_TRACE_AT(P, 10, it);
   return true;
 }
 
@@ -347,9 +340,10 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
                                              uint32_t& seg_count) {
   const int lane = ptx::lane_id();
   const int cw = (threadIdx.x >> 5) - 4, quad = cw & 3, hf = cw >> 2;
-  bool dead = false;
+  bool dead = false, pending = false;  // pending: tile it - 1 still has to be copied into the V tile
+  Seg seg = s.segs[0];
   for (int si = 0; si < n_segs; ++si) {
-    const Seg seg = s.segs[si];
+    seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
     // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
     const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[3], (it - 1) & 1, &s.abort_flag));
@@ -358,14 +352,18 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const bool full = seg.tok0 + (t + 1) * TILE <= seg.tok_end;
-      const bool ok_a = full ? convert_tile_a<N, RAW_SLOTS, true>(s, P, seg, t, it, lane, quad, hf)
-                             : convert_tile_a<N, RAW_SLOTS, false>(s, P, seg, t, it, lane, quad, hf);
-      if (!ok_a || !convert_tile_b<N, RAW_SLOTS>(s, P, it, lane, quad, hf)) {
+      const bool ok_s = !pending ? convert_step<N, RAW_SLOTS, false, true, false>(s, P, seg, t, it, lane, quad, hf)
+                        : full   ? convert_step<N, RAW_SLOTS, true, true, true>(s, P, seg, t, it, lane, quad, hf)
+                                 : convert_step<N, RAW_SLOTS, false, true, true>(s, P, seg, t, it, lane, quad, hf);
+      pending = true;
+      if (!ok_s) {
         dead = true;
         break;
       }
     }
   }
+  // drain: the batch's last tile still has to reach the V tile
+  if (pending && !dead) convert_step<N, RAW_SLOTS, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -448,6 +446,7 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
               ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((mb * kVPanelBytes + (4 * kh + ks) * 2048) >> 4),
                               p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
           }
+          ptx::mma_commit(&s.v_free[mb]);
         }
         ptx::mma_commit(&s.p_free[buf]);
       }
@@ -670,6 +669,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8), ptx::mbar_init(&s.k_free[i], 1);
     ptx::mbar_init(&s.v_full, 8);
+    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_free[i], 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 128);
       ptx::mbar_init(&s.p_full[i], 128), ptx::mbar_init(&s.p_free[i], 1);
