@@ -69,6 +69,37 @@ NVFP4_MLA_API int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const u
                      float ckv_scale, float kpe_scale, int max_kv_len, int num_splits, int precision, void* out,
                      float* out_f32, float* lse, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* nvfp4_mla_decode for callers that have no way to hand over scratch memory. (No counterpart in the reference, whose
+ * launcher always allocates its partial buffers through torch.)
+ *
+ * Some hosts of this library cannot allocate device memory at the point where they decode: an inference server that
+ * reserved the whole GPU for its own pool at start-up and has nothing left for cudaMalloc to hand out, a plugin that is
+ * only given its input and output buffers, or code running where an allocation would stall the device for every other
+ * stream. For them the library carries its own scratch: a fixed 9 MiB array inside the library's device image
+ * (nvfp4_mla_decode_static_capacity() bytes, held by every GPU that loads the library until the process exits).
+ * Arguments and results are those of nvfp4_mla_decode, without `workspace` / `workspace_bytes`.
+ *
+ *   - Limit: the call fails, launching nothing, when nvfp4_mla_decode_workspace_bytes(batch, heads, num_splits) exceeds
+ *     the capacity. On a 148-SM B200 that allows batch * (heads / 16) * max(num_splits, 1) up to about 130, e.g.
+ *     batch 64 with 16 heads, or batch 16 with 128 heads.
+ *   - Nothing is allocated or freed here, by CUDA or by any library, on any call.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and does the one-time
+ *     kernel set-up; make that first call outside any stream capture.
+ *   - All calls on a device share the one array. Calls that can overlap on the GPU (different streams, or graphs
+ *     replayed concurrently) race on it and corrupt each other's results: serialise them, or give the concurrent
+ *     ones their own workspace through nvfp4_mla_decode.
+ *   - The array keeps what the previous call wrote. The one word that has to start from zero, the device-side status,
+ *     is cleared on `stream` at the start of every call; nvfp4_mla_decode_static_status(stream) synchronises `stream`
+ *     and returns the status of the calls made since (same codes as nvfp4_mla_workspace_status). */
+NVFP4_MLA_API int nvfp4_mla_decode_static(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache,
+                                          const uint8_t* ckv_sf_cache, const uint8_t* kpe_cache, int64_t num_pages,
+                                          int page_size, const int32_t* page_table, int64_t page_table_stride,
+                                          const int32_t* kv_lens, int batch, int heads, float sm_scale, float ckv_scale,
+                                          float kpe_scale, int max_kv_len, int num_splits, int precision, void* out,
+                                          float* out_f32, float* lse, void* stream);
+NVFP4_MLA_API int64_t nvfp4_mla_decode_static_capacity(void);
+NVFP4_MLA_API int nvfp4_mla_decode_static_status(void* stream);
+
 /* Synchronises `stream` and returns the status word of a decode workspace: 0 = every kernel ran to completion,
  * 1 = a bounded wait inside the decode kernel gave up (results invalid), 2 = batch * num_splits too large for the
  * schedule kernel; negative = CUDA error (see nvfp4_mla_last_error). No counterpart in the reference, whose kernels

@@ -17,6 +17,10 @@ SIGNATURES = {
     "nvfp4_mla_decode_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "nvfp4_mla_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i32, _i32, _f32, _f32, _f32,
                                 _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "nvfp4_mla_decode_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i32, _i32, _f32, _f32, _f32,
+                                       _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "nvfp4_mla_decode_static_capacity": (_i64, []),
+    "nvfp4_mla_decode_static_status": (_i32, [_vp]),
     "nvfp4_mla_workspace_status": (_i32, [_vp, _vp]),
     "nvfp4_mla_profile_begin": (_i32, [_i32]),
     "nvfp4_mla_profile_end": (_i32, [_vp, _i32]),

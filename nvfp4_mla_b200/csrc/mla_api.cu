@@ -207,6 +207,62 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   return 0;
 }
 
+// ---- decode without caller-provided scratch -----------------------------------------------------------------------
+// Scratch for nvfp4_mla_decode_static: lives in the library's own device image, so no allocation ever happens for it.
+// Every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(9) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device (set up on first use)
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per device.
+int static_scratch(void** out) {
+  int dev = 0;
+  MLA_CUDA(cudaGetDevice(&dev));
+  MLA_CHECK(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    MLA_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    MLA_CHECK(p != nullptr, "cudaGetSymbolAddress returned a null address for the static scratch");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+int64_t nvfp4_mla_decode_static_capacity(void) { return int64_t(kStaticScratchBytes); }
+
+int nvfp4_mla_decode_static(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
+                            const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
+                            int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale,
+                            float ckv_scale, float kpe_scale, int max_kv_len, int num_splits, int precision, void* out,
+                            float* out_f32, float* lse, void* stream) {
+  g_error[0] = 0;
+  const int64_t need = nvfp4_mla_decode_workspace_bytes(batch, heads, num_splits);
+  if (need < 0) return 1;  // message already set
+  MLA_CHECK(need <= int64_t(kStaticScratchBytes),
+            "problem too large for the built-in scratch: batch %d x heads %d x num_splits %d needs %lld bytes, the library holds "
+            "%lld; use nvfp4_mla_decode with a caller-provided workspace",
+            batch, heads, num_splits, (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (static_scratch(&scratch)) return 1;
+  // the status word must start each call at zero: the array keeps whatever the previous call left in it
+  MLA_CUDA(cudaMemsetAsync(scratch, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+  return nvfp4_mla_decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, num_pages, page_size, page_table, page_table_stride,
+                          kv_lens, batch, heads, sm_scale, ckv_scale, kpe_scale, max_kv_len, num_splits, precision, out, out_f32, lse,
+                          scratch, int64_t(kStaticScratchBytes), stream);
+}
+
+int nvfp4_mla_decode_static_status(void* stream) {
+  g_error[0] = 0;
+  void* scratch = nullptr;
+  if (static_scratch(&scratch)) return -1;
+  return nvfp4_mla_workspace_status(scratch, stream);
+}
+
 int nvfp4_mla_profile_begin(int capacity) {
   g_error[0] = 0;
   MLA_CHECK(capacity > 0 && capacity <= (1 << 20), "capacity must be in [1, 2^20]");
