@@ -43,9 +43,16 @@ DeviceInfo g_devices[kMaxDevices];
 
 using DecodeKernel = void (*)(const CUtensorMap, const mla::DecodeParams);
 constexpr int kHeadsPerCta = 16;
-constexpr int kRawSlots = 3;
-DecodeKernel decode_kernel() { return mla::mla_decode_kernel<kHeadsPerCta, kRawSlots>; }
-constexpr size_t kDecodeSmem = mla::decode_smem_bytes<kHeadsPerCta, kRawSlots>();
+// staging slots of 64 tokens: the 16-bit mode's V tile leaves room for 3, the 8-bit mode's for 6
+constexpr int kRawSlots16 = 3, kRawSlots8 = 6;
+DecodeKernel decode_kernel(int precision) {
+  return precision == NVFP4_MLA_PRECISION_FP8 ? mla::mla_decode_kernel<kHeadsPerCta, kRawSlots8, true>
+                                              : mla::mla_decode_kernel<kHeadsPerCta, kRawSlots16, false>;
+}
+size_t decode_smem(int precision) {
+  return precision == NVFP4_MLA_PRECISION_FP8 ? mla::decode_smem_bytes<kHeadsPerCta, kRawSlots8, true>()
+                                              : mla::decode_smem_bytes<kHeadsPerCta, kRawSlots16, false>();
+}
 
 // Per-device one-time setup (SM count, opt-in shared memory). Must first run outside stream capture.
 int device_info(DeviceInfo** out) {
@@ -59,7 +66,8 @@ int device_info(DeviceInfo** out) {
     MLA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
     MLA_CHECK(major == 10, "nvfp4_mla_b200 needs an sm_100a GPU (B200), found compute capability %d.x", major);
     MLA_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
-    MLA_CUDA(cudaFuncSetAttribute(decode_kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSmem)));
+    for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8})
+      MLA_CUDA(cudaFuncSetAttribute(decode_kernel(prec), cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem(prec))));
     d.ready = true;
   }
   *out = &d;
@@ -152,7 +160,6 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   g_error[0] = 0;
   MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16 || precision == NVFP4_MLA_PRECISION_FP8,
             "precision must be 0 (bf16) or 1 (fp8), got %d", precision);
-  MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16, "precision fp8 is not built into this library yet");
   MLA_CHECK(page_size > 0 && (page_size & (page_size - 1)) == 0, "page_size must be a power of two, got %d", page_size);
   MLA_CHECK(num_pages > 0 && num_pages * page_size < (int64_t(1) << 31), "num_pages * page_size must be in [1, 2^31)");
   MLA_CHECK(ckv_scale > 0.f && kpe_scale > 0.f, "ckv_scale and kpe_scale must be positive");
@@ -197,7 +204,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  decode_kernel()<<<pb.n_cta, mla::kDecodeThreads, kDecodeSmem, st>>>(ckv_map, P);
+  decode_kernel(precision)<<<pb.n_cta, mla::kDecodeThreads, decode_smem(precision), st>>>(ckv_map, P);
   MLA_CUDA(cudaGetLastError());
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 

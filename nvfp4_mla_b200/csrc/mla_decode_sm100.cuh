@@ -74,21 +74,24 @@ struct DecodeParams {
 #endif
 };
 
-template <int N, int RAW_SLOTS>
+template <int N, int RAW_SLOTS, bool P8>
 struct DecodeSmem {
-  alignas(1024) uint8_t v16[8][kVPanelBytes];       // V tile: panel p = channels [64p, 64p+64), row = token, 128-B swizzle
-  alignas(1024) uint8_t q[9][N * 128];              // Q^T: panel p = channels [64p, +64) (panel 8 = rope), row = head
-  alignas(1024) uint8_t p[2][2][N * 128];           // P^T, double buffered: [buffer][panel of 64 tokens], row = head
+  // Operand tiles, all with the 128-byte swizzle, one 128-byte row per token (V) or head (Q^T, P^T).
+  //   16-bit mode: a row holds 64 elements. V: 8 panels of 64 channels; Q^T: 8 latent panels + rope; P^T: 2 panels of 64 tokens
+  //   8-bit mode : a row holds 128 elements. V: 4 panels of 128 channels; Q^T: 4 latent panels + rope (half a row); P^T: 1 panel
+  alignas(1024) uint8_t v16[P8 ? 4 : 8][kVPanelBytes];
+  alignas(1024) uint8_t q[P8 ? 5 : 9][N * 128];
+  alignas(1024) uint8_t p[2][P8 ? 1 : 2][N * 128];  // double buffered
   alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
   Seg segs[kSegBatch];
-  float qa[4][N];                                   // per-head score scale, ring indexed by segment count
+  float qa[4][N], qb[4][N];                         // per-head score scales (latent, rope), ring indexed by segment count
   float red[4][N];                                  // softmax group: per-warp partial reductions
-  unsigned int qamax[N];
+  unsigned int qamax[N], qamax_pe[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
   uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {g, g+4}, chunk 4 = rope
   uint64_t v_full;                                  // the V tile is written (one phase per tile)
-  uint64_t v_free[4];                               // PV has read block mb = panels {mb, mb + 4} of the V tile
+  uint64_t v_free[4];                               // PV has read block mb of the V tile
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -97,22 +100,22 @@ struct DecodeSmem {
   int abort_flag;
 };
 
-template <int N, int RAW_SLOTS>
-constexpr size_t decode_smem_bytes() { return sizeof(DecodeSmem<N, RAW_SLOTS>) + 1024; }
+template <int N, int RAW_SLOTS, bool P8>
+constexpr size_t decode_smem_bytes() { return sizeof(DecodeSmem<N, RAW_SLOTS, P8>) + 1024; }
 
-// tensor-memory columns
-template <int N> struct Cols {
-  static constexpr uint32_t K = 0, KROPE = 256, O = 288 + 4 * N;
-  __host__ __device__ static constexpr uint32_t sn(uint32_t buf) { return 288 + buf * 2 * N; }      // latent part of the scores
-  __host__ __device__ static constexpr uint32_t sp(uint32_t buf) { return 288 + buf * 2 * N + N; }  // rope part
+// tensor-memory columns. K: one token row per lane, PANEL columns per 64-channel panel (2 FP16 or 4 E4M3 per column).
+template <int N, bool P8> struct Cols {
+  static constexpr uint32_t PANEL = P8 ? 16 : 32, K = 0, KROPE = 8 * PANEL, S = 9 * PANEL, O = S + 4 * N;
+  __host__ __device__ static constexpr uint32_t sn(uint32_t buf) { return S + buf * 2 * N; }      // latent part of the scores
+  __host__ __device__ static constexpr uint32_t sp(uint32_t buf) { return S + buf * 2 * N + N; }  // rope part
   static_assert(O + 4 * N <= kTmemCols, "tensor memory overflow");
 };
 
 // ---------------------------------------------------------------------------------------------------------------
 // role: TMA producer (one warp; lane 0 issues, all lanes help with page ids)
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
                                               int n_segs, uint32_t& hcount) {
   const int lane = ptx::lane_id();
   const int ps = 1 << P.page_shift;
@@ -175,11 +178,13 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS>& s, const
 // ---------------------------------------------------------------------------------------------------------------
 // role: dequantise (8 warps). cw = warp - 4: quadrant = cw % 4 (tensor-memory lanes), hf = cw / 4 (panel parity).
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int ct, int par) {
-  // ct = 0..255. Pass 1: per-row amax (positive floats compare as unsigned ints). Pass 2: scale by 2^(14 - e) so the
-  // row's largest magnitude lies in [2^14, 2^15), convert to FP16, store swizzled; the score scale undoes it.
-  if (ct < N) s.qamax[ct] = 0;
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int ct, int par) {
+  // ct = 0..255. Pass 1: per-row amax (positive floats compare as unsigned ints), latent and rope parts separately.
+  // Pass 2, 16-bit mode: scale the row by 2^(14 - e) so its largest magnitude lies in [2^14, 2^15), convert to FP16
+  // (exact), store swizzled; the score scale undoes it. 8-bit mode: E4M3 of q * 448 / amax, each part with its own amax
+  // (the reference's fp8 query, nvfp4_mla/csrc/mla_decode.cu:425-457); K is stored as value / 8, hence the 8.
+  if (ct < N) s.qamax[ct] = 0, s.qamax_pe[ct] = 0;
   ptx::bar_sync(2, 256);
   const long long row0 = (long long)seg.b * P.heads + (long long)seg.hg * N;
   constexpr int CH = (CKV + KPE) / 8;  // 72 chunks of 8 channels per row
@@ -194,26 +199,46 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const De
       const unsigned int lo = (w[j] << 16) & 0x7FFFFFFFu, hi = w[j] & 0x7FFF0000u;
       m = max(m, max(lo, hi));
     }
-    if (m < 0x7F800000u) atomicMax(&s.qamax[n], m);  // ignore inf / nan for the scale
+    if (m < 0x7F800000u) atomicMax(c < 64 || !P8 ? &s.qamax[n] : &s.qamax_pe[n], m);  // ignore inf / nan for the scale
   }
   ptx::bar_sync(2, 256);
   for (int i = ct; i < N * CH; i += 256) {
     const int n = i / CH, c = i % CH;
-    int e = int(s.qamax[n] >> 23) - 127;       // floor(log2(amax)); -127 for 0 / subnormal rows
-    e = e < -100 ? -100 : e;
-    const float up = __uint_as_float(uint32_t(14 - e + 127) << 23);  // 2^(14 - e), exact
     const uint4 v = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
                            : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t h[4];
+    if constexpr (!P8) {
+      int e = int(s.qamax[n] >> 23) - 127;       // floor(log2(amax)); -127 for 0 / subnormal rows
+      e = e < -100 ? -100 : e;
+      const float up = __uint_as_float(uint32_t(14 - e + 127) << 23);  // 2^(14 - e), exact
+      uint32_t h[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      h[j] = ptx::f32x2_to_f16x2(__uint_as_float(w[j] << 16) * up, __uint_as_float(w[j] & 0xFFFF0000u) * up);
-    const int panel = c >> 3, cc = c & 7;
-    *reinterpret_cast<uint4*>(s.q[panel] + n * 128 + ((cc ^ (n & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-    if (c == 0) {
-      const float down = __uint_as_float(uint32_t(e - 14 + 127) << 23);  // 2^(e - 14)
-      s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * down;
+      for (int j = 0; j < 4; ++j)
+        h[j] = ptx::f32x2_to_f16x2(__uint_as_float(w[j] << 16) * up, __uint_as_float(w[j] & 0xFFFF0000u) * up);
+      const int panel = c >> 3, cc = c & 7;
+      *reinterpret_cast<uint4*>(s.q[panel] + n * 128 + ((cc ^ (n & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+      if (c == 0) {
+        const float down = __uint_as_float(uint32_t(e - 14 + 127) << 23);  // 2^(e - 14)
+        s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * down;
+        s.qb[par][n] = P.sm_scale_log2 * P.kpe_scale * down;
+      }
+    } else {
+      const float an = fmaxf(__uint_as_float(s.qamax[n]), 1e-30f), ap = fmaxf(__uint_as_float(s.qamax_pe[n]), 1e-30f);
+      const float inv = 448.f / (c < 64 ? an : ap);
+      uint32_t b[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t lo = ptx::f32x2_to_e4m3x2(__uint_as_float(w[2 * j] << 16) * inv, __uint_as_float(w[2 * j] & 0xFFFF0000u) * inv);
+        const uint32_t hi = ptx::f32x2_to_e4m3x2(__uint_as_float(w[2 * j + 1] << 16) * inv, __uint_as_float(w[2 * j + 1] & 0xFFFF0000u) * inv);
+        b[j] = lo | (hi << 16);
+      }
+      // 8 channels = 8 bytes: panel = 128 channels (rope: panel 4), 16-byte chunk (c % 16) / 2, half c % 2
+      const int panel = c >> 4, cc = (c & 15) >> 1;
+      *reinterpret_cast<uint2*>(s.q[panel] + n * 128 + ((cc ^ (n & 7)) << 4) + (c & 1) * 8) = make_uint2(b[0], b[1]);
+      if (c == 0) {
+        s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * 8.f * (an / 448.f);
+        s.qb[par][n] = P.sm_scale_log2 * P.kpe_scale * (ap / 448.f);
+      }
     }
   }
   ptx::fence_proxy_async_smem();
@@ -227,8 +252,8 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS>& s, const De
 //     load B's panel from tensor memory -> compute A's panel -> publish A's previous chunk -> (B's load has landed)
 //     -> store A's panel over it -> store B's panel to the V tile.
 // FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
-template <int N, int RAW_SLOTS, bool FULL, bool has_a, bool has_b>
-__device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
+template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
+__device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
                                              int lane, int quad, int hf) {
   const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
@@ -254,20 +279,28 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const 
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
-    uint32_t h[16];
+    if constexpr (!P8) {
+      uint32_t h[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
-      h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
+      for (int j = 0; j < 8; ++j) {
+        h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
+        h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
+      }
+      ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
+    } else {  // the rope bytes are E4M3 already
+      uint32_t h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = valid ? rw[j] : 0u;
+      ptx::tmem_st8(tm_lane + Cols<N, P8>::KROPE + 8 * hf, h);
     }
-    ptx::tmem_st16(tm_lane + Cols<N>::KROPE + 16 * hf, h);
     if (tr) MLA_TRACE_AT(P, 2, it);
   }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
-    uint32_t hb[32], h[32];
-    if (has_b) ptx::tmem_ld32(tm_lane + Cols<N>::K + 32 * p, hb);  // tile it - 1, on its way to the V tile
+    constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row: 32 (FP16) or 16 (E4M3)
+    uint32_t hb[W], h[W];
+    if (has_b) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);  // tile it - 1, on its way to the V tile
     if (has_a) {
       const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
       const uint32_t c0 = uint32_t(2 * g) << 4;
@@ -278,8 +311,10 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const 
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
       }
-      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
-      const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
+      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s); the 8-bit mode stores (e2m1 x s) / 8 so that the product
+      // (up to 2688) stays inside E4M3's range, and undoes the 8 in the score scale and the output
+      uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
+      if constexpr (P8) s01 = ptx::hmul2(s01, 0x30003000u), s23 = ptx::hmul2(s23, 0x30003000u);  // x 1/8, exact
       const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
                               __byte_perm(s23, s23, 0x3232)};
       const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
@@ -287,8 +322,16 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const 
       for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
         uint32_t e[4];
         ptx::e2m1x8_to_f16x8(wds[j], e);
+        if constexpr (!P8) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+          for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+        } else {  // the FP16 product is exact; the only rounding is the conversion to E4M3
+          uint32_t b[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc[j >> 1]));
+          h[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
+          h[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
+        }
       }
       // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
       ptx::tmem_wait_st();
@@ -302,17 +345,20 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const 
       ok = it == 0 || ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return false;
       ptx::tc_fence_after_sync();
-      ptx::tmem_st32(tm_lane + Cols<N>::K + 32 * p, h);
+      ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
       if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
     if (has_b) {
-      // PV of tile it - 2 must have finished with this block of the V tile
-      ok = it < 2 || ptx::mbar_wait(&s.v_free[g], it & 1, &s.abort_flag);
+      // PV of tile it - 2 must have finished with this block of the V tile. 16-bit: block mb = panels {mb, mb + 4};
+      // 8-bit: block mb = 128-channel panel mb = 64-channel panels {2mb, 2mb + 1}
+      ok = it < 2 || ptx::mbar_wait(&s.v_free[P8 ? p >> 1 : g], it & 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return false;
-      uint8_t* vrow = s.v16[p] + r * 128;
+      uint8_t* vrow = (P8 ? s.v16[p >> 1] : s.v16[p]) + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
+      for (int c = 0; c < W / 4; ++c) {
+        const uint32_t chunk = P8 ? uint32_t(4 * (p & 1) + c) : uint32_t(c);
+        *reinterpret_cast<uint4*>(vrow + ((chunk << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
+      }
       if (tr) MLA_TRACE_AT(P, 8 + g, it);
     }
   }
@@ -335,8 +381,8 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS>& s, const 
 // A warp whose wait gave up does not leave at once: the 256 convert threads meet at a named barrier at the start of
 // every segment, so it carries on (skipping the work) to the next such barrier, where the failure is OR-reduced and
 // all eight warps leave together.
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it,
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, int n_segs, uint32_t& it,
                                              uint32_t& seg_count) {
   const int lane = ptx::lane_id();
   const int cw = (threadIdx.x >> 5) - 4, quad = cw & 3, hf = cw >> 2;
@@ -348,13 +394,13 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
     const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[3], (it - 1) & 1, &s.abort_flag));
     if (ptx::bar_red_or(2, 256, !ok)) return;
-    load_query<N, RAW_SLOTS>(s, P, seg, cw * 32 + lane, seg_count & 3);
+    load_query<N, RAW_SLOTS, P8>(s, P, seg, cw * 32 + lane, seg_count & 3);
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const bool full = seg.tok0 + (t + 1) * TILE <= seg.tok_end;
-      const bool ok_s = !pending ? convert_step<N, RAW_SLOTS, false, true, false>(s, P, seg, t, it, lane, quad, hf)
-                        : full   ? convert_step<N, RAW_SLOTS, true, true, true>(s, P, seg, t, it, lane, quad, hf)
-                                 : convert_step<N, RAW_SLOTS, false, true, true>(s, P, seg, t, it, lane, quad, hf);
+      const bool ok_s = !pending ? convert_step<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
+                        : full   ? convert_step<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
+                                 : convert_step<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
       pending = true;
       if (!ok_s) {
         dead = true;
@@ -363,7 +409,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
     }
   }
   // drain: the batch's last tile still has to reach the V tile
-  if (pending && !dead) convert_step<N, RAW_SLOTS, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
+  if (pending && !dead) convert_step<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -372,12 +418,21 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 // lane issues. A tcgen05.commit tracks only the MMAs of the thread that executes it, so each role's barriers speak
 // for its own MMAs.
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const bool leader = ptx::elect_one();
   const uint32_t tm = s.tmem_base;
-  const uint32_t idesc = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, false, false);
+  constexpr uint32_t FMT = P8 ? ptx::FMT_E4M3 : ptx::FMT_F16;
+  constexpr int KSTEPS = P8 ? 2 : 4;            // MMAs per 64-channel panel (K = 32 E4M3 or 16 FP16 per MMA, 8 columns)
+  constexpr uint32_t W = Cols<N, P8>::PANEL;
+  const uint32_t idesc = ptx::instr_desc(128, N, FMT, FMT, false, false);
   const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q[0]), 16, 1024);
+  // byte offset of (64-channel panel p, K step ks) inside Q^T: 16-bit: panel p, 32 bytes per step;
+  // 8-bit: 128-channel panel p / 2, half p % 2 (64 bytes), 32 bytes per step. Rope = panel 8.
+  auto q_off = [](int p, int ks) { return P8 ? ((p >> 1) * N * 128 + (p & 1) * 64 + ks * 32) : (p * N * 128 + ks * 32); };
+  auto mma = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t accum) {
+    if constexpr (P8) ptx::mma_f8_ts(d, a, b, idesc, accum); else ptx::mma_f16_ts(d, a, b, idesc, accum);
+  };
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
@@ -390,11 +445,11 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
       ptx::tc_fence_after_sync();
       if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_f16_ts(tm + Cols<N>::sp(buf), tm + Cols<N>::KROPE + 8 * ks, q_desc + ((8 * N * 128 + ks * 32) >> 4), idesc, ks > 0);
+        for (int ks = 0; ks < KSTEPS; ++ks)
+          mma(tm + Cols<N, P8>::sp(buf), tm + Cols<N, P8>::KROPE + 8 * ks, q_desc + (q_off(8, ks) >> 4), ks > 0);
         ptx::mma_commit(&s.k_free[4]);
       }
-      // rolled loops (4 MMAs per trip): fully unrolled, the 36 operand sets would occupy ~100 registers of a warp
+      // rolled loops (one panel per trip): fully unrolled, the operand sets would occupy ~100 registers of a warp
       // group that has given most of its registers away
 #pragma unroll 1
       for (int g = 0; g < 4; ++g) {
@@ -406,9 +461,8 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
           for (int half = 0; half < 2; ++half) {
             const int p = g + 4 * half;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              ptx::mma_f16_ts(tm + Cols<N>::sn(buf), tm + Cols<N>::K + 32 * p + 8 * ks, q_desc + ((p * N * 128 + ks * 32) >> 4), idesc,
-                              (g | half | ks) != 0);
+            for (int ks = 0; ks < KSTEPS; ++ks)
+              mma(tm + Cols<N, P8>::sn(buf), tm + Cols<N, P8>::K + W * p + 8 * ks, q_desc + (q_off(p, ks) >> 4), (g | half | ks) != 0);
           }
           ptx::mma_commit(&s.k_free[g]);
           if (g == 3) ptx::mma_commit(&s.s_full[buf]);
@@ -419,13 +473,16 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
   }
 }
 
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const bool leader = ptx::elect_one();
   const uint32_t tm = s.tmem_base;
-  const uint32_t idesc = ptx::instr_desc(128, N, ptx::FMT_F16, ptx::FMT_F16, true, false);
-  // MN-major A: block mb = panels {mb, mb + 4} (channels [64mb, +64) and [256 + 64mb, +64)), so LBO = 4 panels
-  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), 4 * kVPanelBytes, 1024);
+  constexpr uint32_t FMT = P8 ? ptx::FMT_E4M3 : ptx::FMT_F16;
+  const uint32_t idesc = ptx::instr_desc(128, N, FMT, FMT, true, false);
+  // MN-major A, block mb of 128 channels. 16-bit: panels {mb, mb + 4} (channels [64mb, +64) and [256 + 64mb, +64)), so the
+  // second 128-byte run along M is 4 panels away (LBO); 8-bit: panel mb alone (one 128-byte run, LBO unused).
+  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), P8 ? 16 : 4 * kVPanelBytes, 1024);
+  constexpr int KROWS = P8 ? 32 : 16;  // tokens per MMA
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
@@ -440,11 +497,17 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
 #pragma unroll 1
         for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll 1
-          for (int kh = 0; kh < 2; ++kh) {  // 64 tokens = one P^T panel per trip
+          for (int kh = 0; kh < (P8 ? 1 : 2); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              ptx::mma_f16_ss(tm + Cols<N>::O + mb * N, v_desc + ((mb * kVPanelBytes + (4 * kh + ks) * 2048) >> 4),
-                              p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
+            for (int ks = 0; ks < 4; ++ks) {
+              const int row = (4 * kh + ks) * KROWS;  // first token of this K step
+              if constexpr (P8)
+                ptx::mma_f8_ss(tm + Cols<N, P8>::O + mb * N, v_desc + ((mb * kVPanelBytes + row * 128) >> 4),
+                               p_desc + ((ks * 32) >> 4), idesc, (t | ks) != 0);
+              else
+                ptx::mma_f16_ss(tm + Cols<N, P8>::O + mb * N, v_desc + ((mb * kVPanelBytes + row * 128) >> 4),
+                                p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
+            }
           }
           ptx::mma_commit(&s.v_free[mb]);
         }
@@ -458,17 +521,17 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS>& s, const Decod
 // ---------------------------------------------------------------------------------------------------------------
 // role: softmax + epilogue (4 warps; thread r = token row of S^T and channel row of O^T)
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS>
-__device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it,
+template <int N, int RAW_SLOTS, bool P8>
+__device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, int n_segs, uint32_t& it,
                                              uint32_t& seg_count) {
   const int lane = ptx::lane_id(), warp = threadIdx.x >> 5;
   const int r = threadIdx.x;  // 0..127
   const uint32_t tm_lane = s.tmem_base + (uint32_t(warp * 32) << 16);
   constexpr float kGrow = 8.f;  // rescale only when a score exceeds the running max by 2^8 (P stays <= 256)
-  const float ratio = P.kpe_scale / P.ckv_scale;
-  // P^T[head h][token r]: panel r / 64, row h (128 B), 16-byte chunk (r % 64) / 8 swizzled by h % 8
-  const uint32_t p_off = uint32_t(r >> 6) * (N * 128) + (r & 7) * 2;
-  const uint32_t p_chunk = uint32_t((r & 63) >> 3) << 4;
+  // P^T[head h][token r], row h = 128 bytes. 16-bit: panel r / 64, 16-byte chunk (r % 64) / 8; 8-bit: chunk r / 16.
+  // The chunk index is swizzled by h % 8.
+  const uint32_t p_off = P8 ? uint32_t(r & 15) : uint32_t(r >> 6) * (N * 128) + (r & 7) * 2;
+  const uint32_t p_chunk = (P8 ? uint32_t(r >> 4) : uint32_t((r & 63) >> 3)) << 4;
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
@@ -489,12 +552,12 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
         for (int c0 = 0; c0 < N; c0 += 16) {
           uint32_t sn[16], sp[16];
-          ptx::tmem_ld16(tm_lane + Cols<N>::sn(buf) + c0, sn);
-          ptx::tmem_ld16(tm_lane + Cols<N>::sp(buf) + c0, sp);
+          ptx::tmem_ld16(tm_lane + Cols<N, P8>::sn(buf) + c0, sn);
+          ptx::tmem_ld16(tm_lane + Cols<N, P8>::sp(buf) + c0, sp);
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = fmaf(ratio, __uint_as_float(sp[j]), __uint_as_float(sn[j])) * s.qa[par_q][c0 + j];
+            const float v = fmaf(__uint_as_float(sp[j]), s.qb[par_q][c0 + j], __uint_as_float(sn[j]) * s.qa[par_q][c0 + j]);
             x[c0 + j] = valid ? v : -INFINITY;
           }
         }
@@ -546,11 +609,11 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
             for (int c0 = 0; c0 < N; c0 += 16) {
               uint32_t o[16];
-              ptx::tmem_ld16(tm_lane + Cols<N>::O + mb * N + c0, o);
+              ptx::tmem_ld16(tm_lane + Cols<N, P8>::O + mb * N + c0, o);
               ptx::tmem_wait_ld();
 #pragma unroll
               for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr[c0 + j]);
-              ptx::tmem_st16(tm_lane + Cols<N>::O + mb * N + c0, o);
+              ptx::tmem_st16(tm_lane + Cols<N, P8>::O + mb * N + c0, o);
             }
           }
           ptx::tmem_wait_st();
@@ -567,7 +630,10 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
       for (int h = 0; h < N; ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
-        *reinterpret_cast<__half*>(p_base + h * 128 + (p_chunk ^ (uint32_t(h & 7) << 4))) = __float2half_rn(pv);
+        if constexpr (P8)
+          *(p_base + h * 128 + (p_chunk ^ (uint32_t(h & 7) << 4))) = uint8_t(ptx::f32x2_to_e4m3x2(pv, 0.f));
+        else
+          *reinterpret_cast<__half*>(p_base + h * 128 + (p_chunk ^ (uint32_t(h & 7) << 4))) = __float2half_rn(pv);
       }
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
       ptx::fence_proxy_async_smem();
@@ -597,7 +663,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
     for (int h = 0; h < N; ++h) {
       const float l = (s.red[0][h] + s.red[1][h]) + (s.red[2][h] + s.red[3][h]);
-      inv[h] = l > 0.f ? P.ckv_scale / l : 0.f;
+      inv[h] = l > 0.f ? (P8 ? 8.f : 1.f) * P.ckv_scale / l : 0.f;
       lsum[h] = l;
     }
     const long long slot = (long long)seg.cta + seg.w;
@@ -607,11 +673,12 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 #pragma unroll
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t o[16];
-        ptx::tmem_ld16(tm_lane + Cols<N>::O + mb * N + c0, o);
+        ptx::tmem_ld16(tm_lane + Cols<N, P8>::O + mb * N + c0, o);
         ptx::tmem_wait_ld();
+        // lane r of block mb is channel 64mb + r (r < 64) or 256 + 64mb + r - 64 in 16-bit mode, 128mb + r in 8-bit mode
+        const int ch = P8 ? 128 * mb + r : 64 * mb + (r & 63) + 256 * (r >> 6);
 #pragma unroll
-        for (int j = 0; j < 16; ++j)  // lane r of block mb is channel 64mb + r (r < 64) or 256 + 64mb + r - 64
-          obase[(long long)(c0 + j) * CKV + 64 * mb + (r & 63) + 256 * (r >> 6)] = __uint_as_float(o[j]) * inv[c0 + j];
+        for (int j = 0; j < 16; ++j) obase[(long long)(c0 + j) * CKV + ch] = __uint_as_float(o[j]) * inv[c0 + j];
       }
     }
     if (r < N) {
@@ -632,8 +699,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS>& s, const 
 // ---------------------------------------------------------------------------------------------------------------
 enum Role { kRoleSoftmax, kRoleConvert, kRoleQk, kRoleProducer, kRolePv, kRoleIdle };
 
-template <int N, int RAW_SLOTS, int ROLE>
-__device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map) {
+template <int N, int RAW_SLOTS, bool P8, int ROLE>
+__device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map) {
   const int2 range = P.cta_range[blockIdx.x];
   uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
   for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
@@ -644,11 +711,11 @@ __device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS>& s, const Deco
       s.segs[threadIdx.x] = g;
     }
     __syncthreads();
-    if (ROLE == kRoleSoftmax) softmax_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    if (ROLE == kRoleConvert) convert_role<N, RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    if (ROLE == kRoleQk) qk_role<N, RAW_SLOTS>(s, P, n_segs, it);
-    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS>(s, P, ckv_map, n_segs, hcount);
-    if (ROLE == kRolePv) pv_role<N, RAW_SLOTS>(s, P, n_segs, it);
+    if (ROLE == kRoleSoftmax) softmax_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
+    if (ROLE == kRoleConvert) convert_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
+    if (ROLE == kRoleQk) qk_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
+    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS, P8>(s, P, ckv_map, n_segs, hcount);
+    if (ROLE == kRolePv) pv_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
     __syncthreads();
     if (s.abort_flag) break;
   }
@@ -657,11 +724,11 @@ __device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS>& s, const Deco
 // ---------------------------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS>
+template <int N, int RAW_SLOTS, bool P8>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParams P) {
   extern __shared__ uint8_t smem_raw[];
-  using Smem = DecodeSmem<N, RAW_SLOTS>;
+  using Smem = DecodeSmem<N, RAW_SLOTS, P8>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
 
@@ -691,16 +758,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
   if (warp < 4) {
     ptx::reg_alloc<160>();
-    run_role<N, RAW_SLOTS, kRoleSoftmax>(s, P, &ckv_map);
+    run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map);
   } else if (warp < 12) {
     ptx::reg_alloc<152>();
-    run_role<N, RAW_SLOTS, kRoleConvert>(s, P, &ckv_map);
+    run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map);
   } else {
     ptx::reg_dealloc<48>();
-    if (warp == 12) run_role<N, RAW_SLOTS, kRoleQk>(s, P, &ckv_map);
-    else if (warp == 13) run_role<N, RAW_SLOTS, kRoleProducer>(s, P, &ckv_map);
-    else if (warp == 14) run_role<N, RAW_SLOTS, kRolePv>(s, P, &ckv_map);
-    else run_role<N, RAW_SLOTS, kRoleIdle>(s, P, &ckv_map);
+    if (warp == 12) run_role<N, RAW_SLOTS, P8, kRoleQk>(s, P, &ckv_map);
+    else if (warp == 13) run_role<N, RAW_SLOTS, P8, kRoleProducer>(s, P, &ckv_map);
+    else if (warp == 14) run_role<N, RAW_SLOTS, P8, kRolePv>(s, P, &ckv_map);
+    else run_role<N, RAW_SLOTS, P8, kRoleIdle>(s, P, &ckv_map);
   }
 
   ptx::tc_fence_before_sync();

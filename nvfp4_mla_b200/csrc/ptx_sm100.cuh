@@ -161,6 +161,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -171,6 +176,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+
+// by array length
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_stn(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+__device__ __forceinline__ void tmem_stn(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
 
 // ---------------------------------------------------------------------------------------------------------------
 // tcgen05.mma descriptors
@@ -253,13 +264,13 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t x) {
   return d;
 }
 // f16x2 -> two E4M3 bytes, round to nearest even, saturating
-__device__ __forceinline__ uint16_t f16x2_to_e4m3x2(uint32_t h) {
+__device__ __forceinline__ uint32_t f16x2_to_e4m3x2(uint32_t h) {  // element i of the pair -> byte i
   uint16_t d;
   asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(d) : "r"(h));
   return d;
 }
 // (hi, lo) floats -> two E4M3 bytes, lo in the low byte
-__device__ __forceinline__ uint16_t f32x2_to_e4m3x2(float lo, float hi) {
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
   uint16_t d;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
   return d;

@@ -138,6 +138,39 @@ def test_calibrated_scales():
     check(c, out, None, "calibrated")
 
 
+SCALES = {"scale 0.5": (0.5, 2.0), "calibrated": (2.0 ** -9, 2.0 ** -6)}
+
+
+@pytest.mark.parametrize("scales", SCALES.values(), ids=SCALES.keys())
+@pytest.mark.parametrize("num_splits", [0, 3])
+@pytest.mark.parametrize("kv_lens,page_size,heads", CASES[:6])
+def test_decode_fp8(num_splits, kv_lens, page_size, heads, scales):
+    """fp8 mode (E4M3 query rows, K, V and P): the reference's bounds (tests/test_decode.py:77-88): rel-L2 < 0.08 against
+    the dequantised-cache oracle, and at most 1.2x the bf16 mode's error against the unquantised BF16 cache. Both the
+    scale-0.5 and the calibrated global scales (block scales near 448: e2m1 x scale reaches 2688, the saturation guard)."""
+    c = SyntheticCache(kv_lens, page_size, heads, *scales, seed=len(kv_lens) + page_size, keep_bf16=True).to("cuda")
+    out = mla.decode(*c.args(), max_kv_len=c.max_kv_len, num_splits=num_splits, precision="fp8")
+    out16 = mla.decode(*c.args(), max_kv_len=c.max_kv_len, num_splits=num_splits)
+    check_status()
+    assert not out.isnan().any()
+    want, _ = oracle_reference(c)
+    got = out.float().cpu().numpy()
+    err = O.rel_l2(got, want)
+    print(f"fp8 splits={num_splits} {kv_lens} ps={page_size} H={heads}: rel-L2 {err:.3e}")
+    assert err < 0.08
+    ref = c.reference_bf16().cpu().numpy()
+    assert O.rel_l2(got, ref) < 1.2 * O.rel_l2(out16.float().cpu().numpy(), ref)
+
+
+def test_fp8_streamed_reference_8k():
+    c = SyntheticCache([8192] * 8, 64, 16, None, None, seed=4, device="cuda")
+    out = mla.decode(*c.args(), max_kv_len=8192, precision="fp8")
+    check_status()
+    want, _ = attention_paged_nvfp4(*c.args(), requests=[0, 7])
+    assert not out.isnan().any()
+    assert rel_l2(out[[0, 7]], want) < 0.08
+
+
 def test_max_kv_len_is_an_upper_bound():
     c = SyntheticCache([100, 900, 257], 64, 16, 0.5, 2.0, seed=9).to("cuda")
     a = mla.decode(*c.args(), max_kv_len=c.max_kv_len)
@@ -172,6 +205,9 @@ def test_cuda_graph_replay_with_new_lengths():
 def test_public_api():
     c = SyntheticCache([300, 70], 16, 16, 0.5, 2.0, seed=2).to("cuda")
     check(c, mla.decode(*c.args()), None, "decode defaults")
+    assert mla.decode(*c.args(), precision="fp8").dtype == torch.bfloat16
+    with pytest.raises(ValueError, match="precision"):
+        mla.decode(*c.args(), precision="fp4-qk")
     with pytest.raises(ValueError, match="precision"):
         mla.decode(*c.args(), precision="int8")
     with pytest.raises(ValueError, match="dtype"):
