@@ -133,6 +133,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS))
     ap.add_argument("--num-splits", type=int, default=0)
+    ap.add_argument("--precision", default=None, choices=["bf16", "fp8"], help="override the workload's precision mode")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -145,6 +146,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     B, H, kv_len, ps, precision = WORKLOADS[args.workload]
+    precision = args.precision or precision
     config = {"workload": f"{args.workload}: B={B} per GPU, H={H}, kv_len={kv_len}, page_size={ps}, precision={precision}, "
                           f"seeded N(0,1) latent KV quantised to NVFP4 (calibrated global scales), shuffled page table",
               "parallelism": f"batch-sharded dp{world}, no collective", "num_splits": args.num_splits,

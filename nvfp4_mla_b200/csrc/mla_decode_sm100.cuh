@@ -89,9 +89,9 @@ struct DecodeSmem {
   unsigned int qamax[N], qamax_pe[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
-  uint64_t k_full[5], k_free[5];                    // chunk 0..3 = latent panels {g, g+4}, chunk 4 = rope
+  uint64_t k_full[5];                               // K chunk in tensor memory: 0..3 = latent panels {g, g+4}, 4 = rope
+  uint64_t k_done;                                  // QK^T of the tile has finished reading K and Q^T (one phase per tile)
   uint64_t v_full;                                  // the V tile is written (one phase per tile)
-  uint64_t v_free[4];                               // PV has read block mb of the V tile
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -275,7 +275,9 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     // ---- rope chunk: 32 channels of this thread's half
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
-    ok = it == 0 || ptx::mbar_wait(&s.k_free[4], prev, &s.abort_flag);
+    // K of the previous tile may be overwritten once its QK^T has finished. This is the only wait on QK^T in the step:
+    // what follows is straight-line code, so the compiler can overlap one panel's arithmetic with another's stores.
+    ok = it == 0 || ptx::mbar_wait(&s.k_done, prev, &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
@@ -341,18 +343,14 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
-      // ... once the previous tile's QK^T chunk has read them
-      ok = it == 0 || ptx::mbar_wait(&s.k_free[g], prev, &s.abort_flag);
-      if (!__all_sync(~0u, ok)) return false;
-      ptx::tc_fence_after_sync();
       ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
       if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
     if (has_b) {
-      // PV of tile it - 2 must have finished with this block of the V tile. 16-bit: block mb = panels {mb, mb + 4};
-      // 8-bit: block mb = 128-channel panel mb = 64-channel panels {2mb, 2mb + 1}
-      ok = it < 2 || ptx::mbar_wait(&s.v_free[P8 ? p >> 1 : g], it & 1, &s.abort_flag);
-      if (!__all_sync(~0u, ok)) return false;
+      if (g == 0) {  // PV of tile it - 2 must have finished with the V tile (the only wait on PV in the step)
+        ok = it < 2 || ptx::mbar_wait(&s.p_free[it & 1], ((it - 2) >> 1) & 1, &s.abort_flag);
+        if (!__all_sync(~0u, ok)) return false;
+      }
       uint8_t* vrow = (P8 ? s.v16[p >> 1] : s.v16[p]) + r * 128;
 #pragma unroll
       for (int c = 0; c < W / 4; ++c) {
@@ -392,7 +390,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
     // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
-    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[3], (it - 1) & 1, &s.abort_flag));
+    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_done, (it - 1) & 1, &s.abort_flag));
     if (ptx::bar_red_or(2, 256, !ok)) return;
     load_query<N, RAW_SLOTS, P8>(s, P, seg, cw * 32 + lane, seg_count & 3);
     ++seg_count;
@@ -447,7 +445,6 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks)
           mma(tm + Cols<N, P8>::sp(buf), tm + Cols<N, P8>::KROPE + 8 * ks, q_desc + (q_off(8, ks) >> 4), ks > 0);
-        ptx::mma_commit(&s.k_free[4]);
       }
       // rolled loops (one panel per trip): fully unrolled, the operand sets would occupy ~100 registers of a warp
       // group that has given most of its registers away
@@ -464,8 +461,7 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
             for (int ks = 0; ks < KSTEPS; ++ks)
               mma(tm + Cols<N, P8>::sn(buf), tm + Cols<N, P8>::K + W * p + 8 * ks, q_desc + (q_off(p, ks) >> 4), (g | half | ks) != 0);
           }
-          ptx::mma_commit(&s.k_free[g]);
-          if (g == 3) ptx::mma_commit(&s.s_full[buf]);
+          if (g == 3) ptx::mma_commit(&s.k_done), ptx::mma_commit(&s.s_full[buf]);
         }
       }
       if (leader) MLA_TRACE_AT(P, 17, it);
@@ -509,7 +505,6 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
                                 p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
             }
           }
-          ptx::mma_commit(&s.v_free[mb]);
         }
         ptx::mma_commit(&s.p_free[buf]);
       }
@@ -734,9 +729,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
-    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8), ptx::mbar_init(&s.k_free[i], 1);
+    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8);
+    ptx::mbar_init(&s.k_done, 1);
     ptx::mbar_init(&s.v_full, 8);
-    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.v_free[i], 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 128);
       ptx::mbar_init(&s.p_full[i], 128), ptx::mbar_init(&s.p_free[i], 1);
@@ -757,13 +752,13 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
   // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
   if (warp < 4) {
-    ptx::reg_alloc<160>();
+    ptx::reg_alloc<168>();
     run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map);
   } else if (warp < 12) {
-    ptx::reg_alloc<152>();
+    ptx::reg_alloc<144>();
     run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map);
   } else {
-    ptx::reg_dealloc<48>();
+    ptx::reg_dealloc<56>();
     if (warp == 12) run_role<N, RAW_SLOTS, P8, kRoleQk>(s, P, &ckv_map);
     else if (warp == 13) run_role<N, RAW_SLOTS, P8, kRoleProducer>(s, P, &ckv_map);
     else if (warp == 14) run_role<N, RAW_SLOTS, P8, kRolePv>(s, P, &ckv_map);
