@@ -37,7 +37,9 @@ WORKLOADS = {
     "h16_b64_16k": (64, 16, 16384, 64, "bf16"),
     "h16_b8_64k": (8, 16, 65536, 64, "bf16"),        # small case for ncu captures (185 MB of KV, still larger than L2)
     "h128_b64_16k": (64, 128, 16384, 64, "bf16"),
+    "c4_h128_b2_1m_seq": (2, 128, 1048576, 64, "bf16"),  # BASELINE config 4: sequence-sharded, strong scaling
 }
+SEQUENCE_SHARDED = {"c4_h128_b2_1m_seq"}
 TOKEN_BYTES = 352
 # Published by the reference for this exact shape on B200: its SM100 tcgen05 kernel, 0.309 ms = 4.77 TB/s
 # (README.md:194 and benchmarks/results/b200.csv:108 of the reference project).
@@ -189,10 +191,28 @@ def main():
     from nvfp4_mla_b200 import _lib
     from nvfp4_mla_b200.testing import SM_SCALE, SyntheticCache
 
-    cache = SyntheticCache([kv_len] * B, ps, H, None, None, seed=rank, device=dev)
+    seq = args.workload in SEQUENCE_SHARDED
+    if seq:
+        # every rank holds a contiguous 1/world slice of each request's pages (generated directly as the local slice:
+        # rank r's tokens are a seeded stream of their own), queries replicated
+        from nvfp4_mla_b200 import dist as mdist
+        local_len = mdist.shard_sequence(kv_len, ps, world)[rank][2]
+        cache = SyntheticCache([local_len] * B, ps, H, 2.0 ** -9, 2.0 ** -6, seed=1000 + rank, device=dev)
+        qsrc = SyntheticCache([ps] * B, ps, H, 1.0, 1.0, seed=7, device=dev)
+        cache.q_nope, cache.q_pe = qsrc.q_nope, qsrc.q_pe
+        config["parallelism"] = f"sequence-sharded over {world} GPU(s): local split-KV decode, all-gather of (o, lse), merge"
+        kv_len_local = local_len
+    else:
+        cache = SyntheticCache([kv_len] * B, ps, H, None, None, seed=rank, device=dev)
+        kv_len_local = kv_len
     kv_bytes = cache.kv_bytes
     dargs = cache.args(SM_SCALE)
-    kw = dict(max_kv_len=kv_len, num_splits=args.num_splits, precision=precision)
+    kw = dict(max_kv_len=kv_len_local, num_splits=args.num_splits, precision=precision)
+    if seq:
+        def decode_fn(*a, **k):
+            return mdist.decode_sequence_sharded(*a, **k) if world > 1 else mla.decode(*a, **k)
+    else:
+        decode_fn = mla.decode
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -209,7 +229,7 @@ def main():
 
     # ---- device-resident timing -------------------------------------------------------------------------------
     for _ in range(args.warmup):
-        out = mla.decode(*dargs, **kw)
+        out = decode_fn(*dargs, **kw)
     sync_all()
     lib = _lib.load()
     _lib.check(lib.nvfp4_mla_profile_begin(args.steps))
@@ -217,7 +237,7 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        out = mla.decode(*dargs, **kw)
+        out = decode_fn(*dargs, **kw)
     ev1.record()
     sync_all()
     clocks = sampler.stop() if sampler else None
@@ -227,6 +247,13 @@ def main():
         raise RuntimeError(lib.nvfp4_mla_last_error().decode())
     ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     kernel_ms = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
+    kv_bytes_all = kv_bytes
+    if world > 1:
+        t = torch.tensor([float(kv_bytes)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        kv_bytes_all = float(t.item())
+    else:
+        kv_bytes_all = float(kv_bytes)
     status = mla.workspace_status()
     if status != 0 or bool(out.isnan().any()):
         raise SystemExit(f"decode failed: status {status}")
@@ -241,8 +268,8 @@ def main():
     def e2e_step():
         for d, h in zip(devbuf, host):
             d.copy_(h, non_blocking=True)
-        o = mla.decode(devbuf[0], devbuf[1], cache.ckv_cache, cache.ckv_sf_cache, cache.kpe_cache, devbuf[2], devbuf[3],
-                       SM_SCALE, cache.ckv_scale, cache.kpe_scale, **kw)
+        o = decode_fn(devbuf[0], devbuf[1], cache.ckv_cache, cache.ckv_sf_cache, cache.kpe_cache, devbuf[2], devbuf[3],
+                      SM_SCALE, cache.ckv_scale, cache.kpe_scale, **kw)
         out_host.copy_(o, non_blocking=True)
 
     for _ in range(args.warmup):
@@ -262,17 +289,17 @@ def main():
 
     peak, peak_kind = measured_peak()
     achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
-    value = world * kv_bytes / (ms_step * 1e-3) / 1e12
+    value = kv_bytes_all / (ms_step * 1e-3) / 1e12
     line = {
         "metric": "nvfp4_mla_decode_kv_bandwidth", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if seq else "weak",
         "vs_baseline": (value / world / BASELINE_TBPS[args.workload]) if args.workload in BASELINE_TBPS and world == 1 else None,
         "dtype": "f16 operands, f32 accumulate" if precision == "bf16" else "e4m3 operands, f32 accumulate",
         "data": "synthetic", "config": config,
         "decode_us": ms_step * 1e3, "frac_of_8tbps": value / world / 8.0,
-        "e2e": {"value": world * kv_bytes / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": kv_bytes_all / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": KERNELS_PER_DECODE * args.steps,
+        "gpu_launches": (KERNELS_PER_DECODE + (1 if seq and world > 1 else 0)) * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
                      "algorithmic_bytes_per_launch": kv_bytes,

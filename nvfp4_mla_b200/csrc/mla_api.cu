@@ -43,8 +43,8 @@ DeviceInfo g_devices[kMaxDevices];
 
 using DecodeKernel = void (*)(const CUtensorMap, const mla::DecodeParams);
 constexpr int kHeadsPerCta = 16;
-// staging slots of 64 tokens: the 16-bit mode's V tile leaves room for 3, the 8-bit mode's for 6
-constexpr int kRawSlots16 = 3, kRawSlots8 = 6;
+// staging slots of 64 tokens next to the V tile (one FP16 tile of 128 KB, or two E4M3 tiles of 64 KB)
+constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
 DecodeKernel decode_kernel(int precision) {
   return precision == NVFP4_MLA_PRECISION_FP8 ? mla::mla_decode_kernel<kHeadsPerCta, kRawSlots8, true>
                                               : mla::mla_decode_kernel<kHeadsPerCta, kRawSlots16, false>;

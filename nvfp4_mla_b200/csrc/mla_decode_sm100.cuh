@@ -53,6 +53,12 @@ constexpr int kTraceTiles = 64, kTraceEvents = 32;
 #else
 #define MLA_TRACE_AT(P, ev, tile) do {} while (0)
 #endif
+// Timing experiments (results become wrong): compile with -DMLA_EXPERIMENT=<bits>: 1 no V stores, 2 no K stores,
+// 4 no K loads, 8 no arithmetic, 16 no softmax exp / P stores, 32 no PV MMAs, 64 no latent QK MMAs
+#ifndef MLA_EXPERIMENT
+#define MLA_EXPERIMENT 0
+#endif
+#define MLA_EXP(P, bit) ((MLA_EXPERIMENT & (bit)) != 0)
 
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
@@ -79,7 +85,8 @@ struct DecodeSmem {
   // Operand tiles, all with the 128-byte swizzle, one 128-byte row per token (V) or head (Q^T, P^T).
   //   16-bit mode: a row holds 64 elements. V: 8 panels of 64 channels; Q^T: 8 latent panels + rope; P^T: 2 panels of 64 tokens
   //   8-bit mode : a row holds 128 elements. V: 4 panels of 128 channels; Q^T: 4 latent panels + rope (half a row); P^T: 1 panel
-  alignas(1024) uint8_t v16[P8 ? 4 : 8][kVPanelBytes];
+  static constexpr int VBUFS = P8 ? 2 : 1;          // the 8-bit V tile is small enough to double buffer
+  alignas(1024) uint8_t v16[VBUFS][P8 ? 4 : 8][kVPanelBytes];
   alignas(1024) uint8_t q[P8 ? 5 : 9][N * 128];
   alignas(1024) uint8_t p[2][P8 ? 1 : 2][N * 128];  // double buffered
   alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
@@ -91,7 +98,7 @@ struct DecodeSmem {
   uint64_t raw_empty[RAW_SLOTS];
   uint64_t k_full[5];                               // K chunk in tensor memory: 0..3 = latent panels {g, g+4}, 4 = rope
   uint64_t k_done;                                  // QK^T of the tile has finished reading K and Q^T (one phase per tile)
-  uint64_t v_full;                                  // the V tile is written (one phase per tile)
+  uint64_t v_full[2];                               // V buffer b is written (one phase per tile that uses the buffer)
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -126,6 +133,7 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, c
     for (int hk = 0; hk < 2 * seg.ntiles; ++hk, ++hcount) {
       const int slot = hcount % RAW_SLOTS;
       const uint32_t use = hcount / RAW_SLOTS;
+      if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 25, hcount >> 1);
       bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
       if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 24, hcount >> 1);
@@ -267,6 +275,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   bool ok, valid = true;
   uint4 sf16 = make_uint4(0, 0, 0, 0);
   if (has_a) {
+    if (tr) MLA_TRACE_AT(P, 1, it);
     ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
     if (tr) MLA_TRACE_AT(P, 0, it);
@@ -302,7 +311,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
     constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row: 32 (FP16) or 16 (E4M3)
     uint32_t hb[W], h[W];
-    if (has_b) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);  // tile it - 1, on its way to the V tile
+    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);  // tile it - 1, on its way to the V tile
     if (has_a) {
       const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
       const uint32_t c0 = uint32_t(2 * g) << 4;
@@ -323,6 +332,10 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 #pragma unroll
       for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
         uint32_t e[4];
+        if (MLA_EXP(P, 8)) {
+          for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = wds[j] + i + sc[0];
+          continue;
+        }
         ptx::e2m1x8_to_f16x8(wds[j], e);
         if constexpr (!P8) {
 #pragma unroll
@@ -343,17 +356,19 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
-      ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
+      if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
       if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
     if (has_b) {
-      if (g == 0) {  // PV of tile it - 2 must have finished with the V tile (the only wait on PV in the step)
-        ok = it < 2 || ptx::mbar_wait(&s.p_free[it & 1], ((it - 2) >> 1) & 1, &s.abort_flag);
+      constexpr uint32_t VB = DecodeSmem<N, RAW_SLOTS, P8>::VBUFS;
+      const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
+      if (g == 0) {  // the PV that last read this V buffer (tile tb - VB) must have finished: the only wait on PV in the step
+        ok = tb < VB || ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag);
         if (!__all_sync(~0u, ok)) return false;
       }
-      uint8_t* vrow = (P8 ? s.v16[p >> 1] : s.v16[p]) + r * 128;
+      uint8_t* vrow = (P8 ? s.v16[vbuf][p >> 1] : s.v16[vbuf][p]) + r * 128;
 #pragma unroll
-      for (int c = 0; c < W / 4; ++c) {
+      for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c) {
         const uint32_t chunk = P8 ? uint32_t(4 * (p & 1) + c) : uint32_t(c);
         *reinterpret_cast<uint4*>(vrow + ((chunk << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
       }
@@ -371,7 +386,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.v_full);  // phase of tile it - 1
+    if (lane == 0) ptx::mbar_arrive(&s.v_full[(it - 1) % DecodeSmem<N, RAW_SLOTS, P8>::VBUFS]);  // for tile it - 1
   }
   return true;
 }
@@ -455,7 +470,7 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
         ptx::tc_fence_after_sync();
         if (leader) {
 #pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
+          for (int half = 0; half < (MLA_EXP(P, 64) ? 0 : 2); ++half) {
             const int p = g + 4 * half;
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
@@ -477,23 +492,25 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
   const uint32_t idesc = ptx::instr_desc(128, N, FMT, FMT, true, false);
   // MN-major A, block mb of 128 channels. 16-bit: panels {mb, mb + 4} (channels [64mb, +64) and [256 + 64mb, +64)), so the
   // second 128-byte run along M is 4 panels away (LBO); 8-bit: panel mb alone (one 128-byte run, LBO unused).
-  const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0]), P8 ? 16 : 4 * kVPanelBytes, 1024);
+  const uint64_t v_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(s.v16[0][0]), P8 ? 16 : 4 * kVPanelBytes, 1024);
+  constexpr uint32_t VB = DecodeSmem<N, RAW_SLOTS, P8>::VBUFS;
   constexpr int KROWS = P8 ? 32 : 16;  // tokens per MMA
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t par = it & 1, buf = it & 1;
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][0]), 16, 1024);
+      const uint64_t v_desc = v_desc0 + (((it % VB) * sizeof(s.v16[0])) >> 4);
       // ---- O^T += V^T . P^T
       if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full, par, &s.abort_flag))) return;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag))) return;
       if (leader) MLA_TRACE_AT(P, 18, it);
       ptx::tc_fence_after_sync();
       if (leader) {
 #pragma unroll 1
         for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll 1
-          for (int kh = 0; kh < (P8 ? 1 : 2); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
+          for (int kh = 0; kh < (MLA_EXP(P, 32) ? 0 : (P8 ? 1 : 2)); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               const int row = (4 * kh + ks) * KROWS;  // first token of this K step
@@ -535,6 +552,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     float m[N], lsum[N];
 #pragma unroll
     for (int h = 0; h < N; ++h) m[h] = -INFINITY, lsum[h] = 0.f;
+    bool scales_loaded = false;
+    float qa_r[N], qb_r[N];
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
@@ -542,6 +561,11 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       float x[N];
+      if (!scales_loaded) {  // written by the convert warps before the segment's first K chunk was published
+#pragma unroll
+        for (int h = 0; h < N; ++h) qa_r[h] = s.qa[par_q][h], qb_r[h] = s.qb[par_q][h];
+        scales_loaded = true;
+      }
       if (ok) {
         const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
 #pragma unroll
@@ -552,7 +576,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = fmaf(__uint_as_float(sp[j]), s.qb[par_q][c0 + j], __uint_as_float(sn[j]) * s.qa[par_q][c0 + j]);
+            const float v = fmaf(__uint_as_float(sp[j]), qb_r[c0 + j], __uint_as_float(sn[j]) * qa_r[c0 + j]);
             x[c0 + j] = valid ? v : -INFINITY;
           }
         }
@@ -561,7 +585,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
         for (int h = 0; h < N; ++h) x[h] = -INFINITY;
       }
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&s.s_free[buf]);  // QK^T of tile it + 2 may overwrite this S^T buffer
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.s_free[buf]);  // QK^T of tile it + 2 may overwrite this S^T buffer
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       bool need = !ok;
 #pragma unroll
@@ -622,7 +647,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
       uint8_t* const p_base = s.p[buf][0] + p_off;
 #pragma unroll
-      for (int h = 0; h < N; ++h) {
+      for (int h = 0; h < (MLA_EXP(P, 16) ? 0 : N); ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
         if constexpr (P8)
@@ -634,7 +659,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       ptx::fence_proxy_async_smem();
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&s.p_full[buf]);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
@@ -731,10 +757,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8);
     ptx::mbar_init(&s.k_done, 1);
-    ptx::mbar_init(&s.v_full, 8);
+    ptx::mbar_init(&s.v_full[0], 8), ptx::mbar_init(&s.v_full[1], 8);
     for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 128);
-      ptx::mbar_init(&s.p_full[i], 128), ptx::mbar_init(&s.p_free[i], 1);
+      ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 4);  // one arrival per softmax warp
+      ptx::mbar_init(&s.p_full[i], 4), ptx::mbar_init(&s.p_free[i], 1);
     }
     s.abort_flag = 0;
     ptx::fence_mbar_init();
