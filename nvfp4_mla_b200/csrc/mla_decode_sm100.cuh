@@ -50,8 +50,19 @@ constexpr int kTraceTiles = 64, kTraceEvents = 32;
   do {                                                                                        \
     if ((P).trace && blockIdx.x == 0 && (tile) < mla::kTraceTiles) (P).trace[(ev) * mla::kTraceTiles + (tile)] = clock64(); \
   } while (0)
+// wait-time accounting: MLA_WAIT(P, slot, expr) evaluates the (waiting) expression and adds the cycles it took to
+// trace[31][slot] (CTA 0 only; meant to be used by one thread per role)
+#define MLA_WAIT(P, slot, expr)                                                                     \
+  ([&] {                                                                                            \
+    const long long t0_ = clock64();                                                                \
+    const bool r_ = (expr);                                                                         \
+    if ((P).trace && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && ((slot) < 32 || threadIdx.x == ((slot) >> 8)))                   \
+      atomicAdd(reinterpret_cast<unsigned long long*>((P).trace + 31 * mla::kTraceTiles + ((slot) & 31)), (unsigned long long)(clock64() - t0_)); \
+    return r_;                                                                                      \
+  }())
 #else
 #define MLA_TRACE_AT(P, ev, tile) do {} while (0)
+#define MLA_WAIT(P, slot, expr) (expr)
 #endif
 // Timing experiments (results become wrong): compile with -DMLA_EXPERIMENT=<bits>: 1 no V stores, 2 no K stores,
 // 4 no K loads, 8 no arithmetic, 16 no softmax exp / P stores, 32 no PV MMAs, 64 no latent QK MMAs
@@ -134,7 +145,7 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, c
       const int slot = hcount % RAW_SLOTS;
       const uint32_t use = hcount / RAW_SLOTS;
       if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 25, hcount >> 1);
-      bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
+      bool ok = MLA_WAIT(P, 0, ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag));
       if (!__all_sync(~0u, ok)) return;
       if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 24, hcount >> 1);
       const int tok = seg.tok0 + hk * HALF;
@@ -252,7 +263,8 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
   ptx::fence_proxy_async_smem();
 }
 
-// One pipeline step of a convert thread: phase A of tile `it` (dequantise the thread's share of the token row into
+// One pipeline step of a convert thread, interleaved form (used by the 16-bit mode, whose single V tile makes the copy
+// wait for PV in any case; interleaving then hides that wait behind arithmetic): phase A of tile `it` (dequantise the thread's share of the token row into
 // tensor memory, chunk by chunk, so that QK^T chases the conversion) interleaved with phase B of tile `it - 1` (copy
 // that tile's FP16 values from tensor memory into the V tile as PV of tile `it - 2` releases it). The two phases use
 // different units (ALU + tensor-memory stores versus tensor-memory loads + shared-memory stores), so one instruction
@@ -261,7 +273,7 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
 //     -> store A's panel over it -> store B's panel to the V tile.
 // FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
 template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
-__device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
+__device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
                                              int lane, int quad, int hf) {
   const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
@@ -391,6 +403,146 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   return true;
 }
 
+// One pipeline step of a convert thread, in two parts.
+//   Part B (tile it - 1): copy the thread's FP16 / E4M3 row from tensor memory into the V tile and publish it. It
+//   comes first: it needs nothing from QK^T of tile it - 1, whose last MMAs are still in flight when the step starts,
+//   and it lets PV of tile it - 1 start (and finish) early in the step instead of colliding with the next QK^T tail.
+//   Part A (tile it): dequantise the thread's share of the token row into tensor memory, chunk by chunk, so that QK^T
+//   chases the conversion; the publish of a chunk is deferred until the next chunk's values have been computed, so the
+//   latency of the tensor-memory store hides behind arithmetic.
+// FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
+template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
+__device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
+                                             int lane, int quad, int hf) {
+  const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
+  const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
+  const int half = r >> 6, rr = r & 63;
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
+  constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row: 32 (FP16) or 16 (E4M3)
+  bool ok;
+
+  // ------------------------------------------------------------------------------------------------ part B
+  if (has_b) {
+    constexpr uint32_t VB = DecodeSmem<N, RAW_SLOTS, P8>::VBUFS;
+    const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
+    const uint32_t swz_v = uint32_t(r & 7) << 4;
+    uint32_t hb[2][W];
+    if (!MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * (4 * hf), hb[0]);
+    // the PV that last read this V buffer (tile tb - VB) must have finished
+    ok = tb < VB || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag));
+    if (!__all_sync(~0u, ok)) return false;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int p = g + 4 * hf;  // 64-channel panel; 16-bit mode: V panel p, 8-bit mode: half p % 2 of V panel p / 2
+      ptx::tmem_wait_ld();
+      if (g < 3 && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * (p + 1), hb[(g + 1) & 1]);
+      const uint32_t* v = hb[g & 1];
+      uint8_t* vrow = (P8 ? s.v16[vbuf][p >> 1] : s.v16[vbuf][p]) + r * 128;
+#pragma unroll
+      for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c) {
+        const uint32_t chunk = P8 ? uint32_t(4 * (p & 1) + c) : uint32_t(c);
+        *reinterpret_cast<uint4*>(vrow + ((chunk << 4) ^ swz_v)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      }
+      if (tr) MLA_TRACE_AT(P, 8 + g, it);
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.v_full[vbuf]);  // for tile it - 1
+  }
+  if (!has_a) return true;
+
+  // ------------------------------------------------------------------------------------------------ part A
+  const uint32_t hidx = 2 * it + half;
+  const int slot = hidx % RAW_SLOTS;
+  const uint8_t* raw = s.raw[slot];
+  const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
+  const uint32_t swz = uint32_t(rr & 7) << 4;
+  if (tr) MLA_TRACE_AT(P, 1, it);
+  ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag));
+  if (!__all_sync(~0u, ok)) return false;
+  if (tr) MLA_TRACE_AT(P, 0, it);
+  const bool valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
+  const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);  // the 16 block scales of this half row
+  {  // ---- rope chunk: 32 channels of this thread's half
+    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
+    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
+    // K of the previous tile may be overwritten once its QK^T has finished (the copy above has already read it)
+    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tc_fence_after_sync();
+    const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
+    if constexpr (!P8) {
+      uint32_t h[16];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
+        h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
+      }
+      ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
+    } else {  // the rope bytes are E4M3 already
+      uint32_t h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = valid ? rw[j] : 0u;
+      ptx::tmem_st8(tm_lane + Cols<N, P8>::KROPE + 8 * hf, h);
+    }
+    if (tr) MLA_TRACE_AT(P, 2, it);
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
+    uint32_t h[W];
+    const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
+    const uint32_t c0 = uint32_t(2 * g) << 4;
+    const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
+    const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
+    const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
+    if (g == 3) {  // last read of the raw slot by this thread
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+    }
+    // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s); the 8-bit mode stores (e2m1 x s) / 8 so that the product
+    // (up to 2688) stays inside E4M3's range, and undoes the 8 in the score scale and the output
+    uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
+    if constexpr (P8) s01 = ptx::hmul2(s01, 0x30003000u), s23 = ptx::hmul2(s23, 0x30003000u);  // x 1/8, exact
+    const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
+                            __byte_perm(s23, s23, 0x3232)};
+    const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
+      uint32_t e[4];
+      if (MLA_EXP(P, 8)) {
+        for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = wds[j] + i + sc[0];
+        continue;
+      }
+      ptx::e2m1x8_to_f16x8(wds[j], e);
+      if constexpr (!P8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
+      } else {  // the FP16 product is exact; the only rounding is the conversion to E4M3
+        uint32_t b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc[j >> 1]));
+        h[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
+        h[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
+      }
+    }
+    // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+    if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
+    if (tr) MLA_TRACE_AT(P, 3 + g, it);
+  }
+  ptx::tmem_wait_st();
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
+  if (tr) MLA_TRACE_AT(P, 7, it);
+  return true;
+}
+
 // A warp whose wait gave up does not leave at once: the 256 convert threads meet at a named barrier at the start of
 // every segment, so it carries on (skipping the work) to the next such barrier, where the failure is OR-reduced and
 // all eight warps leave together.
@@ -411,9 +563,15 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const bool full = seg.tok0 + (t + 1) * TILE <= seg.tok_end;
-      const bool ok_s = !pending ? convert_step<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
-                        : full   ? convert_step<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
-                                 : convert_step<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
+      bool ok_s;
+      if constexpr (P8)  // double-buffered V tile: copy first, then convert
+        ok_s = !pending ? convert_step<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
+               : full   ? convert_step<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
+                        : convert_step<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
+      else
+        ok_s = !pending ? convert_step_interleaved<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
+               : full   ? convert_step_interleaved<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
+                        : convert_step_interleaved<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
       pending = true;
       if (!ok_s) {
         dead = true;
@@ -451,9 +609,9 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t par = it & 1, buf = it & 1;
       // softmax of tile it - 2 must have read this S^T buffer
-      if (!__all_sync(~0u, it < 2 || ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag))) return;
+      if (!__all_sync(~0u, it < 2 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
       // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag))) return;
+      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag)))) return;
       if (leader) MLA_TRACE_AT(P, 12, it);
       ptx::tc_fence_after_sync();
       if (leader) {
@@ -465,7 +623,7 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       // group that has given most of its registers away
 #pragma unroll 1
       for (int g = 0; g < 4; ++g) {
-        if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag))) return;
+        if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag)))) return;
         if (leader) MLA_TRACE_AT(P, 13 + g, it);
         ptx::tc_fence_after_sync();
         if (leader) {
@@ -502,8 +660,8 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][0]), 16, 1024);
       const uint64_t v_desc = v_desc0 + (((it % VB) * sizeof(s.v16[0])) >> 4);
       // ---- O^T += V^T . P^T
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag))) return;
+      if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag)))) return;
       if (leader) MLA_TRACE_AT(P, 18, it);
       ptx::tc_fence_after_sync();
       if (leader) {
@@ -557,7 +715,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      bool ok = ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag);
+      bool ok = MLA_WAIT(P, 8 | (0 << 8) | 32, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       float x[N];
@@ -642,7 +800,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
-      if (it >= 2) ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
+      if (it >= 2) MLA_WAIT(P, 9 | (0 << 8) | 32, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 28, it);
       // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
       uint8_t* const p_base = s.p[buf][0] + p_off;
@@ -778,13 +936,13 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
   // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
   if (warp < 4) {
-    ptx::reg_alloc<168>();
+    ptx::reg_alloc<176>();
     run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map);
   } else if (warp < 12) {
-    ptx::reg_alloc<144>();
+    ptx::reg_alloc<136>();
     run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map);
   } else {
-    ptx::reg_dealloc<56>();
+    ptx::reg_dealloc<64>();
     if (warp == 12) run_role<N, RAW_SLOTS, P8, kRoleQk>(s, P, &ckv_map);
     else if (warp == 13) run_role<N, RAW_SLOTS, P8, kRoleProducer>(s, P, &ckv_map);
     else if (warp == 14) run_role<N, RAW_SLOTS, P8, kRolePv>(s, P, &ckv_map);
