@@ -114,6 +114,20 @@ struct Profile {
 };
 thread_local Profile* g_profile = nullptr;
 
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream is still
+// running; it must execute griddepcontrol.wait before touching anything the predecessor writes. Used for the
+// schedule -> decode -> combine chain so that launch latency and prologues overlap the previous kernel.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, mla::Problem* pb) {
@@ -204,13 +218,12 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  decode_kernel(precision)<<<pb.n_cta, mla::kDecodeThreads, decode_smem(precision), st>>>(ckv_map, P);
-  MLA_CUDA(cudaGetLastError());
+  MLA_CUDA(launch_dependent(decode_kernel(precision), dim3(pb.n_cta), dim3(mla::kDecodeThreads), decode_smem(precision), st, ckv_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
-  mla::mla_combine_sched_kernel<<<unsigned(batch) * unsigned(heads), mla::kCombineThreads, 0, st>>>(pb, item_range, lse_part, o_part,
-                                                                                                out, out_f32, lse);
-  MLA_CUDA(cudaGetLastError());
+  MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel, dim3(unsigned(batch) * unsigned(heads)), dim3(mla::kCombineThreads), 0, st,
+                            pb, static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
+                            static_cast<const float*>(o_part), out, out_f32, lse));
   return 0;
 }
 

@@ -928,9 +928,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
+  ptx::grid_launch_dependents();  // the combine kernel may be scheduled; it waits for this grid before reading partials
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
 
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert

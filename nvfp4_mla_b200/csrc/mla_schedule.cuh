@@ -7,6 +7,7 @@
 // the partial of (cta, item w) lives in slot cta + w, which is unique because both indices only grow along the cut.
 #pragma once
 #include "mla_common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace mla {
 
@@ -18,6 +19,7 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
   __shared__ int tiles[kSchedMaxBZ];      // tiles of (b, z), then its exclusive prefix
   __shared__ int warp_sums[kSchedThreads / 32];
   __shared__ int total_bz;
+  ptx::grid_launch_dependents();  // the decode kernel may start its prologue; it waits for this grid before reading
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int BZ = pb.batch * pb.splits;
   if (BZ > kSchedMaxBZ) {
@@ -191,6 +193,7 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
                          const float* __restrict__ o_part, void* out_bf16, float* out_f32, float* lse_out) {
   __shared__ int slots[512];
   __shared__ int n_parts_s;
+  ptx::grid_dependency_wait();  // launched as a programmatic dependent of the decode kernel
   const long long row = blockIdx.x;
   const int b = int(row / pb.heads), h = int(row % pb.heads);
   const int N = pb.heads_per_cta, hg = h / N, n = h % N;

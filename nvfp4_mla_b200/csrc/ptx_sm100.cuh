@@ -23,6 +23,12 @@ __device__ __forceinline__ bool elect_one() {
 template <int REGS> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
 template <int REGS> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
 
+// Programmatic dependent launch: a kernel launched with programmatic stream serialization may begin while its
+// predecessor still runs. grid_dependency_wait() blocks until the predecessor has completed and its writes are visible;
+// grid_launch_dependents() lets the successor begin (it still waits at its own grid_dependency_wait()).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------------------------
