@@ -42,17 +42,24 @@ std::mutex g_mutex;
 DeviceInfo g_devices[kMaxDevices];
 
 using DecodeKernel = void (*)(const CUtensorMap, const mla::DecodeParams);
-constexpr int kHeadsPerCta = 16;
 // staging slots of 64 tokens next to the V tile (one FP16 tile of 128 KB, or two E4M3 tiles of 64 KB)
 constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
-DecodeKernel decode_kernel(int precision) {
-  return precision == NVFP4_MLA_PRECISION_FP8 ? mla::mla_decode_kernel<kHeadsPerCta, kRawSlots8, true>
-                                              : mla::mla_decode_kernel<kHeadsPerCta, kRawSlots16, false>;
+// Heads per CTA (the N of both MMAs). One conversion of a tile serves all of the CTA's heads, so more heads per CTA
+// means less conversion work per head; 32 fit next to the tiles only in the 8-bit mode (tensor memory and shared memory).
+int heads_per_cta(int heads, int precision) { return precision == NVFP4_MLA_PRECISION_FP8 && heads % 32 == 0 ? 32 : 16; }
+DecodeKernel decode_kernel(int precision, int hpc) {
+  if (precision == NVFP4_MLA_PRECISION_FP8)
+    return hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true> : mla::mla_decode_kernel<16, kRawSlots8, true>;
+  return mla::mla_decode_kernel<16, kRawSlots16, false>;
 }
-size_t decode_smem(int precision) {
-  return precision == NVFP4_MLA_PRECISION_FP8 ? mla::decode_smem_bytes<kHeadsPerCta, kRawSlots8, true>()
-                                              : mla::decode_smem_bytes<kHeadsPerCta, kRawSlots16, false>();
+size_t decode_smem(int precision, int hpc) {
+  if (precision == NVFP4_MLA_PRECISION_FP8)
+    return hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>() : mla::decode_smem_bytes<16, kRawSlots8, true>();
+  return mla::decode_smem_bytes<16, kRawSlots16, false>();
 }
+static_assert(mla::decode_smem_bytes<32, kRawSlots8, true>() <= 232448 && mla::decode_smem_bytes<16, kRawSlots8, true>() <= 232448 &&
+                  mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448,
+              "decode kernel exceeds the 227 KB of shared memory a CTA can opt in to");
 
 // Per-device one-time setup (SM count, opt-in shared memory). Must first run outside stream capture.
 int device_info(DeviceInfo** out) {
@@ -67,7 +74,9 @@ int device_info(DeviceInfo** out) {
     MLA_CHECK(major == 10, "nvfp4_mla_b200 needs an sm_100a GPU (B200), found compute capability %d.x", major);
     MLA_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
     for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8})
-      MLA_CUDA(cudaFuncSetAttribute(decode_kernel(prec), cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem(prec))));
+      for (int hpc : {16, 32})
+        MLA_CUDA(cudaFuncSetAttribute(decode_kernel(prec, hpc), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      int(decode_smem(prec, hpc))));
     d.ready = true;
   }
   *out = &d;
@@ -130,14 +139,14 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, mla::Problem* pb) {
+int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, int hpc, mla::Problem* pb) {
   MLA_CHECK(batch >= 0, "batch must be non-negative");
   MLA_CHECK(heads > 0 && heads % 16 == 0, "heads must be a multiple of 16, got %d", heads);
   MLA_CHECK(num_splits >= 0, "num_splits must be non-negative");
   const int splits = num_splits > 0 ? num_splits : 1;
   const long long len = max_kv_len > 1 ? max_kv_len : 1;
   const long long chunk = ((len + splits - 1) / splits + mla::TILE - 1) / mla::TILE * mla::TILE;
-  pb->batch = batch, pb->heads = heads, pb->heads_per_cta = kHeadsPerCta, pb->head_groups = heads / kHeadsPerCta;
+  pb->batch = batch, pb->heads = heads, pb->heads_per_cta = hpc, pb->head_groups = heads / hpc;
   pb->splits = splits, pb->chunk = int(chunk), pb->n_cta = n_cta;
   MLA_CHECK((long long)batch * splits <= mla::kSchedMaxBZ, "batch * num_splits = %lld exceeds %d", (long long)batch * splits,
             mla::kSchedMaxBZ);
@@ -161,9 +170,15 @@ const char* nvfp4_mla_last_error(void) { return g_error; }
 int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
   DeviceInfo* d;
   if (device_info(&d)) return -1;
-  mla::Problem pb;
-  if (problem_of(batch, heads, 1, num_splits, d->sm_count, &pb)) return -1;
-  return int64_t(mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total);
+  // the size covers either precision mode (they may group the heads differently)
+  size_t need = 0;
+  for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8}) {
+    mla::Problem pb;
+    if (problem_of(batch, heads, 1, num_splits, d->sm_count, heads_per_cta(heads, prec), &pb)) return -1;
+    const size_t n = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total;
+    need = n > need ? n : need;
+  }
+  return int64_t(need);
 }
 
 int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
@@ -186,7 +201,8 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   DeviceInfo* d;
   if (device_info(&d)) return 1;
   mla::Problem pb;
-  if (problem_of(batch, heads, max_kv_len, num_splits, d->sm_count, &pb)) return 1;
+  const int hpc = heads_per_cta(heads, precision);
+  if (problem_of(batch, heads, max_kv_len, num_splits, d->sm_count, hpc, &pb)) return 1;
   if (batch == 0) return 0;
   const mla::WsLayout L = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta);
   MLA_CHECK(workspace_bytes >= int64_t(L.total), "workspace too small: %lld bytes given, %lld needed", (long long)workspace_bytes,
@@ -218,7 +234,8 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  MLA_CUDA(launch_dependent(decode_kernel(precision), dim3(pb.n_cta), dim3(mla::kDecodeThreads), decode_smem(precision), st, ckv_map, P));
+  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta), dim3(mla::kDecodeThreads), decode_smem(precision, hpc), st,
+                            ckv_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
   MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel, dim3(unsigned(batch) * unsigned(heads)), dim3(mla::kCombineThreads), 0, st,

@@ -70,6 +70,10 @@ constexpr int kTraceTiles = 64, kTraceEvents = 32;
 #define MLA_EXPERIMENT 0
 #endif
 #define MLA_EXP(P, bit) ((MLA_EXPERIMENT & (bit)) != 0)
+// 16-bit mode: hand the V tile from the convert warps to PV (and back) per 128-channel block instead of per tile
+#ifndef MLA_VBLOCK
+#define MLA_VBLOCK 1
+#endif
 
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
@@ -104,12 +108,16 @@ struct DecodeSmem {
   Seg segs[kSegBatch];
   float qa[4][N], qb[4][N];                         // per-head score scales (latent, rope), ring indexed by segment count
   float red[4][N];                                  // softmax group: per-warp partial reductions
+  float corr[N];                                    // softmax group: per-head rescale factors of the current tile
   unsigned int qamax[N], qamax_pe[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
   uint64_t k_full[5];                               // K chunk in tensor memory: 0..3 = latent panels {g, g+4}, 4 = rope
   uint64_t k_done;                                  // QK^T of the tile has finished reading K and Q^T (one phase per tile)
   uint64_t v_full[2];                               // V buffer b is written (one phase per tile that uses the buffer)
+  // 16-bit mode (single V tile): per 128-channel block mb = panels {mb, mb + 4}, one phase per tile. PV of a tile chases
+  // the copy block by block, and the copy of the next tile chases PV.
+  uint64_t vb_full[4], vb_free[4];
   // S^T and P^T are double buffered; each of these barriers belongs to one buffer and completes once per two tiles, so
   // a waiter that runs up to two tiles ahead or behind can never mistake one phase for another of the same parity.
   uint64_t s_full[2], s_free[2];                    // S^T written by QK^T / read by softmax
@@ -284,6 +292,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
   const uint8_t* raw = s.raw[slot];
   const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
   const uint32_t swz = uint32_t(rr & 7) << 4, swz_v = uint32_t(r & 7) << 4;
+  constexpr bool kVBlock = MLA_VBLOCK && !P8;
   bool ok, valid = true;
   uint4 sf16 = make_uint4(0, 0, 0, 0);
   if (has_a) {
@@ -362,9 +371,17 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       }
       // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
       ptx::tmem_wait_st();
+      if (kVBlock && has_b && g > 0) ptx::fence_proxy_async_smem();  // and the V panel stored one trip ago
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+      if (lane == 0) {
+        ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+        if (kVBlock && has_b && g > 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
+      }
+    } else if (kVBlock && has_b && g > 0) {
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
     }
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
@@ -374,7 +391,10 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     if (has_b) {
       constexpr uint32_t VB = DecodeSmem<N, RAW_SLOTS, P8>::VBUFS;
       const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
-      if (g == 0) {  // the PV that last read this V buffer (tile tb - VB) must have finished: the only wait on PV in the step
+      if (kVBlock) {  // PV of tile tb - 1 must have finished with block g (panels g and g + 4) of the V tile
+        ok = tb < 1 || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag));
+        if (!__all_sync(~0u, ok)) return false;
+      } else if (g == 0) {  // the PV that last read this V buffer (tile tb - VB) must have finished: the only wait on PV in the step
         ok = tb < VB || ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag);
         if (!__all_sync(~0u, ok)) return false;
       }
@@ -398,7 +418,10 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.v_full[(it - 1) % DecodeSmem<N, RAW_SLOTS, P8>::VBUFS]);  // for tile it - 1
+    if (lane == 0) {
+      if (kVBlock) ptx::mbar_arrive(&s.vb_full[3]);
+      else ptx::mbar_arrive(&s.v_full[(it - 1) % DecodeSmem<N, RAW_SLOTS, P8>::VBUFS]);  // for tile it - 1
+    }
   }
   return true;
 }
@@ -580,7 +603,10 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
   }
   // drain: the batch's last tile still has to reach the V tile
-  if (pending && !dead) convert_step<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
+  if (pending && !dead) {
+    if constexpr (P8) convert_step<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
+    else convert_step_interleaved<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -661,12 +687,17 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       const uint64_t v_desc = v_desc0 + (((it % VB) * sizeof(s.v16[0])) >> 4);
       // ---- O^T += V^T . P^T
       if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
-      if (!__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag)))) return;
+      constexpr bool kVBlock = MLA_VBLOCK && !P8;
+      if (!kVBlock && !__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag)))) return;
       if (leader) MLA_TRACE_AT(P, 18, it);
       ptx::tc_fence_after_sync();
-      if (leader) {
 #pragma unroll 1
-        for (int mb = 0; mb < 4; ++mb) {
+      for (int mb = 0; mb < 4; ++mb) {
+        if (kVBlock) {
+          if (!__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.vb_full[mb], par, &s.abort_flag)))) return;
+          ptx::tc_fence_after_sync();
+        }
+        if (leader) {
 #pragma unroll 1
           for (int kh = 0; kh < (MLA_EXP(P, 32) ? 0 : (P8 ? 1 : 2)); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
 #pragma unroll
@@ -680,8 +711,9 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
                                 p_desc + ((kh * N * 128 + ks * 32) >> 4), idesc, (t | kh | ks) != 0);
             }
           }
+          if (kVBlock) ptx::mma_commit(&s.vb_free[mb]);
+          if (mb == 3) ptx::mma_commit(&s.p_free[buf]);
         }
-        ptx::mma_commit(&s.p_free[buf]);
       }
       if (leader) MLA_TRACE_AT(P, 19, it);
     }
@@ -710,8 +742,10 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     float m[N], lsum[N];
 #pragma unroll
     for (int h = 0; h < N; ++h) m[h] = -INFINITY, lsum[h] = 0.f;
+    // per-head score scales: kept in registers for 16 heads, read from shared memory (broadcast) for more
+    constexpr bool kScalesInRegs = N <= 16;
     bool scales_loaded = false;
-    float qa_r[N], qb_r[N];
+    float qa_r[kScalesInRegs ? N : 1], qb_r[kScalesInRegs ? N : 1];
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
@@ -719,9 +753,9 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       float x[N];
-      if (!scales_loaded) {  // written by the convert warps before the segment's first K chunk was published
+      if (kScalesInRegs && !scales_loaded) {  // written by the convert warps before the segment's first K chunk was published
 #pragma unroll
-        for (int h = 0; h < N; ++h) qa_r[h] = s.qa[par_q][h], qb_r[h] = s.qb[par_q][h];
+        for (int h = 0; h < (kScalesInRegs ? N : 0); ++h) qa_r[h] = s.qa[par_q][h], qb_r[h] = s.qb[par_q][h];
         scales_loaded = true;
       }
       if (ok) {
@@ -734,7 +768,9 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = fmaf(__uint_as_float(sp[j]), qb_r[c0 + j], __uint_as_float(sn[j]) * qa_r[c0 + j]);
+            const float qa = kScalesInRegs ? qa_r[kScalesInRegs ? c0 + j : 0] : s.qa[par_q][c0 + j];
+            const float qb = kScalesInRegs ? qb_r[kScalesInRegs ? c0 + j : 0] : s.qb[par_q][c0 + j];
+            const float v = fmaf(__uint_as_float(sp[j]), qb, __uint_as_float(sn[j]) * qa);
             x[c0 + j] = valid ? v : -INFINITY;
           }
         }
@@ -752,29 +788,27 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       if (ptx::bar_red_or(1, 128, need)) {
         if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
         // new running max per head over the 128 token rows
-        float tm_[N];
 #pragma unroll
         for (int h = 0; h < N; ++h) {
           float v = x[h];
 #pragma unroll
           for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(~0u, v, o));
-          tm_[h] = v;
-        }
-        if (lane == 0) {
-#pragma unroll
-          for (int h = 0; h < N; ++h) s.red[warp][h] = tm_[h];
+          if (lane == 0) s.red[warp][h] = v;
         }
         ptx::bar_sync(1, 128);
-        float corr[N];
+        // The correction factors are the same in every thread (the running max is shared by all rows); they are parked
+        // in shared memory (every thread stores the same values and reads back its own store) to keep this rare path
+        // from raising the role's register need.
         bool any_scale = false;
 #pragma unroll
         for (int h = 0; h < N; ++h) {
           const float mx = fmaxf(fmaxf(s.red[0][h], s.red[1][h]), fmaxf(s.red[2][h], s.red[3][h]));
           const float mn = fmaxf(m[h], mx);
-          corr[h] = (m[h] == -INFINITY) ? 0.f : ptx::ex2(m[h] - mn);  // mn = -inf only if m = -inf
-          any_scale |= corr[h] != 1.f;
-          lsum[h] *= corr[h];
+          const float c = (m[h] == -INFINITY) ? 0.f : ptx::ex2(m[h] - mn);  // mn = -inf only if m = -inf
+          any_scale |= c != 1.f;
+          lsum[h] *= c;
           m[h] = mn;
+          s.corr[h] = c;
         }
         // O^T *= corr per head (column): after the previous tile's PV has finished; this tile's PV is not issued
         // before this thread arrives on p_full.
@@ -790,7 +824,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
               ptx::tmem_ld16(tm_lane + Cols<N, P8>::O + mb * N + c0, o);
               ptx::tmem_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr[c0 + j]);
+              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * s.corr[c0 + j]);
               ptx::tmem_st16(tm_lane + Cols<N, P8>::O + mb * N + c0, o);
             }
           }
@@ -916,6 +950,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8);
     ptx::mbar_init(&s.k_done, 1);
     ptx::mbar_init(&s.v_full[0], 8), ptx::mbar_init(&s.v_full[1], 8);
+    for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.vb_full[i], 8), ptx::mbar_init(&s.vb_free[i], 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 4);  // one arrival per softmax warp
       ptx::mbar_init(&s.p_full[i], 4), ptx::mbar_init(&s.p_free[i], 1);
@@ -937,11 +972,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
   // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
+  // The pool is the launch allocation (512 threads x 128): 4 x softmax + 8 x convert + 4 x 64 <= 16 x 128.
+  constexpr int kSoftmaxRegs = N > 16 ? 200 : 176, kConvertRegs = N > 16 ? 120 : 136;
+  static_assert(4 * kSoftmaxRegs + 8 * kConvertRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
-    ptx::reg_alloc<176>();
+    ptx::reg_alloc<kSoftmaxRegs>();
     run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map);
   } else if (warp < 12) {
-    ptx::reg_alloc<136>();
+    if constexpr (kConvertRegs >= 128) ptx::reg_alloc<kConvertRegs>(); else ptx::reg_dealloc<kConvertRegs>();
     run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map);
   } else {
     ptx::reg_dealloc<64>();
