@@ -18,6 +18,7 @@ value is the bytes all ranks streamed divided by the slowest rank's time (weak s
 """
 import argparse
 import ctypes
+import datetime
 import json
 import os
 import pathlib
@@ -37,6 +38,9 @@ WORKLOADS = {
     "h16_b64_16k": (64, 16, 16384, 64, "bf16"),
     "h16_b8_64k": (8, 16, 65536, 64, "bf16"),        # small case for ncu captures (185 MB of KV, still larger than L2)
     "h128_b64_16k": (64, 128, 16384, 64, "bf16"),
+    # BASELINE config 3: ragged lengths drawn uniformly from [1024, 32768] (seeded, per rank), 8-bit mode; tensor-bound
+    "c3_h128_b64_ragged_fp8": (64, 128, (1024, 32768), 64, "fp8"),
+    "h128_b32_16k_fp8": (32, 128, 16384, 64, "fp8"),  # small case for ncu captures of the 128-head shape
     "c4_h128_b2_1m_seq": (2, 128, 1048576, 64, "bf16"),  # BASELINE config 4: sequence-sharded, strong scaling
 }
 SEQUENCE_SHARDED = {"c4_h128_b2_1m_seq"}
@@ -58,17 +62,39 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak(precision):
+    """Dense tensor peak in TFLOP/s for the roofline of the 128-head shapes: the measured cuBLAS bf16 burst figure; the
+    8-bit mode is held against twice that (E4M3 MMAs run at twice the 16-bit rate; no measured fp8 figure exists)."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    bf16, kind = (float(json.loads(p.read_text())["bf16_tflops"]), "measured") if p.exists() else (1590.0, "fallback")
+    return (bf16, f"of {kind} bf16") if precision == "bf16" else (2 * bf16, f"of 2 x {kind} bf16")
+
+
+def request_lengths(kv_len, batch, seed):
+    """kv_len is one length for every request, or (lo, hi) for seeded uniform ragged lengths."""
+    if isinstance(kv_len, tuple):
+        import numpy as np
+        return [int(x) for x in np.random.default_rng(1234 + seed).integers(kv_len[0], kv_len[1] + 1, size=batch)]
+    return [kv_len] * batch
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi.
+
+    The process is started early (nvidia-smi needs a moment before its first sample) and runs until stop(); the
+    benchmark marks the wall-clock window of its timed region and the summary uses the samples inside it. If the
+    region is too short to hold three samples, the window is widened to everything from the first mark to stop()
+    (warm-up, timed and end-to-end loops, all of them under the same load) and the summary says so."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    PERIOD_MS = 50
 
     def __init__(self, index):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.marks = [], None, {}
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.PERIOD_MS)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -79,23 +105,37 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
 
+    def mark(self, name):
+        self.marks[name] = datetime.datetime.now()
+
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        self.mark("stop")
+        time.sleep(2.5 * self.PERIOD_MS / 1e3)  # let the last samples of the window arrive
         self.proc.terminate()
         self.thread.join(timeout=2)
-        clocks, mx, reasons = [], None, set()
+        samples = []
         for r in self.rows:
             try:
-                clocks.append(float(r[0])), (mx := float(r[1]))
+                ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f")
+                samples.append((ts, float(r[1]), float(r[2]), float(r[3]), r[4:8]))
             except (ValueError, IndexError):
                 continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+
+        def inside(a, b):
+            return [x for x in samples if self.marks.get(a) and self.marks.get(b) and self.marks[a] <= x[0] <= self.marks[b]]
+        chosen, window = inside("timed_begin", "timed_end"), "timed region"
+        if len(chosen) < 3:
+            chosen, window = inside("load_begin", "stop"), "warm-up, timed and end-to-end loops (timed region too short)"
+        reasons = set()
+        for x in chosen:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), x[4]):
                 if v == "Active":
                     reasons.add(name)
-        busy = [c for c in clocks if mx and c > 0.5 * mx] or clocks
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        return {"sm_mhz": statistics.median(x[1] for x in chosen) if chosen else None,
+                "sm_max_mhz": chosen[0][2] if chosen else None, "power_w_max": max((x[3] for x in chosen), default=None),
+                "reasons": sorted(reasons), "samples": len(chosen), "window": window}
 
 
 def cpu_reference_sample(cache, n_requests, repeats=1):
@@ -131,7 +171,7 @@ def cpu_reference_sample(cache, n_requests, repeats=1):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS))
@@ -153,7 +193,7 @@ def main():
     config = {"workload": f"{args.workload}: B={B} per GPU, H={H}, kv_len={kv_len}, page_size={ps}, precision={precision}, "
                           f"seeded N(0,1) latent KV quantised to NVFP4 (calibrated global scales), shuffled page table",
               "parallelism": f"batch-sharded dp{world}, no collective", "num_splits": args.num_splits,
-              "l2": "inputs larger than L2 (1.48 GB per GPU), no flush",
+              "l2": None,
               "baseline": "reference SM100 tcgen05 kernel v3, 0.309 ms = 4.77 TB/s (published, B200)"}
 
     if args.impl == "reference":
@@ -162,19 +202,21 @@ def main():
             return
         from nvfp4_mla_b200.testing import SyntheticCache
         n = args.cpu_sample_requests
-        cache = SyntheticCache([kv_len] * n, ps, H, None, None, seed=0, device="cpu")
+        cache = SyntheticCache(request_lengths(kv_len, B, 0)[:n], ps, H, None, None, seed=0, device="cpu")
         for _ in range(min(args.warmup, 1)):
             cpu_reference_sample(cache, 1)
-        times = []
+        times, budget_s = [], 90.0  # the CPU arm stops after about a minute and a half, whatever --steps asks for
         for _ in range(args.steps):
             dt, nbytes, threads = cpu_reference_sample(cache, n)
             times.append(dt)
+            if sum(times) + dt > budget_s:
+                break
         t = sum(times) / len(times)
         val = nbytes / t / 1e12
-        sample = f"{n} of {B} requests per step ({n * kv_len} tokens), numpy port of the reference torch path"
+        sample = f"{n} of {B} requests per step ({nbytes // TOKEN_BYTES} tokens), numpy port of the reference torch path"
         print(json.dumps({
             "impl": "reference", "metric": "nvfp4_mla_decode_kv_bandwidth", "value": val, "unit": "TB/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+            "n_gpus": args.gpus, "steps": len(times), "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config,
             "cpu_baseline": {"value": val, "unit": "TB/s", "cores": threads, "kind": "port", "sample": sample},
@@ -185,6 +227,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    sampler = ClockSampler(local_rank) if rank == 0 else None  # started early: nvidia-smi takes a while to produce samples
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -204,8 +247,8 @@ def main():
         config["parallelism"] = f"sequence-sharded over {world} GPU(s): local split-KV decode, all-gather of (o, lse), merge"
         kv_len_local = local_len
     else:
-        cache = SyntheticCache([kv_len] * B, ps, H, None, None, seed=rank, device=dev)
-        kv_len_local = kv_len
+        cache = SyntheticCache(request_lengths(kv_len, B, rank), ps, H, None, None, seed=rank, device=dev)
+        kv_len_local = kv_len[1] if isinstance(kv_len, tuple) else kv_len
     kv_bytes = cache.kv_bytes
     dargs = cache.args(SM_SCALE)
     kw = dict(max_kv_len=kv_len_local, num_splits=args.num_splits, precision=precision)
@@ -229,24 +272,44 @@ def main():
         return float(t.item())
 
     # ---- device-resident timing -------------------------------------------------------------------------------
+    if sampler:
+        sampler.mark("load_begin")
     for _ in range(args.warmup):
         out = decode_fn(*dargs, **kw)
     sync_all()
     lib = _lib.load()
     _lib.check(lib.nvfp4_mla_profile_begin(args.steps))
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.mark("timed_begin")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        out = decode_fn(*dargs, **kw)
-    ev1.record()
-    sync_all()
-    clocks = sampler.stop() if sampler else None
+    # Inputs larger than twice the L2 evict themselves between steps; smaller workloads get an L2 flush (a 256 MB
+    # write) before every step, and each step is then timed with its own event pair so that the flush is not counted.
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if kv_bytes < (256 << 20) else None
+    config["l2"] = ("inputs larger than L2 (126 MB), no flush" if flush is None else
+                    "256 MB written between timed steps (inputs smaller than 2 x L2); each step timed by its own event pair")
+    if flush is None:
+        ev0.record()
+        for _ in range(args.steps):
+            out = decode_fn(*dargs, **kw)
+        ev1.record()
+        sync_all()
+        total_ms = ev0.elapsed_time(ev1)
+    else:
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in pairs:
+            flush.zero_()
+            a.record()
+            out = decode_fn(*dargs, **kw)
+            b.record()
+        sync_all()
+        total_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    if sampler:
+        sampler.mark("timed_end")
     kern_ms = (ctypes.c_float * args.steps)()
     n_k = lib.nvfp4_mla_profile_end(kern_ms, args.steps)
     if n_k < 0:
         raise RuntimeError(lib.nvfp4_mla_last_error().decode())
-    ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    ms_step = max_over_ranks(total_ms / args.steps)
     kernel_ms = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
     kv_bytes_all = kv_bytes
     if world > 1:
@@ -276,12 +339,23 @@ def main():
     for _ in range(args.warmup):
         e2e_step()
     sync_all()
-    ev0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    ev1.record()
-    sync_all()
-    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    if flush is None:
+        ev0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        ev1.record()
+        sync_all()
+        total_ms = ev0.elapsed_time(ev1)
+    else:
+        for a, b in pairs:
+            flush.zero_()
+            a.record()
+            e2e_step()
+            b.record()
+        sync_all()
+        total_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    e2e_ms = max_over_ranks(total_ms / args.steps)
+    clocks = sampler.stop() if sampler else None
 
     if rank != 0:
         if world > 1:
@@ -290,6 +364,18 @@ def main():
 
     peak, peak_kind = measured_peak()
     achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
+    tokens = kv_bytes // TOKEN_BYTES
+    if H >= 128:  # 2176 flop per token and head: the tensor pipe is the bound, the HBM figure becomes secondary
+        tpeak, tkind = measured_tensor_peak(precision)
+        tflops = 2176.0 * H * tokens / (kernel_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": tflops, "peak": tpeak, "unit": "TFLOP/s", "frac": tflops / tpeak,
+                    "peak_kind": tkind, "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
+                    "algorithmic_flops_per_launch": 2176.0 * H * tokens, "hbm_gbs": achieved, "traffic": None}
+    else:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "peak_kind": f"of {peak_kind}", "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
+                    "algorithmic_bytes_per_launch": kv_bytes,
+                    "traffic": (NCU_TRAFFIC_BYTES_PER_TOKEN * tokens) if NCU_TRAFFIC_BYTES_PER_TOKEN else None}
     value = kv_bytes_all / (ms_step * 1e-3) / 1e12
     line = {
         "metric": "nvfp4_mla_decode_kv_bandwidth", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps,
@@ -301,10 +387,7 @@ def main():
         "e2e": {"value": kv_bytes_all / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": (KERNELS_PER_DECODE + (1 if seq and world > 1 else 0)) * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
-                     "algorithmic_bytes_per_launch": kv_bytes,
-                     "traffic": (NCU_TRAFFIC_BYTES_PER_TOKEN * kv_bytes // TOKEN_BYTES) if NCU_TRAFFIC_BYTES_PER_TOKEN else None},
+        "roofline": roofline,
         "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -312,7 +395,7 @@ def main():
         dt, nbytes, threads = cpu_reference_sample(cache, n)
         line["cpu_baseline"] = {"value": nbytes / dt / 1e12, "unit": "TB/s", "cores": threads, "kind": "port",
                                 "seconds": dt,
-                                "sample": f"{n} of {B} requests ({n * kv_len} tokens), numpy port of the reference torch path"}
+                                "sample": f"{n} of {B} requests ({nbytes // TOKEN_BYTES} tokens), numpy port of the reference torch path"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
