@@ -122,6 +122,21 @@ NVFP4_MLA_API int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* 
                          int64_t num_tokens, float ckv_scale, float kpe_scale, int out_bf16, void* ckv_out,
                          void* kpe_out, void* stream);
 
+/* Cache writer: quantises `nnz` new tokens (ckv [nnz, 512] and kpe [nnz, 64], bfloat16) and appends them to the paged
+ * cache. Token i belongs to request batch_indices[i] at position positions[i]; its slot is page
+ * kv_indices[kv_indptr[b] + position / page_size], row position % page_size. Per 16 latent channels the block scale is
+ * e4m3(amax / 6 / ckv_scale), the codes are the nearest E2M1 of x / (scale * ckv_scale) (ties to even, saturating),
+ * packed low nibble = even channel; rope is e4m3(kpe / kpe_scale). `status` (optional device word) is set to 1 if a
+ * token names a request, position or page outside the tables; such a token is skipped.
+ * The reference has no writer of its own: it calls FlashInfer's nvfp4_quantize_append_paged_mla_kv_cache with these
+ * arguments (nvfp4_mla/testing.py:51-53, README.md:77-79); this entry point takes the same tables so that it can stand
+ * in for that call. */
+NVFP4_MLA_API int nvfp4_mla_quantize_append(const void* ckv, const void* kpe, const int32_t* batch_indices,
+                              const int32_t* positions, int64_t nnz, uint8_t* ckv_cache, uint8_t* ckv_sf_cache,
+                              uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* kv_indices,
+                              const int32_t* kv_indptr, int batch, float ckv_scale, float kpe_scale, int32_t* status,
+                              void* stream);
+
 /* Log-sum-exp merge of `parts` partial results: o_part [parts, rows, 512] float (each normalised by its own
  * softmax sum), lse_part [parts, rows] float in log2 units (-inf = empty partial, weight 0). Any of out
  * (bfloat16 [rows, 512]), out_f32 (float [rows, 512]) and lse (float [rows]) may be NULL.

@@ -8,7 +8,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["decode", "dequantize", "decode_partial", "combine", "workspace_status"]
+__all__ = ["decode", "dequantize", "decode_partial", "combine", "workspace_status", "quantize_append_paged_mla_kv_cache",
+           "get_batch_indices_positions"]
 __version__ = "0.1.0"
 
 CKV, KPE = 512, 64
@@ -184,6 +185,50 @@ def dequantize(ckv_cache, ckv_sf_cache, kpe_cache, ckv_scale=1.0, kpe_scale=1.0,
                                             float(ckv_scale), float(kpe_scale), int(dtype == torch.bfloat16),
                                             _ptr(ckv), _ptr(kpe), torch.cuda.current_stream(dev).cuda_stream))
     return ckv, kpe
+
+
+def get_batch_indices_positions(append_indptr, seq_lens, nnz):
+    """``(batch_indices [nnz], positions [nnz])`` int32 of appended tokens, FlashInfer's helper of the same name
+    (used by the reference at ``nvfp4_mla/testing.py:36``): request ``b`` appends tokens
+    ``append_indptr[b] .. append_indptr[b + 1]``, which become the last positions of its ``seq_lens[b]`` tokens."""
+    append_indptr, seq_lens = append_indptr.to(torch.int64), seq_lens.to(torch.int64)
+    counts = append_indptr[1:] - append_indptr[:-1]
+    bi = torch.repeat_interleave(torch.arange(counts.numel(), device=counts.device), counts, output_size=nnz)
+    pos = torch.arange(nnz, device=counts.device) - append_indptr[:-1][bi] + (seq_lens - counts)[bi]
+    return bi.to(torch.int32), pos.to(torch.int32)
+
+
+def quantize_append_paged_mla_kv_cache(ckv, kpe, batch_indices, positions, ckv_cache, ckv_sf_cache, kpe_cache,
+                                       kv_indices, kv_indptr, kv_last_page_len=None, ckv_scale=1.0, kpe_scale=1.0,
+                                       check=False):
+    """Quantises new tokens to NVFP4 / E4M3 and writes them into the paged cache, in place.
+
+    Same arguments as FlashInfer's ``nvfp4_quantize_append_paged_mla_kv_cache``, the writer the reference uses
+    (``nvfp4_mla/testing.py:51-53``): ``ckv [nnz, 512]`` and ``kpe [nnz, 64]`` bfloat16, ``batch_indices`` /
+    ``positions`` ``[nnz]`` int32, the three cache tensors, the page list ``kv_indices`` with ``kv_indptr [B + 1]``;
+    ``kv_last_page_len`` is accepted and not needed. ``check=True`` synchronises and raises if a token pointed
+    outside the tables (such tokens are skipped)."""
+    _check_cache(ckv_cache, ckv_sf_cache, kpe_cache)
+    nnz = ckv.shape[0]
+    if ckv.dtype != torch.bfloat16 or kpe.dtype != torch.bfloat16:
+        raise RuntimeError("ckv and kpe must be bfloat16")
+    if tuple(ckv.shape) != (nnz, CKV) or tuple(kpe.shape) != (nnz, KPE) or not (ckv.is_contiguous() and kpe.is_contiguous()):
+        raise RuntimeError("ckv must be a contiguous [nnz, 512] and kpe a contiguous [nnz, 64] tensor")
+    for name, t, n in (("batch_indices", batch_indices, nnz), ("positions", positions, nnz), ("kv_indices", kv_indices, None),
+                       ("kv_indptr", kv_indptr, None)):
+        if t.dtype != torch.int32 or t.dim() != 1 or not t.is_contiguous() or (n is not None and t.numel() != n):
+            raise RuntimeError(f"{name} must be a contiguous 1-D int32 tensor" + (f" of {n} elements" if n is not None else ""))
+    P, ps = ckv_cache.shape[:2]
+    dev = ckv_cache.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if check else None
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        _lib.check(lib.nvfp4_mla_quantize_append(
+            _ptr(ckv), _ptr(kpe), _ptr(batch_indices), _ptr(positions), nnz, _ptr(ckv_cache), _ptr(ckv_sf_cache),
+            _ptr(kpe_cache), P, ps, _ptr(kv_indices), _ptr(kv_indptr), kv_indptr.numel() - 1, float(ckv_scale),
+            float(kpe_scale), _ptr(status) if check else None, torch.cuda.current_stream(dev).cuda_stream))
+    if check and int(status.item()) != 0:
+        raise RuntimeError("quantize_append: a token named a request, position or page outside the tables")
 
 
 def workspace_status(device=None):

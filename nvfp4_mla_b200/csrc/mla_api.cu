@@ -10,6 +10,7 @@
 #include "mla_common.cuh"
 #include "mla_decode_sm100.cuh"
 #include "mla_dequant.cuh"
+#include "mla_quantize.cuh"
 #include "mla_schedule.cuh"
 
 namespace {
@@ -363,6 +364,34 @@ int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache, 
     mla::mla_dequant_kernel<float><<<unsigned(blocks), mla::kDequantThreads, 0, st>>>(
         ckv_cache, ckv_sf_cache, kpe_cache, ckv_scale, kpe_scale, static_cast<float*>(ckv_out), static_cast<float*>(kpe_out),
         num_tokens);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_mla_quantize_append(const void* ckv, const void* kpe, const int32_t* batch_indices, const int32_t* positions,
+                              int64_t nnz, uint8_t* ckv_cache, uint8_t* ckv_sf_cache, uint8_t* kpe_cache, int64_t num_pages,
+                              int page_size, const int32_t* kv_indices, const int32_t* kv_indptr, int batch, float ckv_scale,
+                              float kpe_scale, int32_t* status, void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(nnz >= 0 && batch >= 0, "nnz and batch must be non-negative");
+  MLA_CHECK(page_size > 0 && (page_size & (page_size - 1)) == 0, "page_size must be a power of two, got %d", page_size);
+  MLA_CHECK(num_pages > 0 && num_pages * page_size < (int64_t(1) << 31), "num_pages * page_size must be in [1, 2^31)");
+  MLA_CHECK(ckv_scale > 0.f && kpe_scale > 0.f, "ckv_scale and kpe_scale must be positive");
+  if (nnz == 0) return 0;
+  MLA_CHECK(ckv && kpe && batch_indices && positions && ckv_cache && ckv_sf_cache && kpe_cache && kv_indices && kv_indptr,
+            "null pointer argument");
+  MLA_CHECK(aligned(ckv, 16) && aligned(kpe, 4) && aligned(ckv_cache, 8) && aligned(kpe_cache, 2),
+            "ckv must be 16-byte, kpe 4-byte, ckv_cache 8-byte and kpe_cache 2-byte aligned");
+  DeviceInfo* d;
+  if (device_info(&d)) return 1;
+  const long long warps_per_block = mla::kQuantThreads / 32;
+  long long blocks = (nnz + warps_per_block - 1) / warps_per_block;
+  const long long cap = (long long)d->sm_count * 32;  // grid-stride beyond 32 CTAs per SM
+  if (blocks > cap) blocks = cap;
+  mla::mla_quantize_append_kernel<<<unsigned(blocks), mla::kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), batch_indices, positions, nnz, ckv_cache,
+      ckv_sf_cache, kpe_cache, num_pages, __builtin_ctz(unsigned(page_size)), kv_indices, kv_indptr, batch, ckv_scale, kpe_scale,
+      status);
   MLA_CUDA(cudaGetLastError());
   return 0;
 }
