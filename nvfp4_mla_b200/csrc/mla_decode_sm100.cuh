@@ -70,10 +70,6 @@ constexpr int kTraceTiles = 64, kTraceEvents = 32;
 #define MLA_EXPERIMENT 0
 #endif
 #define MLA_EXP(P, bit) ((MLA_EXPERIMENT & (bit)) != 0)
-// 16-bit mode: hand the V tile from the convert warps to PV (and back) per 128-channel block instead of per tile
-#ifndef MLA_VBLOCK
-#define MLA_VBLOCK 1
-#endif
 
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
@@ -271,18 +267,21 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
   ptx::fence_proxy_async_smem();
 }
 
-// One pipeline step of a convert thread, interleaved form (used by the 16-bit mode, whose single V tile makes the copy
-// wait for PV in any case; interleaving then hides that wait behind arithmetic): phase A of tile `it` (dequantise the thread's share of the token row into
-// tensor memory, chunk by chunk, so that QK^T chases the conversion) interleaved with phase B of tile `it - 1` (copy
-// that tile's FP16 values from tensor memory into the V tile as PV of tile `it - 2` releases it). The two phases use
-// different units (ALU + tensor-memory stores versus tensor-memory loads + shared-memory stores), so one instruction
-// stream keeps both busy. Per 64-channel panel p of this thread:
-//     load B's panel from tensor memory -> compute A's panel -> publish A's previous chunk -> (B's load has landed)
-//     -> store A's panel over it -> store B's panel to the V tile.
+// One pipeline step of a convert thread, interleaved form (16-bit mode, whose single V tile makes the copy wait for PV
+// in any case; interleaving hides that wait behind arithmetic): phase A of tile `it` (dequantise the thread's share of
+// the token row into tensor memory, chunk by chunk, so that QK^T chases the conversion) interleaved with phase B of
+// tile `it - 1` (copy that tile's FP16 values from tensor memory into the V tile, block by block, as PV of tile
+// `it - 2` releases it; PV of tile `it - 1` chases the copy). Per 64-channel panel g of this thread:
+//     load A's packed words -> store B's previous panel to the V tile -> start loading B's panel from tensor memory
+//     -> compute A's panel -> publish A's previous chunk and B's previous panel -> (B's load has landed)
+//     -> store A's panel over it.
+// The shared-memory loads come before the V stores because the load/store unit works in order: a load issued behind
+// the eight 16-byte stores would hold the arithmetic until they have drained; this way the arithmetic overlaps the drain.
 // FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
 template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
 __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
                                              int lane, int quad, int hf) {
+  static_assert(!P8, "the 8-bit mode uses convert_step");
   const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
@@ -292,12 +291,12 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
   const uint8_t* raw = s.raw[slot];
   const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
   const uint32_t swz = uint32_t(rr & 7) << 4, swz_v = uint32_t(r & 7) << 4;
-  constexpr bool kVBlock = MLA_VBLOCK && !P8;
+  constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row
   bool ok, valid = true;
   uint4 sf16 = make_uint4(0, 0, 0, 0);
   if (has_a) {
     if (tr) MLA_TRACE_AT(P, 1, it);
-    ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
+    ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
     if (tr) MLA_TRACE_AT(P, 0, it);
     valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
@@ -305,108 +304,95 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     // ---- rope chunk: 32 channels of this thread's half
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
-    // K of the previous tile may be overwritten once its QK^T has finished. This is the only wait on QK^T in the step:
-    // what follows is straight-line code, so the compiler can overlap one panel's arithmetic with another's stores.
-    ok = it == 0 || ptx::mbar_wait(&s.k_done, prev, &s.abort_flag);
+    // K of the previous tile may be overwritten once its QK^T has finished: the only wait on QK^T in the step
+    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
-    if constexpr (!P8) {
-      uint32_t h[16];
+    uint32_t h[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
-        h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
-      }
-      ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
-    } else {  // the rope bytes are E4M3 already
-      uint32_t h[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] = valid ? rw[j] : 0u;
-      ptx::tmem_st8(tm_lane + Cols<N, P8>::KROPE + 8 * hf, h);
+    for (int j = 0; j < 8; ++j) {
+      h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
+      h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
     }
+    ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
     if (tr) MLA_TRACE_AT(P, 2, it);
   }
+  uint32_t hb[W];  // a panel of tile it - 1 on its way from tensor memory to the V tile
+  // stores panel g of tile it - 1 (in hb) to the V tile, once PV of tile it - 2 has finished with that 128-channel block
+  auto store_v = [&](int g) -> bool {
+    const uint32_t tb = it - 1;
+    const bool okv = tb < 1 || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag));
+    if (!__all_sync(~0u, okv)) return false;
+    uint8_t* vrow = s.v16[0][g + 4 * hf] + r * 128;
+#pragma unroll
+    for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c)
+      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
+    if (tr) MLA_TRACE_AT(P, 8 + g, it);
+    return true;
+  };
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
-    constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row: 32 (FP16) or 16 (E4M3)
-    uint32_t hb[W], h[W];
-    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);  // tile it - 1, on its way to the V tile
+    uint32_t h[W / 2];         // half a panel (32 channels) at a time
+    uint32_t wds[8] = {}, sc[4] = {};
     if (has_a) {
       const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
       const uint32_t c0 = uint32_t(2 * g) << 4;
       const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
       const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
-      const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
+      wds[0] = n0.x, wds[1] = n0.y, wds[2] = n0.z, wds[3] = n0.w, wds[4] = n1.x, wds[5] = n1.y, wds[6] = n1.z, wds[7] = n1.w;
       if (g == 3) {  // last read of the raw slot by this thread
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
       }
-      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s); the 8-bit mode stores (e2m1 x s) / 8 so that the product
-      // (up to 2688) stays inside E4M3's range, and undoes the 8 in the score scale and the output
-      uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
-      if constexpr (P8) s01 = ptx::hmul2(s01, 0x30003000u), s23 = ptx::hmul2(s23, 0x30003000u);  // x 1/8, exact
-      const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010),
-                              __byte_perm(s23, s23, 0x3232)};
-      const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+    }
+    if (has_b && g > 0 && !store_v(g - 1)) return false;
+    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);
+    auto convert_half = [&](int j0) {  // words j0 .. j0 + 3 of the panel -> h
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
+      for (int j = 0; j < 4; ++j) {  // word j0 + j = channels [8 (j0 + j), + 8) of the panel, scale block (j0 + j) / 2
         uint32_t e[4];
         if (MLA_EXP(P, 8)) {
-          for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = wds[j] + i + sc[0];
+          for (int i = 0; i < 4; ++i) h[4 * j + i] = wds[j0 + j] + i + sc[0];
           continue;
         }
-        ptx::e2m1x8_to_f16x8(wds[j], e);
-        if constexpr (!P8) {
+        ptx::e2m1x8_to_f16x8(wds[j0 + j], e);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
-        } else {  // the FP16 product is exact; the only rounding is the conversion to E4M3
-          uint32_t b[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc[j >> 1]));
-          h[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
-          h[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
-        }
+        for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[(j0 + j) >> 1]) : 0u;
       }
-      // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
+    };
+    if (has_a) {
+      const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
+      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
+      const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
+      sc[0] = __byte_perm(s01, s01, 0x1010), sc[1] = __byte_perm(s01, s01, 0x3232);
+      sc[2] = __byte_perm(s23, s23, 0x1010), sc[3] = __byte_perm(s23, s23, 0x3232);
+      convert_half(0);
+      // publish the previous chunk (rope for g = 0), whose tensor-memory store has been in flight during the arithmetic
+      // above, and the V panel stored at the top of this trip
       ptx::tmem_wait_st();
-      if (kVBlock && has_b && g > 0) ptx::fence_proxy_async_smem();  // and the V panel stored one trip ago
+      if (has_b && g > 0) ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
         ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
-        if (kVBlock && has_b && g > 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
+        if (has_b && g > 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
       }
-    } else if (kVBlock && has_b && g > 0) {
+    } else if (has_b && g > 0) {
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
     }
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
-      if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
+      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::K + W * p, h);
+      convert_half(4);
+      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::K + W * p + W / 2, h);
       if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
-    if (has_b) {
-      constexpr uint32_t VB = DecodeSmem<N, RAW_SLOTS, P8>::VBUFS;
-      const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
-      if (kVBlock) {  // PV of tile tb - 1 must have finished with block g (panels g and g + 4) of the V tile
-        ok = tb < 1 || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag));
-        if (!__all_sync(~0u, ok)) return false;
-      } else if (g == 0) {  // the PV that last read this V buffer (tile tb - VB) must have finished: the only wait on PV in the step
-        ok = tb < VB || ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag);
-        if (!__all_sync(~0u, ok)) return false;
-      }
-      uint8_t* vrow = (P8 ? s.v16[vbuf][p >> 1] : s.v16[vbuf][p]) + r * 128;
-#pragma unroll
-      for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c) {
-        const uint32_t chunk = P8 ? uint32_t(4 * (p & 1) + c) : uint32_t(c);
-        *reinterpret_cast<uint4*>(vrow + ((chunk << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
-      }
-      if (tr) MLA_TRACE_AT(P, 8 + g, it);
-    }
   }
+  if (has_b && !store_v(3)) return false;
   if (has_a) {
     ptx::tmem_wait_st();
     ptx::tc_fence_before_sync();
@@ -418,10 +404,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) {
-      if (kVBlock) ptx::mbar_arrive(&s.vb_full[3]);
-      else ptx::mbar_arrive(&s.v_full[(it - 1) % DecodeSmem<N, RAW_SLOTS, P8>::VBUFS]);  // for tile it - 1
-    }
+    if (lane == 0) ptx::mbar_arrive(&s.vb_full[3]);
   }
   return true;
 }
@@ -687,7 +670,7 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       const uint64_t v_desc = v_desc0 + (((it % VB) * sizeof(s.v16[0])) >> 4);
       // ---- O^T += V^T . P^T
       if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
-      constexpr bool kVBlock = MLA_VBLOCK && !P8;
+      constexpr bool kVBlock = !P8;  // 16-bit mode: the single V tile is handed over per 128-channel block
       if (!kVBlock && !__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag)))) return;
       if (leader) MLA_TRACE_AT(P, 18, it);
       ptx::tc_fence_after_sync();
