@@ -42,7 +42,7 @@ struct DeviceInfo {
 std::mutex g_mutex;
 DeviceInfo g_devices[kMaxDevices];
 
-using DecodeKernel = void (*)(const CUtensorMap, const mla::DecodeParams);
+using DecodeKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const mla::DecodeParams);
 // staging slots of 64 tokens next to the V tile (one FP16 tile of 128 KB, or two E4M3 tiles of 64 KB)
 constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
 // Heads per CTA (the N of both MMAs). One conversion of a tile serves all of the CTA's heads, so more heads per CTA
@@ -103,15 +103,18 @@ int encode_fn(EncodeTiledFn* out) {
 
 // ckv_cache as a 2-D byte tensor [num_pages * page_size, 256]; a box is min(page_size, 64) token rows by 128 bytes,
 // written to shared memory with the 128-byte swizzle that makes thread-per-token reads conflict free.
-int make_ckv_map(const uint8_t* ckv, int64_t rows, int page_size, CUtensorMap* map) {
+// 2-D byte map over one of the cache tensors seen as [rows = pages * page_size, row_bytes]; a box is `box_bytes` of up
+// to 64 rows (one staging slot, or one page if pages are smaller), written to shared memory with the given swizzle.
+int make_row_map(const uint8_t* base, int64_t rows, int row_bytes, int box_bytes, int page_size, CUtensorMapSwizzle swizzle,
+                 CUtensorMap* map) {
   EncodeTiledFn encode;
   if (encode_fn(&encode)) return 1;
-  const cuuint64_t dims[2] = {256, cuuint64_t(rows)};
-  const cuuint64_t strides[1] = {256};
-  const cuuint32_t box[2] = {128, cuuint32_t(page_size < mla::HALF ? page_size : mla::HALF)};
+  const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+  const cuuint32_t box[2] = {cuuint32_t(box_bytes), cuuint32_t(page_size < mla::HALF ? page_size : mla::HALF)};
   const cuuint32_t elem_strides[2] = {1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(ckv), dims, strides, box, elem_strides,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MLA_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
   return 0;
@@ -209,8 +212,10 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   MLA_CHECK(workspace_bytes >= int64_t(L.total), "workspace too small: %lld bytes given, %lld needed", (long long)workspace_bytes,
             (long long)L.total);
 
-  CUtensorMap ckv_map;
-  if (make_ckv_map(ckv_cache, num_pages * page_size, page_size, &ckv_map)) return 1;
+  CUtensorMap ckv_map, sf_map, kpe_map;
+  if (make_row_map(ckv_cache, num_pages * page_size, 256, 128, page_size, CU_TENSOR_MAP_SWIZZLE_128B, &ckv_map)) return 1;
+  if (make_row_map(ckv_sf_cache, num_pages * page_size, 32, 32, page_size, CU_TENSOR_MAP_SWIZZLE_32B, &sf_map)) return 1;
+  if (make_row_map(kpe_cache, num_pages * page_size, 64, 64, page_size, CU_TENSOR_MAP_SWIZZLE_64B, &kpe_map)) return 1;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* header = reinterpret_cast<int*>(ws + L.header);
@@ -228,6 +233,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
   P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
   P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads;
+  P.sf_swz_mask = page_size >= mla::HALF ? 1u : 0u, P.kpe_swz_mask = page_size >= mla::HALF ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
 #ifdef MLA_TRACE
@@ -236,7 +242,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
   MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta), dim3(mla::kDecodeThreads), decode_smem(precision, hpc), st,
-                            ckv_map, P));
+                            ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
   MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel, dim3(unsigned(batch) * unsigned(heads)), dim3(mla::kCombineThreads), 0, st,

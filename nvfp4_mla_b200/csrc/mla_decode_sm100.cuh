@@ -79,6 +79,11 @@ struct DecodeParams {
   const int* page_table;
   long long pt_stride;
   int page_shift;  // log2(page_size)
+  // Pages of at least a staging slot (64 tokens) arrive through swizzled tensor maps: the 32-byte scale rows with the
+  // 32-byte swizzle (16-byte chunk ^= row / 4 % 2), the 64-byte rope rows with the 64-byte swizzle (chunk ^= row / 2 % 4),
+  // so that 32 threads reading the same chunk of 32 consecutive rows touch every bank once. Smaller pages arrive
+  // through linear bulk copies (a box of fewer than 128 bytes cannot be a TMA tile destination): masks 0.
+  uint32_t sf_swz_mask, kpe_swz_mask;
   int heads;
   float sm_scale_log2, ckv_scale, kpe_scale;
   const int2* cta_range;
@@ -138,7 +143,7 @@ template <int N, bool P8> struct Cols {
 // ---------------------------------------------------------------------------------------------------------------
 template <int N, int RAW_SLOTS, bool P8>
 __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
-                                              int n_segs, uint32_t& hcount) {
+                                              const CUtensorMap* sf_map, const CUtensorMap* kpe_map, int n_segs, uint32_t& hcount) {
   const int lane = ptx::lane_id();
   const int ps = 1 << P.page_shift;
   for (int si = 0; si < n_segs; ++si) {
@@ -166,8 +171,8 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, c
           ptx::mbar_arrive_expect_tx(bar, HALF * TOKEN_BYTES);
           ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kRawCkvHi, ckv_map, 128, row, bar);
-          ptx::bulk_load(dst + kRawSf, P.sf + (long long)row * 32, HALF * 32, bar);
-          ptx::bulk_load(dst + kRawKpe, P.kpe + (long long)row * 64, HALF * 64, bar);
+          ptx::tma_load_2d(dst + kRawSf, sf_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kRawKpe, kpe_map, 0, row, bar);
           // L2 prefetch a few slots ahead (the ring itself is too shallow to cover HBM latency)
           const int tok_pf = tok + 6 * HALF;
           if (tok_pf < seg.tok_end) {
@@ -175,8 +180,8 @@ __device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, c
             const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
             ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
             ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
-            ptx::bulk_prefetch_l2(P.sf + (long long)row2 * 32, HALF * 32);
-            ptx::bulk_prefetch_l2(P.kpe + (long long)row2 * 64, HALF * 64);
+            ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
           }
         }
       } else {
@@ -300,10 +305,11 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     if (!__all_sync(~0u, ok)) return false;
     if (tr) MLA_TRACE_AT(P, 0, it);
     valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
-    sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);  // the 16 block scales of this half row
+    sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((uint32_t(hf) ^ ((rr >> 2) & P.sf_swz_mask)) << 4));  // the 16 block scales of this half row
     // ---- rope chunk: 32 channels of this thread's half
-    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
-    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
+    const uint32_t kswz = (rr >> 1) & P.kpe_swz_mask;
+    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
+    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
     // K of the previous tile may be overwritten once its QK^T has finished: the only wait on QK^T in the step
     ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
@@ -469,10 +475,11 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   if (!__all_sync(~0u, ok)) return false;
   if (tr) MLA_TRACE_AT(P, 0, it);
   const bool valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
-  const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + 16 * hf);  // the 16 block scales of this half row
+  const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((uint32_t(hf) ^ ((rr >> 2) & P.sf_swz_mask)) << 4));  // the 16 block scales of this half row
   {  // ---- rope chunk: 32 channels of this thread's half
-    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf);
-    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + 32 * hf + 16);
+    const uint32_t kswz = (rr >> 1) & P.kpe_swz_mask;
+    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
+    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
     // K of the previous tile may be overwritten once its QK^T has finished (the copy above has already read it)
     ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
@@ -896,7 +903,8 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 enum Role { kRoleSoftmax, kRoleConvert, kRoleQk, kRoleProducer, kRolePv, kRoleIdle };
 
 template <int N, int RAW_SLOTS, bool P8, int ROLE>
-__device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map) {
+__device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+                                         const CUtensorMap* sf_map, const CUtensorMap* kpe_map) {
   const int2 range = P.cta_range[blockIdx.x];
   uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
   for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
@@ -910,7 +918,7 @@ __device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const 
     if (ROLE == kRoleSoftmax) softmax_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
     if (ROLE == kRoleConvert) convert_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
     if (ROLE == kRoleQk) qk_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
-    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS, P8>(s, P, ckv_map, n_segs, hcount);
+    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS, P8>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
     if (ROLE == kRolePv) pv_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
     __syncthreads();
     if (s.abort_flag) break;
@@ -922,7 +930,8 @@ __device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const 
 // ---------------------------------------------------------------------------------------------------------------
 template <int N, int RAW_SLOTS, bool P8>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
-mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParams P) {
+mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_constant__ CUtensorMap sf_map,
+                  const __grid_constant__ CUtensorMap kpe_map, const DecodeParams P) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = DecodeSmem<N, RAW_SLOTS, P8>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -940,7 +949,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
     }
     s.abort_flag = 0;
     ptx::fence_mbar_init();
-    ptx::prefetch_tensormap(&ckv_map);
+    ptx::prefetch_tensormap(&ckv_map), ptx::prefetch_tensormap(&sf_map), ptx::prefetch_tensormap(&kpe_map);
   }
   if (warp == 12) {
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
@@ -956,20 +965,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const DecodeParam
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
   // warp groups. Registers are granted per warp group (4 warps): 0-3 softmax, 4-7 and 8-11 convert, 12-15 the rest.
   // The pool is the launch allocation (512 threads x 128): 4 x softmax + 8 x convert + 4 x 64 <= 16 x 128.
-  constexpr int kSoftmaxRegs = N > 16 ? 200 : 176, kConvertRegs = N > 16 ? 120 : 136;
+  constexpr int kSoftmaxRegs = N > 16 ? 200 : 168, kConvertRegs = N > 16 ? 120 : 136;
   static_assert(4 * kSoftmaxRegs + 8 * kConvertRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
     ptx::reg_alloc<kSoftmaxRegs>();
-    run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map);
+    run_role<N, RAW_SLOTS, P8, kRoleSoftmax>(s, P, &ckv_map, &sf_map, &kpe_map);
   } else if (warp < 12) {
     if constexpr (kConvertRegs >= 128) ptx::reg_alloc<kConvertRegs>(); else ptx::reg_dealloc<kConvertRegs>();
-    run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map);
+    run_role<N, RAW_SLOTS, P8, kRoleConvert>(s, P, &ckv_map, &sf_map, &kpe_map);
   } else {
     ptx::reg_dealloc<64>();
-    if (warp == 12) run_role<N, RAW_SLOTS, P8, kRoleQk>(s, P, &ckv_map);
-    else if (warp == 13) run_role<N, RAW_SLOTS, P8, kRoleProducer>(s, P, &ckv_map);
-    else if (warp == 14) run_role<N, RAW_SLOTS, P8, kRolePv>(s, P, &ckv_map);
-    else run_role<N, RAW_SLOTS, P8, kRoleIdle>(s, P, &ckv_map);
+    if (warp == 12) run_role<N, RAW_SLOTS, P8, kRoleQk>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 13) run_role<N, RAW_SLOTS, P8, kRoleProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 14) run_role<N, RAW_SLOTS, P8, kRolePv>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else run_role<N, RAW_SLOTS, P8, kRoleIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
   }
 
   ptx::tc_fence_before_sync();
