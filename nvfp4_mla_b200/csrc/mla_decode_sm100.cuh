@@ -360,7 +360,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       for (int j = 0; j < 4; ++j) {  // word j0 + j = channels [8 (j0 + j), + 8) of the panel, scale block (j0 + j) / 2
         uint32_t e[4];
         if (MLA_EXP(P, 8)) {
-          for (int i = 0; i < 4; ++i) h[4 * j + i] = wds[j0 + j] + i + sc[0];
+          for (int i = 0; i < 4; ++i) h[4 * j + i] = (wds[j0 + j] + i + sc[0]) & 0x03FF03FFu;  // tiny finite values
           continue;
         }
         ptx::e2m1x8_to_f16x8(wds[j0 + j], e);
@@ -525,7 +525,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
       uint32_t e[4];
       if (MLA_EXP(P, 8)) {
-        for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = wds[j] + i + sc[0];
+        for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = (wds[j] + i + sc[0]) & 0x07070707u;  // tiny finite values
         continue;
       }
       ptx::e2m1x8_to_f16x8(wds[j], e);
