@@ -49,9 +49,9 @@ TOKEN_BYTES = 352
 # (README.md:194 and benchmarks/results/b200.csv:108 of the reference project).
 BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
 # DRAM bytes (read + write) per cached token of the decode kernel, from the committed ncu capture of a smaller case
-# (profiles/decode_kernel_h16_b8_64k_ncu_full.md: 208.6 MB for 524 288 tokens); traffic grows with the token count, so the
+# (profiles/decode_kernel_h16_b8_64k_ncu_full.md: 211.3 MB for 524 288 tokens); traffic grows with the token count, so the
 # benchmark scales it to its own workload.
-NCU_TRAFFIC_BYTES_PER_TOKEN = 398
+NCU_TRAFFIC_BYTES_PER_TOKEN = 403
 KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 
@@ -168,19 +168,103 @@ def cpu_reference_sample(cache, n_requests, repeats=1):
     return dt, nbytes, os.cpu_count()
 
 
+def bench_writer(args):
+    """`--workload writer_1m`: one step = quantise and append 1 048 576 new tokens (64 requests x 16 384) into an empty
+    paged cache with the CUDA cache writer. HBM-bound: 1152 bytes read + 352 written per token. One GPU."""
+    import numpy as np
+    import torch
+    import nvfp4_mla_b200 as mla
+    B, L, ps = 64, 16384, 64
+    nnz, bytes_per_token = B * L, 1152 + TOKEN_BYTES
+    if args.impl == "reference" or not torch.cuda.is_available():
+        # CPU arm: the numpy writer of the oracle on a sample of the tokens
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import mla_oracle as O
+        n = 16384
+        rng = np.random.default_rng(0)
+        ckv, kpe = rng.standard_normal((n, 512), dtype=np.float32), rng.standard_normal((n, 64), dtype=np.float32)
+        t0 = time.perf_counter()
+        O.quantize_ckv(ckv, 2.0 ** -9), O.quantize_kpe(kpe, 2.0 ** -6)
+        dt = time.perf_counter() - t0
+        val = n * bytes_per_token / dt / 1e9
+        print(json.dumps({"impl": "reference", "metric": "nvfp4_mla_writer_bandwidth", "value": val, "unit": "GB/s", "n_gpus": 1,
+                          "steps": 1, "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": "writer_1m"},
+                          "cpu_baseline": {"value": val, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                           "sample": f"{n} tokens, numpy writer of the oracle"},
+                          "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    ckv = torch.randn(nnz, 512, generator=g, device=dev).bfloat16()
+    kpe = torch.randn(nnz, 64, generator=g, device=dev).bfloat16()
+    P = B * L // ps
+    kv_indices = torch.randperm(P, generator=g, device=dev).int()
+    kv_indptr = (torch.arange(B + 1, device=dev) * (L // ps)).int()
+    lens = torch.full((B,), L, dtype=torch.int32, device=dev)
+    bi, pos = mla.get_batch_indices_positions((torch.arange(B + 1, device=dev) * L).int(), lens, nnz)
+    caches = (torch.zeros(P, ps, 256, dtype=torch.uint8, device=dev),
+              torch.zeros(P, ps, 32, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+              torch.zeros(P, ps, 64, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn))
+
+    def step():
+        mla.quantize_append_paged_mla_kv_cache(ckv, kpe, bi, pos, *caches, kv_indices, kv_indptr, None, 2.0 ** -9, 2.0 ** -6)
+    steps = min(args.steps, 200)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.mark("load_begin"), sampler.mark("timed_begin")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.mark("timed_end")
+    ms = e0.elapsed_time(e1) / steps
+    # end to end: the new rows come from pinned host memory every step, a device-to-host read of one cache page ends it
+    hc, hk = ckv.cpu().pin_memory(), kpe.cpu().pin_memory()
+    page = torch.empty(ps, 256, dtype=torch.uint8).pin_memory()
+    e0.record()
+    for _ in range(3):
+        ckv.copy_(hc, non_blocking=True), kpe.copy_(hk, non_blocking=True)
+        step()
+        page.copy_(caches[0][0], non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / 3
+    peak, kind = measured_peak()
+    val = nnz * bytes_per_token / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "nvfp4_mla_writer_bandwidth", "value": val, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16 inputs",
+        "data": "synthetic",
+        "config": {"workload": f"writer_1m: {nnz} new tokens (B={B} x {L}), page_size={ps}, shuffled pages",
+                   "l2": "1.6 GB touched per step, larger than L2, no flush"},
+        "e2e": {"value": nnz * bytes_per_token / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": nnz * 1152, "d2h_bytes_per_step": ps * 256},
+        "gpu_launches": steps,
+        "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "peak_kind": f"of {kind}",
+                     "kernel": "mla_quantize_append_kernel", "algorithmic_bytes_per_launch": nnz * bytes_per_token, "traffic": None},
+        "clocks": sampler.stop()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS) + ["writer_1m"])
     ap.add_argument("--num-splits", type=int, default=0)
     ap.add_argument("--precision", default=None, choices=["bf16", "fp8"], help="override the workload's precision mode")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "writer_1m":
+        return bench_writer(args)
 
     import torch
     import torch.distributed as dist
