@@ -138,7 +138,7 @@ NVFP4_MLA_API int nvfp4_mla_quantize_append(const void* ckv, const void* kpe, co
                               void* stream);
 
 /* Log-sum-exp merge of `parts` partial results: o_part [parts, rows, 512] float (each normalised by its own
- * softmax sum), lse_part [parts, rows] float in log2 units (-inf = empty partial, weight 0). Any of out
+ * softmax sum), lse_part [parts, rows] float in log2 units (-inf = empty partial, weight 0); parts <= 512. Any of out
  * (bfloat16 [rows, 512]), out_f32 (float [rows, 512]) and lse (float [rows]) may be NULL.
  * Replaces the pybind `combine` (nvfp4_mla/csrc/mla_decode.cu:1281-1294, kernel :933-966); also the merge step of
  * sequence-sharded decode across GPUs. */

@@ -245,9 +245,16 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
                             ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
-  MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel, dim3(unsigned(batch) * unsigned(heads)), dim3(mla::kCombineThreads), 0, st,
-                            pb, static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
-                            static_cast<const float*>(o_part), out, out_f32, lse));
+  // few rows: four thread groups share a row's partials; many rows: one group per row keeps the CTAs small
+  const unsigned rows = unsigned(batch) * unsigned(heads);
+  if (rows <= 2u * unsigned(d->sm_count))
+    MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel<4>, dim3(rows), dim3(512), 0, st, pb,
+                              static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
+                              static_cast<const float*>(o_part), out, out_f32, lse));
+  else
+    MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel<1>, dim3(rows), dim3(128), 0, st, pb,
+                              static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
+                              static_cast<const float*>(o_part), out, out_f32, lse));
   return 0;
 }
 
@@ -406,13 +413,18 @@ int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int
                       void* stream) {
   g_error[0] = 0;
   MLA_CHECK(parts > 0 && rows >= 0, "parts must be positive and rows non-negative");
+  MLA_CHECK(parts <= mla::kCombineMaxParts, "at most %d partials per row, got %d", mla::kCombineMaxParts, parts);
   if (rows == 0) return 0;
   MLA_CHECK(o_part && lse_part, "null pointer argument");
   MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
   MLA_CHECK(aligned(o_part, 16) && aligned(out, 8) && aligned(out_f32, 16), "o_part and out_f32 must be 16-byte, out 8-byte aligned");
   MLA_CHECK(rows < (int64_t(1) << 31), "rows must be below 2^31");
-  mla::mla_combine_dense_kernel<<<unsigned(rows), mla::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      o_part, lse_part, parts, rows, out, out_f32, lse);
+  if (rows <= 296)
+    mla::mla_combine_dense_kernel<4><<<unsigned(rows), 512, 0, static_cast<cudaStream_t>(stream)>>>(o_part, lse_part, parts, rows, out,
+                                                                                                   out_f32, lse);
+  else
+    mla::mla_combine_dense_kernel<1><<<unsigned(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(o_part, lse_part, parts, rows, out,
+                                                                                                   out_f32, lse);
   MLA_CUDA(cudaGetLastError());
   return 0;
 }

@@ -130,11 +130,14 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
 
 // ---------------------------------------------------------------------------------------------------------------
 // Merge of the partials of one output row (b, h): out = sum_i 2^(lse_i - M) o_i / sum_i 2^(lse_i - M).
-// One CTA of 128 threads per row; each thread owns 4 channels. Log-sum-exp weights are computed by the lanes of a
-// warp in parallel (one partial per lane) and reduced with shuffles; every warp repeats that small reduction so the
-// four warps never have to meet.
+// One CTA per row: GROUPS groups of 128 threads, each thread owns 4 channels; group g takes the partials
+// i = g, g + GROUPS, ... in batches of 8 independent 16-byte loads (a row with a hundred partials, one long request
+// spread over every SM, is a chain of memory latencies otherwise), and the groups' sums meet in shared memory. The
+// host picks GROUPS = 4 when there are few rows (their CTAs cannot fill the GPU anyway) and 1 when there are many. Log-sum-exp
+// weights are computed by the lanes of a warp in parallel (one partial per lane) and reduced with shuffles; every
+// warp repeats that small reduction so the warps only meet once.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kCombineThreads = 128;
+constexpr int kCombineMaxGroups = 4;
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -153,46 +156,63 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // Shared tail: `n_parts` partials whose (lse, o-row) addresses are produced by `lse_of(i)` / `o_of(i)`.
-template <class LseOf, class OOf>
+// `weights` and `partial` are shared-memory scratch of at least n_parts (up to kCombineMaxParts) and 3 x 128 x 4 floats.
+constexpr int kCombineMaxParts = 512;
+template <int GROUPS, class LseOf, class OOf>
 __device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, long long row, void* out_bf16,
-                                          float* out_f32, float* lse_out) {
-  const int lane = threadIdx.x & 31;
+                                          float* out_f32, float* lse_out, float* weights, float4* partial) {
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 7, t = threadIdx.x & 127;
   float M = -INFINITY;
   for (int i = lane; i < n_parts; i += 32) M = fmaxf(M, lse_of(i));
   M = warp_max(M);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
-  if (M > -INFINITY) {
-    for (int i0 = 0; i0 < n_parts; i0 += 32) {
-      const int i = i0 + lane;
-      const float wl = i < n_parts ? exp2f(lse_of(i) - M) : 0.f;  // lse = -inf (empty partial) gives weight 0
-      den += wl;
-      const int cnt = n_parts - i0 < 32 ? n_parts - i0 : 32;
-      for (int j = 0; j < cnt; ++j) {
-        const float wj = __shfl_sync(~0u, wl, j);
-        if (wj != 0.f) {
-          const float4 v = reinterpret_cast<const float4*>(o_of(i0 + j))[threadIdx.x];
-          acc.x += wj * v.x, acc.y += wj * v.y, acc.z += wj * v.z, acc.w += wj * v.w;
-        }
-      }
+  for (int i = lane; i < n_parts; i += 32) {
+    const float wl = M > -INFINITY ? exp2f(lse_of(i) - M) : 0.f;  // lse = -inf (empty partial) gives weight 0
+    den += wl;
+    if (threadIdx.x < 32 && i < kCombineMaxParts) weights[i] = wl;
+  }
+  den = warp_sum(den);
+  __syncthreads();
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i0 = grp; i0 < n_parts; i0 += 8 * GROUPS) {
+    float4 v[8];
+    float w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * GROUPS;
+      w[j] = i < n_parts ? weights[i] : 0.f;
+      v[j] = w[j] != 0.f ? reinterpret_cast<const float4*>(o_of(i))[t] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    den = warp_sum(den);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc.x += w[j] * v[j].x, acc.y += w[j] * v[j].y, acc.z += w[j] * v[j].z, acc.w += w[j] * v[j].w;
+  }
+  if (GROUPS > 1) {
+    if (grp > 0) partial[(grp - 1) * 128 + t] = acc;
+    __syncthreads();
+    if (grp > 0) return;
+#pragma unroll
+    for (int g = 0; g < GROUPS - 1; ++g) {
+      const float4 o = partial[g * 128 + t];
+      acc.x += o.x, acc.y += o.y, acc.z += o.z, acc.w += o.w;
+    }
   }
   const float s = den > 0.f ? 1.f / den : 0.f;
   acc.x *= s, acc.y *= s, acc.z *= s, acc.w *= s;
   if (out_bf16)
-    reinterpret_cast<uint2*>(out_bf16)[row * (CKV / 4) + threadIdx.x] =
-        make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
-  if (out_f32) reinterpret_cast<float4*>(out_f32)[row * (CKV / 4) + threadIdx.x] = acc;
-  if (lse_out && threadIdx.x == 0) lse_out[row] = den > 0.f ? M + log2f(den) : -INFINITY;
+    reinterpret_cast<uint2*>(out_bf16)[row * (CKV / 4) + t] = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+  if (out_f32) reinterpret_cast<float4*>(out_f32)[row * (CKV / 4) + t] = acc;
+  if (lse_out && t == 0) lse_out[row] = den > 0.f ? M + log2f(den) : -INFINITY;
 }
 
 // Partials addressed through the schedule (what the decode kernel wrote).
-__global__ void __launch_bounds__(kCombineThreads)
+template <int GROUPS>
+__global__ void __launch_bounds__(128 * GROUPS)
 mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const float* __restrict__ lse_part,
                          const float* __restrict__ o_part, void* out_bf16, float* out_f32, float* lse_out) {
-  __shared__ int slots[512];
+  __shared__ int slots[kCombineMaxParts];
   __shared__ int n_parts_s;
+  __shared__ float weights[kCombineMaxParts];
+  __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
   ptx::grid_dependency_wait();  // launched as a programmatic dependent of the decode kernel
   const long long row = blockIdx.x;
   const int b = int(row / pb.heads), h = int(row % pb.heads);
@@ -217,27 +237,30 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
       }
       int pos = count + incl - mine;
       for (int c = c0; c <= c1; ++c, ++pos)
-        if (pos < 512) slots[pos] = int(c + w);
+        if (pos < kCombineMaxParts) slots[pos] = int(c + w);
       count += __shfl_sync(~0u, incl, 31);
     }
-    if (threadIdx.x == 0) n_parts_s = count < 512 ? count : 512;
+    if (threadIdx.x == 0) n_parts_s = count < kCombineMaxParts ? count : kCombineMaxParts;
   }
   __syncthreads();
   const int n_parts = n_parts_s;
-  merge_row(
+  merge_row<GROUPS>(
       n_parts, [&](int i) { return lse_part[(long long)slots[i] * N + n]; },
-      [&](int i) { return o_part + ((long long)slots[i] * N + n) * CKV; }, row, out_bf16, out_f32, lse_out);
+      [&](int i) { return o_part + ((long long)slots[i] * N + n) * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
 }
 
 // Dense partials [parts, rows, 512] / [parts, rows]: the merge a caller runs on (o, lse) pairs gathered from
 // several GPUs or produced by its own splits.
-__global__ void __launch_bounds__(kCombineThreads)
+template <int GROUPS>
+__global__ void __launch_bounds__(128 * GROUPS)
 mla_combine_dense_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, int parts, long long rows,
                          void* out_bf16, float* out_f32, float* lse_out) {
+  __shared__ float weights[kCombineMaxParts];
+  __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
   const long long row = blockIdx.x;
-  merge_row(
+  merge_row<GROUPS>(
       parts, [&](int i) { return lse_part[(long long)i * rows + row]; },
-      [&](int i) { return o_part + ((long long)i * rows + row) * CKV; }, row, out_bf16, out_f32, lse_out);
+      [&](int i) { return o_part + ((long long)i * rows + row) * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
 }
 
 }  // namespace mla
