@@ -9,6 +9,7 @@
 #include "../../include/nvfp4_mla_b200.h"
 #include "mla_common.cuh"
 #include "mla_decode_sm100.cuh"
+#include "mla_decode_hm_sm100.cuh"
 #include "mla_dequant.cuh"
 #include "mla_quantize.cuh"
 #include "mla_schedule.cuh"
@@ -47,17 +48,29 @@ using DecodeKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtens
 constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
 // Heads per CTA (the N of both MMAs). One conversion of a tile serves all of the CTA's heads, so more heads per CTA
 // means less conversion work per head; 32 fit next to the tiles only in the 8-bit mode (tensor memory and shared memory).
-int heads_per_cta(int heads, int precision) { return precision == NVFP4_MLA_PRECISION_FP8 && heads % 32 == 0 ? 32 : 16; }
+// With 128 heads per request the 8-bit mode runs the heads-as-M kernel: a pair of CTAs per 128 heads (each CTA
+// accumulates half of the output channels), scheduled as one unit, so the schedule sees half as many "CTAs".
+int heads_per_cta(int heads, int precision) {
+  if (precision != NVFP4_MLA_PRECISION_FP8) return 16;
+  return heads % 128 == 0 ? 128 : heads % 32 == 0 ? 32 : 16;
+}
+int schedule_units(int sm_count, int hpc) { return hpc == 128 ? sm_count / 2 : sm_count; }
+int ctas_per_unit(int hpc) { return hpc == 128 ? 2 : 1; }
 DecodeKernel decode_kernel(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
-    return hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true> : mla::mla_decode_kernel<16, kRawSlots8, true>;
+    return hpc == 128  ? mla::mla_decode_hm_kernel<kRawSlots8>
+           : hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true>
+                       : mla::mla_decode_kernel<16, kRawSlots8, true>;
   return mla::mla_decode_kernel<16, kRawSlots16, false>;
 }
 size_t decode_smem(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
-    return hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>() : mla::decode_smem_bytes<16, kRawSlots8, true>();
+    return hpc == 128  ? mla::hm_smem_bytes<kRawSlots8>()
+           : hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>()
+                       : mla::decode_smem_bytes<16, kRawSlots8, true>();
   return mla::decode_smem_bytes<16, kRawSlots16, false>();
 }
+static_assert(mla::hm_smem_bytes<kRawSlots8>() <= 232448, "heads-as-M kernel exceeds the shared memory a CTA can opt in to");
 static_assert(mla::decode_smem_bytes<32, kRawSlots8, true>() <= 232448 && mla::decode_smem_bytes<16, kRawSlots8, true>() <= 232448 &&
                   mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448,
               "decode kernel exceeds the 227 KB of shared memory a CTA can opt in to");
@@ -75,7 +88,7 @@ int device_info(DeviceInfo** out) {
     MLA_CHECK(major == 10, "nvfp4_mla_b200 needs an sm_100a GPU (B200), found compute capability %d.x", major);
     MLA_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
     for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8})
-      for (int hpc : {16, 32})
+      for (int hpc : {16, 32, 128})
         MLA_CUDA(cudaFuncSetAttribute(decode_kernel(prec, hpc), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       int(decode_smem(prec, hpc))));
     d.ready = true;
@@ -178,7 +191,8 @@ int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
   size_t need = 0;
   for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8}) {
     mla::Problem pb;
-    if (problem_of(batch, heads, 1, num_splits, d->sm_count, heads_per_cta(heads, prec), &pb)) return -1;
+    const int hpc = heads_per_cta(heads, prec);
+    if (problem_of(batch, heads, 1, num_splits, schedule_units(d->sm_count, hpc), hpc, &pb)) return -1;
     const size_t n = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total;
     need = n > need ? n : need;
   }
@@ -206,7 +220,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   if (device_info(&d)) return 1;
   mla::Problem pb;
   const int hpc = heads_per_cta(heads, precision);
-  if (problem_of(batch, heads, max_kv_len, num_splits, d->sm_count, hpc, &pb)) return 1;
+  if (problem_of(batch, heads, max_kv_len, num_splits, schedule_units(d->sm_count, hpc), hpc, &pb)) return 1;
   if (batch == 0) return 0;
   const mla::WsLayout L = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta);
   MLA_CHECK(workspace_bytes >= int64_t(L.total), "workspace too small: %lld bytes given, %lld needed", (long long)workspace_bytes,
@@ -241,7 +255,8 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta), dim3(mla::kDecodeThreads), decode_smem(precision, hpc), st,
+  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)), dim3(mla::kDecodeThreads),
+                            decode_smem(precision, hpc), st,
                             ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 

@@ -1,0 +1,425 @@
+// Weight-absorbed MLA decode for 128 heads per request, 8-bit mode, with the HEADS as the M dimension of both MMAs.
+//
+// With 128 heads the query block fills the 128 rows of a tcgen05 MMA, so one conversion of a token serves all of
+// them (the tokens-as-M kernel in mla_decode_sm100.cuh converts a token once per 16 or 32 heads):
+//
+//   HBM --TMA--> raw ring (smem) --convert warps--> K/V tile in smem, E4M3, [token][channel], 128-byte swizzle
+//   QK^T : S[head, token]  = Q[head, 576] . K^T     A = Q (E4M3) from TENSOR MEMORY (latent part) / smem (rope part),
+//                                                   B = the K/V tile read K-major, N = 64 tokens
+//   PV   : O[head, chan]  += P[head, token] . V     A = P (E4M3) from tensor memory, written there by the softmax threads,
+//                                                   B = the same K/V tile read MN-major, N = 256 channels, K = 32 tokens
+// One dequantised copy of a token in shared memory feeds both MMAs; nothing of K or V passes through tensor memory.
+// O for 128 heads x 512 channels would need all 512 tensor-memory columns, so a PAIR of CTAs shares a request: both
+// compute the full scores, CTA `cg` of the pair accumulates channels [256 cg, 256 cg + 256). The pair gets the same
+// segments from the schedule (which is run over pairs) and writes one partial slot, so the combine kernel is unchanged.
+// The two CTAs are independent (no cluster); the second reader of a cache line finds it in L2.
+//
+// Tensor memory (512 columns): Q latent 0..127 | S buffer 0: 128..191 | S buffer 1: 192..255 | O: 256..511.
+// P of a tile overwrites the first 16 columns of the S buffer it was computed from.
+// Softmax: thread = head (= tensor-memory lane), so the running max, the sum and the O rescale are thread-local; the
+// tcgen05.ld/st of a rescale are warp-wide, so a warp rescales when any of its heads needs it.
+// Numerics (8-bit mode): Q rows are E4M3 with one scale per row covering both parts (the rope part is pre-multiplied
+// by kpe_scale / (8 ckv_scale) so that one accumulator holds the whole score), K/V bytes are
+// E4M3((e2m1 x block scale) / 8) exactly as in the tokens-as-M kernel, P is E4M3 of 2^(x - m) <= 2^8.
+//
+// Warp roles (512 threads): 0-3 softmax + query load + epilogue, 4-11 dequantise, 12 QK^T issue, 13 TMA producer,
+// 14 PV issue. Every wait is bounded (ptx::mbar_wait) as in the other kernel.
+#pragma once
+#include "mla_decode_sm100.cuh"
+
+namespace mla {
+
+constexpr int kHmHeads = 128;      // heads per CTA pair = MMA M
+constexpr int kHmTile = HALF;      // tokens per tile = one staging slot
+constexpr int kHmKvBufs = 3;
+constexpr int kHmPanelBytes = kHmTile * 128;  // one 128-channel panel of the E4M3 K/V tile
+
+template <int RAW_SLOTS>
+struct HmSmem {
+  alignas(1024) uint8_t kv[kHmKvBufs][5][kHmPanelBytes];  // panels 0..3: latent channels, panel 4: rope (64 of 128 bytes per row)
+  alignas(1024) uint8_t qpe[kHmHeads * 128];              // rope part of Q, E4M3, row = head (64 of 128 bytes used)
+  alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
+  Seg segs[kSegBatch];
+  alignas(8) uint64_t raw_full[RAW_SLOTS];
+  uint64_t raw_empty[RAW_SLOTS];
+  uint64_t kv_full[kHmKvBufs];   // tile converted (8 convert warps)
+  uint64_t kv_free[kHmKvBufs];   // PV of the tile (hence its QK^T too) has finished reading the buffer
+  uint64_t s_full[2];            // QK^T of the tile complete
+  uint64_t p_full[2];            // P written to tensor memory (4 softmax warps)
+  uint64_t pv_done[2];           // PV of the tile complete: O may be rescaled, the S/P buffer reused
+  uint64_t q_full;               // query of the segment in place (4 softmax warps)
+  uint32_t tmem_base;
+  int abort_flag;
+};
+template <int RAW_SLOTS>
+constexpr size_t hm_smem_bytes() { return sizeof(HmSmem<RAW_SLOTS>) + 1024; }
+
+struct HmCols {
+  static constexpr uint32_t QN = 0, S0 = 128, O = 256;
+  __host__ __device__ static constexpr uint32_t s(uint32_t buf) { return S0 + 64 * buf; }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: dequantise (8 warps). Warp cw: panel cw % 4 (128 channels), token rows 32 (cw / 4) .. + 31; thread = one row of
+// one panel: 64 packed bytes in, 128 E4M3 bytes out, plus a 16-byte piece of the row's rope bytes.
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+  const int lane = ptx::lane_id();
+  const int cw = (threadIdx.x >> 5) - 4, p = cw & 3, r = (cw >> 2) * 32 + lane;
+  const uint32_t swz = uint32_t(r & 7) << 4;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
+      const int slot = it % RAW_SLOTS, kb = it % kHmKvBufs;
+      bool ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (it / RAW_SLOTS) & 1, &s.abort_flag));
+      if (!__all_sync(~0u, ok)) return;
+      if (threadIdx.x == 128) MLA_TRACE_AT(P, 0, it);
+      const uint8_t* raw = s.raw[slot];
+      const bool valid = seg.tok0 + t * kHmTile + r < seg.tok_end;
+      // the 8 block scales of this panel row, the 64 packed bytes, 16 bytes of rope
+      const uint2 sf8 = *reinterpret_cast<const uint2*>(raw + kRawSf + r * 32 + ((uint32_t(p >> 1) ^ ((r >> 2) & P.sf_swz_mask)) << 4) +
+                                                        (p & 1) * 8);
+      const uint8_t* half_row = raw + (p >> 1) * kRawCkvHi + r * 128;
+      uint4 w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(half_row + ((uint32_t((p & 1) * 4 + i) << 4) ^ swz));
+      const uint4 rope = *reinterpret_cast<const uint4*>(raw + kRawKpe + r * 64 + ((uint32_t(p) ^ ((r >> 1) & P.kpe_swz_mask)) << 4));
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
+      // the buffer's previous tile (it - kHmKvBufs) must have been consumed
+      ok = it < kHmKvBufs || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag));
+      if (!__all_sync(~0u, ok)) return;
+      uint8_t* out_row = s.kv[kb][p] + r * 128;
+      const uint32_t words[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
+                                  w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = channels [16c, 16c + 16) of the panel = scale block c
+        const uint32_t sfb = ((c < 4 ? sf8.x : sf8.y) >> (8 * (c & 3))) & 0xFFu;
+        uint32_t sc = ptx::e4m3x2_to_f16x2(uint16_t(sfb | (sfb << 8)));
+        sc = ptx::hmul2(sc, 0x30003000u);  // x 1/8, exact
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t e[4], b[4];
+          ptx::e2m1x8_to_f16x8(words[2 * c + j], e);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc));
+          o[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
+          o[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
+        }
+        *reinterpret_cast<uint4*>(out_row + ((uint32_t(c) << 4) ^ swz)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      // rope bytes are E4M3 already: chunk p of the row's 64 bytes
+      *reinterpret_cast<uint4*>(s.kv[kb][4] + r * 128 + ((uint32_t(p) << 4) ^ swz)) =
+          valid ? rope : make_uint4(0, 0, 0, 0);
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.kv_full[kb]);
+      if (threadIdx.x == 128) MLA_TRACE_AT(P, 7, it);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// roles: MMA issue
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_qk_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it, uint32_t& seg_count) {
+  const bool leader = ptx::elect_one();
+  const uint32_t tm = s.tmem_base;
+  const uint32_t idesc = ptx::instr_desc(kHmHeads, kHmTile, ptx::FMT_E4M3, ptx::FMT_E4M3, false, false);
+  const uint64_t qpe_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.qpe), 16, 1024);
+  for (int si = 0; si < n_segs; ++si) {
+    const int ntiles = 2 * s.segs[si].ntiles;
+    if (ntiles <= 0) continue;
+    if (!__all_sync(~0u, ptx::mbar_wait(&s.q_full, seg_count & 1, &s.abort_flag))) return;
+    ++seg_count;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t buf = it & 1, kb = it % kHmKvBufs;
+      // PV of tile it - 2 read its P from this S buffer
+      if (!__all_sync(~0u, it < 2 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.pv_done[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.kv_full[kb], (it / kHmKvBufs) & 1, &s.abort_flag)))) return;
+      ptx::tc_fence_after_sync();
+      if (leader) {
+        const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][0]), 16, 1024);
+#pragma unroll 1
+        for (int p = 0; p < 4; ++p) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)  // 32 channels per MMA: 8 tensor-memory columns of Q, 32 bytes of the K rows
+            ptx::mma_f8_ts(tm + HmCols::s(buf), tm + HmCols::QN + 32 * p + 8 * ks, k_desc + ((p * kHmPanelBytes + ks * 32) >> 4), idesc,
+                           (p | ks) != 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          ptx::mma_f8_ss(tm + HmCols::s(buf), qpe_desc + ((ks * 32) >> 4), k_desc + ((4 * kHmPanelBytes + ks * 32) >> 4), idesc, 1);
+        ptx::mma_commit(&s.s_full[buf]);
+      }
+      __syncwarp();
+    }
+  }
+}
+
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it, int cg) {
+  const bool leader = ptx::elect_one();
+  const uint32_t tm = s.tmem_base;
+  // B = V read MN-major: N = 256 channels = two 128-byte runs (panels 2 cg, 2 cg + 1, one panel apart), K = 32 token rows
+  const uint32_t idesc = ptx::instr_desc(kHmHeads, 256, ptx::FMT_E4M3, ptx::FMT_E4M3, false, true);
+  for (int si = 0; si < n_segs; ++si) {
+    const int ntiles = 2 * s.segs[si].ntiles;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t buf = it & 1, kb = it % kHmKvBufs;
+      if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      ptx::tc_fence_after_sync();
+      if (leader) {
+        const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][2 * cg]), kHmPanelBytes, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          ptx::mma_f8_ts(tm + HmCols::O, tm + HmCols::s(buf) + 8 * ks, v_desc + ((ks * 32 * 128) >> 4), idesc, (t | ks) != 0);
+        ptx::mma_commit(&s.pv_done[buf]);
+        ptx::mma_commit(&s.kv_free[kb]);
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: softmax + query load + epilogue (4 warps; thread h = head h of the group = tensor-memory lane h)
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it, int cg) {
+  const int lane = ptx::lane_id(), warp = threadIdx.x >> 5;
+  const int h = threadIdx.x;  // 0..127
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(warp * 32) << 16);
+  constexpr float kGrow = 8.f;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    // ---- query of (request seg.b, head group seg.hg): this thread's row. Every MMA that read the previous segment's
+    // query has completed (this thread consumed the scores of its last tile).
+    const long long row = (long long)seg.b * P.heads + (long long)seg.hg * kHmHeads + h;
+    const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV);
+    const uint4* qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE);
+    const float ratio = P.kpe_scale / (8.f * P.ckv_scale);  // rope scores in units of the latent ones
+    float an = 0.f, ap = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < CKV / 8; ++c) {
+      const uint4 v = qn[c];
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = fabsf(__uint_as_float(wv[j] << 16)), hi = fabsf(__uint_as_float(wv[j] & 0xFFFF0000u));
+        an = fmaxf(an, (lo < INFINITY ? lo : 0.f)), an = fmaxf(an, (hi < INFINITY ? hi : 0.f));  // ignore inf / nan for the scale
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < KPE / 8; ++c) {
+      const uint4 v = qp[c];
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = fabsf(__uint_as_float(wv[j] << 16)), hi = fabsf(__uint_as_float(wv[j] & 0xFFFF0000u));
+        ap = fmaxf(ap, (lo < INFINITY ? lo : 0.f)), ap = fmaxf(ap, (hi < INFINITY ? hi : 0.f));
+      }
+    }
+    const float amax = fmaxf(fmaxf(an, ap * ratio), 1e-30f);
+    const float inv_n = 448.f / amax, inv_p = ratio * inv_n;
+    const float qa = P.sm_scale_log2 * P.ckv_scale * 8.f * (amax / 448.f);  // score scale of this head, log2 units
+#pragma unroll 1
+    for (int c0 = 0; c0 < CKV / 8; c0 += 8) {  // 64 channels = 16 tensor-memory columns per trip
+      uint32_t col[16];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = qn[c0 + c];
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          b[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(wv[j] << 16) * inv_n, __uint_as_float(wv[j] & 0xFFFF0000u) * inv_n);
+        col[2 * c] = b[0] | (b[1] << 16), col[2 * c + 1] = b[2] | (b[3] << 16);
+      }
+      ptx::tmem_st16(tm_lane + HmCols::QN + 2 * c0, col);
+    }
+#pragma unroll
+    for (int c = 0; c < KPE / 8; c += 2) {  // 16 rope channels = one 16-byte chunk of the head's row in shared memory
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const uint4 v = qp[c + k];
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          b[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(wv[j] << 16) * inv_p, __uint_as_float(wv[j] & 0xFFFF0000u) * inv_p);
+        o[2 * k] = b[0] | (b[1] << 16), o[2 * k + 1] = b[2] | (b[3] << 16);
+      }
+      *reinterpret_cast<uint4*>(s.qpe + h * 128 + ((uint32_t(c >> 1) << 4) ^ (uint32_t(h & 7) << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    ptx::tmem_wait_st();
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.q_full);
+
+    float m = -INFINITY, l = 0.f;
+    const int ntiles = 2 * seg.ntiles;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t buf = it & 1;
+      const bool ok = MLA_WAIT(P, 8 | 32, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
+      if (!__all_sync(~0u, ok)) return;
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
+      ptx::tc_fence_after_sync();
+      const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile);  // columns at or beyond it are masked
+      float x[kHmTile];
+#pragma unroll
+      for (int c0 = 0; c0 < kHmTile; c0 += 32) {
+        uint32_t sr[32];
+        ptx::tmem_ld32(tm_lane + HmCols::s(buf) + c0, sr);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[c0 + j] = (c0 + j < nvalid) ? __uint_as_float(sr[j]) * qa : -INFINITY;
+      }
+      float mx = x[0];
+#pragma unroll
+      for (int j = 1; j < kHmTile; ++j) mx = fmaxf(mx, x[j]);
+      const bool need = mx > m + kGrow;
+      if (__any_sync(~0u, need)) {  // tcgen05.ld / st are warp-wide: the warp rescales when any of its heads must
+        const float mn = need ? mx : m;
+        const float corr = need ? ((m == -INFINITY) ? 0.f : ptx::ex2(m - mn)) : 1.f;
+        l *= corr, m = mn;
+        if (t > 0) {  // O holds the segment's earlier tiles: wait for the PV of tile it - 1, then scale this head's row
+          const bool okv = MLA_WAIT(P, 9 | 32, ptx::mbar_wait(&s.pv_done[buf ^ 1], ((it - 1) >> 1) & 1, &s.abort_flag));
+          if (!__all_sync(~0u, okv)) return;
+          ptx::tc_fence_after_sync();
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 32) {
+            uint32_t o[32];
+            ptx::tmem_ld32(tm_lane + HmCols::O + c0, o);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+            ptx::tmem_st32(tm_lane + HmCols::O + c0, o);
+          }
+          ptx::tmem_wait_st();
+        }
+      }
+      // P = 2^(x - m) as E4M3 into the first 16 columns of this S buffer (its scores are in registers now)
+      const float mm = (m == -INFINITY) ? 0.f : m;
+      uint32_t pk[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float p0 = ptx::ex2(x[4 * c] - mm), p1 = ptx::ex2(x[4 * c + 1] - mm), p2 = ptx::ex2(x[4 * c + 2] - mm),
+                    p3 = ptx::ex2(x[4 * c + 3] - mm);
+        l += (p0 + p1) + (p2 + p3);
+        pk[c] = ptx::f32x2_to_e4m3x2(p0, p1) | (ptx::f32x2_to_e4m3x2(p2, p3) << 16);
+      }
+      ptx::tmem_st16(tm_lane + HmCols::s(buf), pk);
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
+    }
+
+    // ---- segment epilogue: wait for the last PV, write this head's 256 channels of the normalised partial
+    const bool ok = ptx::mbar_wait(&s.pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);
+    if (!__all_sync(~0u, ok)) return;
+    ptx::tc_fence_after_sync();
+    const float inv = l > 0.f ? 8.f * P.ckv_scale / l : 0.f;
+    const long long slot = (long long)seg.cta + seg.w;
+    float* orow = P.o_part + (slot * kHmHeads + h) * CKV + 256 * cg;
+#pragma unroll 1
+    for (int c0 = 0; c0 < 256; c0 += 32) {
+      uint32_t o[32];
+      ptx::tmem_ld32(tm_lane + HmCols::O + c0, o);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(orow + c0 + j) = make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
+                                                                __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+    }
+    if (cg == 0) P.lse_part[slot * kHmHeads + h] = l > 0.f ? m + log2f(l) : -INFINITY;
+    ptx::tc_fence_before_sync();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS, int ROLE>
+__device__ __forceinline__ void hm_run_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+                                            const CUtensorMap* sf_map, const CUtensorMap* kpe_map) {
+  const int pair = blockIdx.x >> 1, cg = blockIdx.x & 1;
+  const int2 range = P.cta_range[pair];
+  uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
+  for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
+    const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
+    if (ROLE == kRoleSoftmax && int(threadIdx.x) < n_segs) {
+      Seg g = P.segs[(long long)pair + w0 + threadIdx.x];
+      if (g.cta != pair || g.w != w0 + int(threadIdx.x)) g.ntiles = 0;  // empty item or foreign slot
+      s.segs[threadIdx.x] = g;
+    }
+    __syncthreads();
+    if (ROLE == kRoleSoftmax) hm_softmax_role<RAW_SLOTS>(s, P, n_segs, it, cg);
+    if (ROLE == kRoleConvert) hm_convert_role<RAW_SLOTS>(s, P, n_segs, it);
+    if (ROLE == kRoleQk) hm_qk_role<RAW_SLOTS>(s, P, n_segs, it, seg_count);
+    if (ROLE == kRoleProducer) producer_role<RAW_SLOTS>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
+    if (ROLE == kRolePv) hm_pv_role<RAW_SLOTS>(s, P, n_segs, it, cg);
+    __syncthreads();
+    if (s.abort_flag) break;
+  }
+}
+
+template <int RAW_SLOTS>
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_constant__ CUtensorMap sf_map,
+                     const __grid_constant__ CUtensorMap kpe_map, const DecodeParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = HmSmem<RAW_SLOTS>;
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 8);
+    for (int i = 0; i < kHmKvBufs; ++i) ptx::mbar_init(&s.kv_full[i], 8), ptx::mbar_init(&s.kv_free[i], 1);
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.p_full[i], 4), ptx::mbar_init(&s.pv_done[i], 1);
+    ptx::mbar_init(&s.q_full, 4);
+    s.abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&ckv_map), ptx::prefetch_tensormap(&sf_map), ptx::prefetch_tensormap(&kpe_map);
+  }
+  if (warp == 12) {
+    ptx::tmem_alloc(&s.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::grid_launch_dependents();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  ptx::grid_dependency_wait();
+
+  constexpr int kSoftmaxRegs = 184, kConvertRegs = 128;
+  static_assert(4 * kSoftmaxRegs + 8 * kConvertRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
+  if (warp < 4) {
+    ptx::reg_alloc<kSoftmaxRegs>();
+    hm_run_role<RAW_SLOTS, kRoleSoftmax>(s, P, &ckv_map, &sf_map, &kpe_map);
+  } else if (warp < 12) {
+    ptx::reg_alloc<kConvertRegs>();
+    hm_run_role<RAW_SLOTS, kRoleConvert>(s, P, &ckv_map, &sf_map, &kpe_map);
+  } else {
+    ptx::reg_dealloc<64>();
+    if (warp == 12) hm_run_role<RAW_SLOTS, kRoleQk>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 13) hm_run_role<RAW_SLOTS, kRoleProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 14) hm_run_role<RAW_SLOTS, kRolePv>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else hm_run_role<RAW_SLOTS, kRoleIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
+}
+
+}  // namespace mla

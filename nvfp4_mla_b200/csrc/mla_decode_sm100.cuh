@@ -141,8 +141,9 @@ template <int N, bool P8> struct Cols {
 // ---------------------------------------------------------------------------------------------------------------
 // role: TMA producer (one warp; lane 0 issues, all lanes help with page ids)
 // ---------------------------------------------------------------------------------------------------------------
-template <int N, int RAW_SLOTS, bool P8>
-__device__ __forceinline__ void producer_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+// Smem: any struct with raw[RAW_SLOTS][kRawSlotBytes], raw_full / raw_empty[RAW_SLOTS], segs[] and abort_flag.
+template <int RAW_SLOTS, class Smem>
+__device__ __forceinline__ void producer_role(Smem& s, const DecodeParams& P, const CUtensorMap* ckv_map,
                                               const CUtensorMap* sf_map, const CUtensorMap* kpe_map, int n_segs, uint32_t& hcount) {
   const int lane = ptx::lane_id();
   const int ps = 1 << P.page_shift;
@@ -918,7 +919,7 @@ __device__ __forceinline__ void run_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const 
     if (ROLE == kRoleSoftmax) softmax_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
     if (ROLE == kRoleConvert) convert_role<N, RAW_SLOTS, P8>(s, P, n_segs, it, seg_count);
     if (ROLE == kRoleQk) qk_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
-    if (ROLE == kRoleProducer) producer_role<N, RAW_SLOTS, P8>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
+    if (ROLE == kRoleProducer) producer_role<RAW_SLOTS>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
     if (ROLE == kRolePv) pv_role<N, RAW_SLOTS, P8>(s, P, n_segs, it);
     __syncthreads();
     if (s.abort_flag) break;
