@@ -93,22 +93,29 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
       uint8_t* out_row = s.kv[kb][p] + r * 128;
       const uint32_t words[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
                                   w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
+      // rows past the end of the request become zeros (a live tile skips the masking: `full` is warp-uniform)
+      const bool full = seg.tok0 + (t + 1) * kHmTile <= seg.tok_end;
+      const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = channels [16c, 16c + 16) of the panel = scale block c
-        const uint32_t sfb = ((c < 4 ? sf8.x : sf8.y) >> (8 * (c & 3))) & 0xFFu;
-        uint32_t sc = ptx::e4m3x2_to_f16x2(uint16_t(sfb | (sfb << 8)));
-        sc = ptx::hmul2(sc, 0x30003000u);  // x 1/8, exact
-        uint32_t o[4];
+      for (int c2 = 0; c2 < 4; ++c2) {  // two 16-byte chunks (= two scale blocks) per trip
+        const uint32_t sfw = c2 < 2 ? sf8.x : sf8.y;
+        uint32_t s2 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> (16 * (c2 & 1))));  // (scale of chunk 2 c2, of chunk 2 c2 + 1)
+        s2 = ptx::hmul2(s2, 0x30003000u);                                        // x 1/8, exact
+        const uint32_t sc[2] = {__byte_perm(s2, s2, 0x1010), __byte_perm(s2, s2, 0x3232)};
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          uint32_t e[4], b[4];
-          ptx::e2m1x8_to_f16x8(words[2 * c + j], e);
+        for (int k = 0; k < 2; ++k) {  // 16-byte chunk c = channels [16c, 16c + 16) of the panel
+          const int c = 2 * c2 + k;
+          uint32_t o[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc));
-          o[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
-          o[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
+          for (int j = 0; j < 2; ++j) {
+            uint32_t e[4];
+            ptx::e2m1x8_to_f16x8(words[2 * c + j], e);
+            o[2 * j] = ptx::f16x4_to_e4m3x4(ptx::hmul2(e[0], sc[k]), ptx::hmul2(e[1], sc[k]));
+            o[2 * j + 1] = ptx::f16x4_to_e4m3x4(ptx::hmul2(e[2], sc[k]), ptx::hmul2(e[3], sc[k]));
+          }
+          if (!full) o[0] &= vmask, o[1] &= vmask, o[2] &= vmask, o[3] &= vmask;
+          *reinterpret_cast<uint4*>(out_row + ((uint32_t(c) << 4) ^ swz)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        *reinterpret_cast<uint4*>(out_row + ((uint32_t(c) << 4) ^ swz)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       // rope bytes are E4M3 already: chunk p of the row's 64 bytes
       *reinterpret_cast<uint4*>(s.kv[kb][4] + r * 128 + ((uint32_t(p) << 4) ^ swz)) =
@@ -272,18 +279,23 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile);  // columns at or beyond it are masked
-      float x[kHmTile];
+      // raw scores of this head for the tile's 64 tokens; the score scale qa > 0 is applied inside the exponent
+      uint32_t sr[kHmTile];
+      ptx::tmem_ld32(tm_lane + HmCols::s(buf), reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+      ptx::tmem_ld32(tm_lane + HmCols::s(buf) + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+      ptx::tmem_wait_ld();
+      if (nvalid < kHmTile) {  // tail tile: masked tokens get the score -inf
 #pragma unroll
-      for (int c0 = 0; c0 < kHmTile; c0 += 32) {
-        uint32_t sr[32];
-        ptx::tmem_ld32(tm_lane + HmCols::s(buf) + c0, sr);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) x[c0 + j] = (c0 + j < nvalid) ? __uint_as_float(sr[j]) * qa : -INFINITY;
+        for (int j = 0; j < kHmTile; ++j) sr[j] = j < nvalid ? sr[j] : 0xFF800000u;
       }
-      float mx = x[0];
+      float mxs[4] = {__uint_as_float(sr[0]), __uint_as_float(sr[1]), __uint_as_float(sr[2]), __uint_as_float(sr[3])};
 #pragma unroll
-      for (int j = 1; j < kHmTile; ++j) mx = fmaxf(mx, x[j]);
+      for (int j = 4; j + 8 <= kHmTile; j += 8)  // four chains of three-input maxima
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mxs[k] = ptx::max3(mxs[k], __uint_as_float(sr[j + 2 * k]), __uint_as_float(sr[j + 2 * k + 1]));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) mxs[k] = fmaxf(mxs[k], __uint_as_float(sr[60 + k]));
+      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * qa;
       const bool need = mx > m + kGrow;
       if (__any_sync(~0u, need)) {  // tcgen05.ld / st are warp-wide: the warp rescales when any of its heads must
         const float mn = need ? mx : m;
@@ -305,16 +317,18 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
           ptx::tmem_wait_st();
         }
       }
-      // P = 2^(x - m) as E4M3 into the first 16 columns of this S buffer (its scores are in registers now)
-      const float mm = (m == -INFINITY) ? 0.f : m;
+      // P = 2^(s qa - m) as E4M3 into the first 16 columns of this S buffer (its scores are in registers now)
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
       uint32_t pk[16];
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const float p0 = ptx::ex2(x[4 * c] - mm), p1 = ptx::ex2(x[4 * c + 1] - mm), p2 = ptx::ex2(x[4 * c + 2] - mm),
-                    p3 = ptx::ex2(x[4 * c + 3] - mm);
-        l += (p0 + p1) + (p2 + p3);
-        pk[c] = ptx::f32x2_to_e4m3x2(p0, p1) | (ptx::f32x2_to_e4m3x2(p2, p3) << 16);
+        const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c]), qa, neg_m)), p1 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 1]), qa, neg_m));
+        const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 2]), qa, neg_m)), p3 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 3]), qa, neg_m));
+        ls[0] += p0, ls[1] += p1, ls[2] += p2, ls[3] += p3;
+        pk[c] = ptx::pack_e4m3x4(p0, p1, p2, p3);
       }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       ptx::tmem_st16(tm_lane + HmCols::s(buf), pk);
       ptx::tmem_wait_st();
       ptx::tc_fence_before_sync();

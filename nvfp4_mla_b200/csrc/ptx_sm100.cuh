@@ -281,6 +281,28 @@ __device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
   return d;
 }
+// four floats -> four E4M3 bytes (round to nearest even, saturating), p0 in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float p0, float p1, float p2, float p3) {
+  uint32_t d;
+  asm("{\n.reg .b16 lo, hi;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n"
+      "mov.b32 %0, {lo, hi};\n}"
+      : "=r"(d)
+      : "f"(p0), "f"(p1), "f"(p2), "f"(p3));
+  return d;
+}
+// two f16x2 (four halves) -> four E4M3 bytes, element 0 of `a` in the lowest byte
+__device__ __forceinline__ uint32_t f16x4_to_e4m3x4(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("{\n.reg .b16 lo, hi;\n"
+      "cvt.rn.satfinite.e4m3x2.f16x2 lo, %1;\n"
+      "cvt.rn.satfinite.e4m3x2.f16x2 hi, %2;\n"
+      "mov.b32 %0, {lo, hi};\n}"
+      : "=r"(d)
+      : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -289,6 +311,11 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
   uint32_t d;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {  // one instruction on sm_100
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 __device__ __forceinline__ float ex2(float x) {
