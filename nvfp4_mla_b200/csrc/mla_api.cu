@@ -255,7 +255,8 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)), dim3(mla::kDecodeThreads),
+  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)),
+                            dim3(hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads),
                             decode_smem(precision, hpc), st,
                             ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));

@@ -22,13 +22,14 @@
 // by kpe_scale / (8 ckv_scale) so that one accumulator holds the whole score), K/V bytes are
 // E4M3((e2m1 x block scale) / 8) exactly as in the tokens-as-M kernel, P is E4M3 of 2^(x - m) <= 2^8.
 //
-// Warp roles (512 threads): 0-3 softmax + query load + epilogue, 4-11 dequantise, 12 QK^T issue, 13 TMA producer,
-// 14 PV issue. Every wait is bounded (ptx::mbar_wait) as in the other kernel.
+// Warp roles (640 threads): 0-7 softmax + query load + epilogue, 8-15 dequantise, 16 QK^T issue, 17 TMA producer,
+// 18 PV issue. Every wait is bounded (ptx::mbar_wait) as in the other kernel.
 #pragma once
 #include "mla_decode_sm100.cuh"
 
 namespace mla {
 
+constexpr int kHmThreads = 640;
 constexpr int kHmHeads = 128;      // heads per CTA pair = MMA M
 constexpr int kHmTile = HALF;      // tokens per tile = one staging slot
 constexpr int kHmKvBufs = 3;
@@ -45,9 +46,11 @@ struct HmSmem {
   uint64_t kv_full[kHmKvBufs];   // tile converted (8 convert warps)
   uint64_t kv_free[kHmKvBufs];   // PV of the tile (hence its QK^T too) has finished reading the buffer
   uint64_t s_full[2];            // QK^T of the tile complete
-  uint64_t p_full[2];            // P written to tensor memory (4 softmax warps)
+  uint64_t p_full[2];            // P written to tensor memory (8 softmax warps)
   uint64_t pv_done[2];           // PV of the tile complete: O may be rescaled, the S/P buffer reused
-  uint64_t q_full;               // query of the segment in place (4 softmax warps)
+  uint64_t q_full;               // query of the segment in place (8 softmax warps)
+  float xch[2][kHmHeads];        // softmax pairs: per-head maxima exchanged between a quadrant's two warps
+  float xl[2][kHmHeads];         // softmax pairs: the two halves of a head's softmax sum (segment epilogue)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -66,15 +69,15 @@ struct HmCols {
 template <int RAW_SLOTS>
 __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const int lane = ptx::lane_id();
-  const int cw = (threadIdx.x >> 5) - 4, p = cw & 3, r = (cw >> 2) * 32 + lane;
+  const int cw = (threadIdx.x >> 5) - 8, p = cw & 3, r = (cw >> 2) * 32 + lane;
   const uint32_t swz = uint32_t(r & 7) << 4;
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
       const int slot = it % RAW_SLOTS, kb = it % kHmKvBufs;
-      bool ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (it / RAW_SLOTS) & 1, &s.abort_flag));
+      bool ok = MLA_WAIT(P, 1 | (256 << 8), ptx::mbar_wait(&s.raw_full[slot], (it / RAW_SLOTS) & 1, &s.abort_flag));
       if (!__all_sync(~0u, ok)) return;
-      if (threadIdx.x == 128) MLA_TRACE_AT(P, 0, it);
+      if (threadIdx.x == 256) MLA_TRACE_AT(P, 0, it);
       const uint8_t* raw = s.raw[slot];
       const bool valid = seg.tok0 + t * kHmTile + r < seg.tok_end;
       // the 8 block scales of this panel row, the 64 packed bytes, 16 bytes of rope
@@ -88,7 +91,7 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
       // the buffer's previous tile (it - kHmKvBufs) must have been consumed
-      ok = it < kHmKvBufs || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag));
+      ok = it < kHmKvBufs || MLA_WAIT(P, 2 | (256 << 8), ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag));
       if (!__all_sync(~0u, ok)) return;
       uint8_t* out_row = s.kv[kb][p] + r * 128;
       const uint32_t words[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
@@ -123,7 +126,7 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.kv_full[kb]);
-      if (threadIdx.x == 128) MLA_TRACE_AT(P, 7, it);
+      if (threadIdx.x == 256) MLA_TRACE_AT(P, 7, it);
     }
   }
 }
@@ -193,143 +196,147 @@ __device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodePar
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// role: softmax + query load + epilogue (4 warps; thread h = head h of the group = tensor-memory lane h)
+// role: softmax + query load + epilogue (8 warps). Warp w: tensor-memory quadrant w % 4 (heads 32 (w % 4) .. + 31),
+// column half w / 4: the two warps of a quadrant share each head's tile (32 tokens each), its O row (128 columns each)
+// and its query row (256 latent channels each; the upper half also takes the rope part). A head's running max must be
+// the same in both, so the pair meets at a named barrier once per tile to vote (bar.red.or) and, only when some head
+// of the quadrant outgrows its max, a second time to exchange the maxima through shared memory.
 // ---------------------------------------------------------------------------------------------------------------
 template <int RAW_SLOTS>
 __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it, int cg) {
   const int lane = ptx::lane_id(), warp = threadIdx.x >> 5;
-  const int h = threadIdx.x;  // 0..127
-  const uint32_t tm_lane = s.tmem_base + (uint32_t(warp * 32) << 16);
+  const int quad = warp & 3, half = warp >> 2;
+  const int h = quad * 32 + lane;  // head = tensor-memory lane
+  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
+  const uint32_t pair_bar = 1 + quad;  // named barrier of this quadrant's two warps
   constexpr float kGrow = 8.f;
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
-    // ---- query of (request seg.b, head group seg.hg): this thread's row. Every MMA that read the previous segment's
-    // query has completed (this thread consumed the scores of its last tile).
+    // ---- query of (request seg.b, head group seg.hg), this head's row: channels [256 half, +256), rope with half 1.
+    // Every MMA that read the previous segment's query has completed (both warps consumed the scores of its last tile).
     const long long row = (long long)seg.b * P.heads + (long long)seg.hg * kHmHeads + h;
-    const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV);
+    const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV) + 32 * half;
     const uint4* qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE);
     const float ratio = P.kpe_scale / (8.f * P.ckv_scale);  // rope scores in units of the latent ones
-    float an = 0.f, ap = 0.f;
+    auto amax8 = [](const uint4& v, float a) {
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = fabsf(__uint_as_float(wv[j] << 16)), hi = fabsf(__uint_as_float(wv[j] & 0xFFFF0000u));
+        a = fmaxf(a, (lo < INFINITY ? lo : 0.f)), a = fmaxf(a, (hi < INFINITY ? hi : 0.f));  // ignore inf / nan for the scale
+      }
+      return a;
+    };
+    float a_loc = 0.f;
 #pragma unroll 8
-    for (int c = 0; c < CKV / 8; ++c) {
-      const uint4 v = qn[c];
-      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+    for (int c = 0; c < 32; ++c) a_loc = amax8(qn[c], a_loc);
+    if (half) {
+      float ap = 0.f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float lo = fabsf(__uint_as_float(wv[j] << 16)), hi = fabsf(__uint_as_float(wv[j] & 0xFFFF0000u));
-        an = fmaxf(an, (lo < INFINITY ? lo : 0.f)), an = fmaxf(an, (hi < INFINITY ? hi : 0.f));  // ignore inf / nan for the scale
-      }
+      for (int c = 0; c < KPE / 8; ++c) ap = amax8(qp[c], ap);
+      a_loc = fmaxf(a_loc, ap * ratio);
     }
-#pragma unroll
-    for (int c = 0; c < KPE / 8; ++c) {
-      const uint4 v = qp[c];
-      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float lo = fabsf(__uint_as_float(wv[j] << 16)), hi = fabsf(__uint_as_float(wv[j] & 0xFFFF0000u));
-        ap = fmaxf(ap, (lo < INFINITY ? lo : 0.f)), ap = fmaxf(ap, (hi < INFINITY ? hi : 0.f));
-      }
-    }
-    const float amax = fmaxf(fmaxf(an, ap * ratio), 1e-30f);
+    s.xch[half][h] = a_loc;
+    ptx::bar_sync(pair_bar, 64);
+    const float amax = fmaxf(fmaxf(s.xch[0][h], s.xch[1][h]), 1e-30f);
     const float inv_n = 448.f / amax, inv_p = ratio * inv_n;
     const float qa = P.sm_scale_log2 * P.ckv_scale * 8.f * (amax / 448.f);  // score scale of this head, log2 units
+    auto e4m3x8 = [](const uint4& v, float sc, uint32_t& o0, uint32_t& o1) {
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+      o0 = ptx::pack_e4m3x4(__uint_as_float(wv[0] << 16) * sc, __uint_as_float(wv[0] & 0xFFFF0000u) * sc,
+                            __uint_as_float(wv[1] << 16) * sc, __uint_as_float(wv[1] & 0xFFFF0000u) * sc);
+      o1 = ptx::pack_e4m3x4(__uint_as_float(wv[2] << 16) * sc, __uint_as_float(wv[2] & 0xFFFF0000u) * sc,
+                            __uint_as_float(wv[3] << 16) * sc, __uint_as_float(wv[3] & 0xFFFF0000u) * sc);
+    };
 #pragma unroll 1
-    for (int c0 = 0; c0 < CKV / 8; c0 += 8) {  // 64 channels = 16 tensor-memory columns per trip
+    for (int c0 = 0; c0 < 32; c0 += 8) {  // 64 channels = 16 tensor-memory columns per trip
       uint32_t col[16];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v = qn[c0 + c];
-        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-        uint32_t b[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          b[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(wv[j] << 16) * inv_n, __uint_as_float(wv[j] & 0xFFFF0000u) * inv_n);
-        col[2 * c] = b[0] | (b[1] << 16), col[2 * c + 1] = b[2] | (b[3] << 16);
-      }
-      ptx::tmem_st16(tm_lane + HmCols::QN + 2 * c0, col);
+      for (int c = 0; c < 8; ++c) e4m3x8(qn[c0 + c], inv_n, col[2 * c], col[2 * c + 1]);
+      ptx::tmem_st16(tm_lane + HmCols::QN + 64 * half + 2 * c0, col);
     }
+    if (half) {
 #pragma unroll
-    for (int c = 0; c < KPE / 8; c += 2) {  // 16 rope channels = one 16-byte chunk of the head's row in shared memory
-      uint32_t o[4];
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const uint4 v = qp[c + k];
-        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-        uint32_t b[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          b[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(wv[j] << 16) * inv_p, __uint_as_float(wv[j] & 0xFFFF0000u) * inv_p);
-        o[2 * k] = b[0] | (b[1] << 16), o[2 * k + 1] = b[2] | (b[3] << 16);
+      for (int c = 0; c < KPE / 8; c += 2) {  // 16 rope channels = one 16-byte chunk of the head's row in shared memory
+        uint32_t o[4];
+        e4m3x8(qp[c], inv_p, o[0], o[1]), e4m3x8(qp[c + 1], inv_p, o[2], o[3]);
+        *reinterpret_cast<uint4*>(s.qpe + h * 128 + ((uint32_t(c >> 1) << 4) ^ (uint32_t(h & 7) << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      *reinterpret_cast<uint4*>(s.qpe + h * 128 + ((uint32_t(c >> 1) << 4) ^ (uint32_t(h & 7) << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
+      ptx::fence_proxy_async_smem();
     }
     ptx::tmem_wait_st();
-    ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.q_full);
 
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;  // m is identical in the head's two threads; l is this thread's share of the sum
     const int ntiles = 2 * seg.ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
       const bool ok = MLA_WAIT(P, 8 | 32, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
-      if (!__all_sync(~0u, ok)) return;
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
-      const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile);  // columns at or beyond it are masked
-      // raw scores of this head for the tile's 64 tokens; the score scale qa > 0 is applied inside the exponent
-      uint32_t sr[kHmTile];
-      ptx::tmem_ld32(tm_lane + HmCols::s(buf), reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-      ptx::tmem_ld32(tm_lane + HmCols::s(buf) + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
-      ptx::tmem_wait_ld();
-      if (nvalid < kHmTile) {  // tail tile: masked tokens get the score -inf
+      const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile) - 32 * half;  // this warp's columns at or beyond it are masked
+      // raw scores of this head for this warp's 32 tokens; the score scale qa > 0 is applied inside the exponent
+      uint32_t sr[32];
+      if (ok) {
+        ptx::tmem_ld32(tm_lane + HmCols::s(buf) + 32 * half, sr);
+        ptx::tmem_wait_ld();
+      }
+      if (!ok || nvalid < 32) {  // tail tile: masked tokens get the score -inf
 #pragma unroll
-        for (int j = 0; j < kHmTile; ++j) sr[j] = j < nvalid ? sr[j] : 0xFF800000u;
+        for (int j = 0; j < 32; ++j) sr[j] = (ok && j < nvalid) ? sr[j] : 0xFF800000u;
       }
       float mxs[4] = {__uint_as_float(sr[0]), __uint_as_float(sr[1]), __uint_as_float(sr[2]), __uint_as_float(sr[3])};
 #pragma unroll
-      for (int j = 4; j + 8 <= kHmTile; j += 8)  // four chains of three-input maxima
+      for (int j = 4; j + 8 <= 32; j += 8)  // four chains of three-input maxima
 #pragma unroll
         for (int k = 0; k < 4; ++k) mxs[k] = ptx::max3(mxs[k], __uint_as_float(sr[j + 2 * k]), __uint_as_float(sr[j + 2 * k + 1]));
 #pragma unroll
-      for (int k = 0; k < 4; ++k) mxs[k] = fmaxf(mxs[k], __uint_as_float(sr[60 + k]));
+      for (int k = 0; k < 4; ++k) mxs[k] = fmaxf(mxs[k], __uint_as_float(sr[28 + k]));
       const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * qa;
-      const bool need = mx > m + kGrow;
-      if (__any_sync(~0u, need)) {  // tcgen05.ld / st are warp-wide: the warp rescales when any of its heads must
-        const float mn = need ? mx : m;
+      if (ptx::bar_red_or(pair_bar, 64, !ok || mx > m + kGrow)) {
+        // some head of the quadrant outgrew its max (or a wait gave up): exchange the maxima, decide per head
+        s.xch[half][h] = mx;
+        if (ptx::bar_red_or(pair_bar, 64, s.abort_flag != 0)) return;  // uniform in the pair, whoever raised the flag
+        const float mxp = fmaxf(s.xch[0][h], s.xch[1][h]);
+        const bool need = mxp > m + kGrow;
+        const float mn = need ? mxp : m;
         const float corr = need ? ((m == -INFINITY) ? 0.f : ptx::ex2(m - mn)) : 1.f;
         l *= corr, m = mn;
-        if (t > 0) {  // O holds the segment's earlier tiles: wait for the PV of tile it - 1, then scale this head's row
+        if (t > 0) {  // O holds the segment's earlier tiles: wait for the PV of tile it - 1, then scale this head's half row
           const bool okv = MLA_WAIT(P, 9 | 32, ptx::mbar_wait(&s.pv_done[buf ^ 1], ((it - 1) >> 1) & 1, &s.abort_flag));
-          if (!__all_sync(~0u, okv)) return;
+          if (ptx::bar_red_or(pair_bar, 64, !okv)) return;
           ptx::tc_fence_after_sync();
 #pragma unroll 1
-          for (int c0 = 0; c0 < 256; c0 += 32) {
+          for (int c0 = 0; c0 < 128; c0 += 32) {
             uint32_t o[32];
-            ptx::tmem_ld32(tm_lane + HmCols::O + c0, o);
+            ptx::tmem_ld32(tm_lane + HmCols::O + 128 * half + c0, o);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-            ptx::tmem_st32(tm_lane + HmCols::O + c0, o);
+            ptx::tmem_st32(tm_lane + HmCols::O + 128 * half + c0, o);
           }
           ptx::tmem_wait_st();
         }
       }
-      // P = 2^(s qa - m) as E4M3 into the first 16 columns of this S buffer (its scores are in registers now)
+      // P = 2^(s qa - m) as E4M3 into this warp's 8 of the first 16 columns of the S buffer (the scores are in registers)
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
-      uint32_t pk[16];
+      uint32_t pk[8];
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
         const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c]), qa, neg_m)), p1 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 1]), qa, neg_m));
         const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 2]), qa, neg_m)), p3 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 3]), qa, neg_m));
         ls[0] += p0, ls[1] += p1, ls[2] += p2, ls[3] += p3;
         pk[c] = ptx::pack_e4m3x4(p0, p1, p2, p3);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      ptx::tmem_st16(tm_lane + HmCols::s(buf), pk);
+      // The other warp of the pair may still be reading its scores from columns 32.. of this buffer: P occupies
+      // columns 0..15 only, and columns 0..31 are this pair's lower warp's scores, which it has read (half 0) or which
+      // the barrier above ordered (half 1 stores after the vote that half 0 joined after its load).
+      ptx::tmem_st8(tm_lane + HmCols::s(buf) + 8 * half, pk);
       ptx::tmem_wait_st();
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -337,25 +344,29 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
-    // ---- segment epilogue: wait for the last PV, write this head's 256 channels of the normalised partial
+    // ---- segment epilogue: wait for the last PV, add the two halves of the sum, write this warp's 128 of the head's
+    // 256 channels of the normalised partial
     const bool ok = ptx::mbar_wait(&s.pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);
-    if (!__all_sync(~0u, ok)) return;
+    s.xl[half][h] = l;
+    if (ptx::bar_red_or(pair_bar, 64, !ok)) return;
     ptx::tc_fence_after_sync();
-    const float inv = l > 0.f ? 8.f * P.ckv_scale / l : 0.f;
+    const float lt = s.xl[0][h] + s.xl[1][h];
+    const float inv = lt > 0.f ? 8.f * P.ckv_scale / lt : 0.f;
     const long long slot = (long long)seg.cta + seg.w;
-    float* orow = P.o_part + (slot * kHmHeads + h) * CKV + 256 * cg;
+    float* orow = P.o_part + (slot * kHmHeads + h) * CKV + 256 * cg + 128 * half;
 #pragma unroll 1
-    for (int c0 = 0; c0 < 256; c0 += 32) {
+    for (int c0 = 0; c0 < 128; c0 += 32) {
       uint32_t o[32];
-      ptx::tmem_ld32(tm_lane + HmCols::O + c0, o);
+      ptx::tmem_ld32(tm_lane + HmCols::O + 128 * half + c0, o);
       ptx::tmem_wait_ld();
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(orow + c0 + j) = make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
                                                                 __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
     }
-    if (cg == 0) P.lse_part[slot * kHmHeads + h] = l > 0.f ? m + log2f(l) : -INFINITY;
+    if (cg == 0 && half == 0) P.lse_part[slot * kHmHeads + h] = lt > 0.f ? m + log2f(lt) : -INFINITY;
     ptx::tc_fence_before_sync();
+    ptx::bar_sync(pair_bar, 64);  // s.xl and s.xch are reused by the next segment
   }
 }
 
@@ -387,7 +398,7 @@ __device__ __forceinline__ void hm_run_role(HmSmem<RAW_SLOTS>& s, const DecodePa
 }
 
 template <int RAW_SLOTS>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+__global__ void __launch_bounds__(kHmThreads, 1)
 mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_constant__ CUtensorMap sf_map,
                      const __grid_constant__ CUtensorMap kpe_map, const DecodeParams P) {
   extern __shared__ uint8_t smem_raw[];
@@ -398,13 +409,13 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 8);
     for (int i = 0; i < kHmKvBufs; ++i) ptx::mbar_init(&s.kv_full[i], 8), ptx::mbar_init(&s.kv_free[i], 1);
-    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.p_full[i], 4), ptx::mbar_init(&s.pv_done[i], 1);
-    ptx::mbar_init(&s.q_full, 4);
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.p_full[i], 8), ptx::mbar_init(&s.pv_done[i], 1);
+    ptx::mbar_init(&s.q_full, 8);
     s.abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&ckv_map), ptx::prefetch_tensormap(&sf_map), ptx::prefetch_tensormap(&kpe_map);
   }
-  if (warp == 12) {
+  if (warp == 16) {
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -414,25 +425,27 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::tc_fence_after_sync();
   ptx::grid_dependency_wait();
 
-  constexpr int kSoftmaxRegs = 184, kConvertRegs = 128;
-  static_assert(4 * kSoftmaxRegs + 8 * kConvertRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
-  if (warp < 4) {
+  // 640 threads are launched with 96 registers each (65536 / 640 rounded down to a multiple of 8); that allocation is
+  // the pool the role budgets must fit in, warp group by warp group (4 warps each): 2 softmax, 2 convert, 1 issue.
+  constexpr int kLaunchRegs = 96, kSoftmaxRegs = 104, kConvertRegs = 112, kIssueRegs = 48;
+  static_assert(8 * kSoftmaxRegs + 8 * kConvertRegs + 4 * kIssueRegs <= 20 * kLaunchRegs, "register budgets exceed the CTA's allocation");
+  if (warp < 8) {
     ptx::reg_alloc<kSoftmaxRegs>();
     hm_run_role<RAW_SLOTS, kRoleSoftmax>(s, P, &ckv_map, &sf_map, &kpe_map);
-  } else if (warp < 12) {
+  } else if (warp < 16) {
     ptx::reg_alloc<kConvertRegs>();
     hm_run_role<RAW_SLOTS, kRoleConvert>(s, P, &ckv_map, &sf_map, &kpe_map);
   } else {
-    ptx::reg_dealloc<64>();
-    if (warp == 12) hm_run_role<RAW_SLOTS, kRoleQk>(s, P, &ckv_map, &sf_map, &kpe_map);
-    else if (warp == 13) hm_run_role<RAW_SLOTS, kRoleProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
-    else if (warp == 14) hm_run_role<RAW_SLOTS, kRolePv>(s, P, &ckv_map, &sf_map, &kpe_map);
+    ptx::reg_dealloc<kIssueRegs>();
+    if (warp == 16) hm_run_role<RAW_SLOTS, kRoleQk>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 17) hm_run_role<RAW_SLOTS, kRoleProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 18) hm_run_role<RAW_SLOTS, kRolePv>(s, P, &ckv_map, &sf_map, &kpe_map);
     else hm_run_role<RAW_SLOTS, kRoleIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
   }
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
+  if (warp == 16) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }
 
