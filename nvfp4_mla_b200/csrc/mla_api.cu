@@ -2,6 +2,7 @@
 // Declarations and their documentation: include/nvfp4_mla_b200.h.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -39,6 +40,7 @@ constexpr int kMaxDevices = 64;
 struct DeviceInfo {
   bool ready = false;
   int sm_count = 0;
+  int hm_pairs = 0;  // CTA pairs (clusters of two) of the heads-as-M kernel that can be resident at once; 0 = do not use it
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[kMaxDevices];
@@ -46,31 +48,32 @@ DeviceInfo g_devices[kMaxDevices];
 using DecodeKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const mla::DecodeParams);
 // staging slots of 64 tokens next to the V tile (one FP16 tile of 128 KB, or two E4M3 tiles of 64 KB)
 constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
+constexpr int kRawSlotsHm = 4;  // heads-as-M kernel: staging slots of 32 tokens
 // Heads per CTA (the N of both MMAs). One conversion of a tile serves all of the CTA's heads, so more heads per CTA
 // means less conversion work per head; 32 fit next to the tiles only in the 8-bit mode (tensor memory and shared memory).
 // With 128 heads per request the 8-bit mode runs the heads-as-M kernel: a pair of CTAs per 128 heads (each CTA
 // accumulates half of the output channels), scheduled as one unit, so the schedule sees half as many "CTAs".
-int heads_per_cta(int heads, int precision) {
+int heads_per_cta(int heads, int precision, const DeviceInfo& d) {
   if (precision != NVFP4_MLA_PRECISION_FP8) return 16;
-  return heads % 128 == 0 ? 128 : heads % 32 == 0 ? 32 : 16;
+  return heads % 128 == 0 && d.hm_pairs > 0 ? 128 : heads % 32 == 0 ? 32 : 16;
 }
-int schedule_units(int sm_count, int hpc) { return hpc == 128 ? sm_count / 2 : sm_count; }
+int schedule_units(const DeviceInfo& d, int hpc) { return hpc == 128 ? d.hm_pairs : d.sm_count; }
 int ctas_per_unit(int hpc) { return hpc == 128 ? 2 : 1; }
 DecodeKernel decode_kernel(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
-    return hpc == 128  ? mla::mla_decode_hm_kernel<kRawSlots8>
+    return hpc == 128  ? mla::mla_decode_hm_kernel<kRawSlotsHm>
            : hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true>
                        : mla::mla_decode_kernel<16, kRawSlots8, true>;
   return mla::mla_decode_kernel<16, kRawSlots16, false>;
 }
 size_t decode_smem(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
-    return hpc == 128  ? mla::hm_smem_bytes<kRawSlots8>()
+    return hpc == 128  ? mla::hm_smem_bytes<kRawSlotsHm>()
            : hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>()
                        : mla::decode_smem_bytes<16, kRawSlots8, true>();
   return mla::decode_smem_bytes<16, kRawSlots16, false>();
 }
-static_assert(mla::hm_smem_bytes<kRawSlots8>() <= 232448, "heads-as-M kernel exceeds the shared memory a CTA can opt in to");
+static_assert(mla::hm_smem_bytes<kRawSlotsHm>() <= 232448, "heads-as-M kernel exceeds the shared memory a CTA can opt in to");
 static_assert(mla::decode_smem_bytes<32, kRawSlots8, true>() <= 232448 && mla::decode_smem_bytes<16, kRawSlots8, true>() <= 232448 &&
                   mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448,
               "decode kernel exceeds the 227 KB of shared memory a CTA can opt in to");
@@ -91,6 +94,23 @@ int device_info(DeviceInfo** out) {
       for (int hpc : {16, 32, 128})
         MLA_CUDA(cudaFuncSetAttribute(decode_kernel(prec, hpc), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       int(decode_smem(prec, hpc))));
+    {  // clusters of two need both SMs in one GPC: ask how many can be resident rather than assuming sm_count / 2
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(unsigned(d.sm_count / 2 * 2)), cfg.blockDim = dim3(mla::kHmThreads);
+      cfg.dynamicSmemBytes = decode_smem(NVFP4_MLA_PRECISION_FP8, 128);
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr, cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, decode_kernel(NVFP4_MLA_PRECISION_FP8, 128), &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        clusters = 0;
+      }
+      d.hm_pairs = clusters < d.sm_count / 2 ? clusters : d.sm_count / 2;
+      if (getenv("NVFP4_MLA_DEBUG"))
+        fprintf(stderr, "nvfp4_mla_b200: device %d: %d SMs, %d resident CTA pairs for the 128-head kernel\n", dev, d.sm_count, d.hm_pairs);
+    }
     d.ready = true;
   }
   *out = &d;
@@ -117,14 +137,14 @@ int encode_fn(EncodeTiledFn* out) {
 // ckv_cache as a 2-D byte tensor [num_pages * page_size, 256]; a box is min(page_size, 64) token rows by 128 bytes,
 // written to shared memory with the 128-byte swizzle that makes thread-per-token reads conflict free.
 // 2-D byte map over one of the cache tensors seen as [rows = pages * page_size, row_bytes]; a box is `box_bytes` of up
-// to 64 rows (one staging slot, or one page if pages are smaller), written to shared memory with the given swizzle.
-int make_row_map(const uint8_t* base, int64_t rows, int row_bytes, int box_bytes, int page_size, CUtensorMapSwizzle swizzle,
-                 CUtensorMap* map) {
+// to `slot_rows` rows (one staging slot, or one page if pages are smaller), written to shared memory with the given swizzle.
+int make_row_map(const uint8_t* base, int64_t rows, int row_bytes, int box_bytes, int page_size, int slot_rows,
+                 CUtensorMapSwizzle swizzle, CUtensorMap* map) {
   EncodeTiledFn encode;
   if (encode_fn(&encode)) return 1;
   const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
-  const cuuint32_t box[2] = {cuuint32_t(box_bytes), cuuint32_t(page_size < mla::HALF ? page_size : mla::HALF)};
+  const cuuint32_t box[2] = {cuuint32_t(box_bytes), cuuint32_t(page_size < slot_rows ? page_size : slot_rows)};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -143,15 +163,26 @@ thread_local Profile* g_profile = nullptr;
 // Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream is still
 // running; it must execute griddepcontrol.wait before touching anything the predecessor writes. Used for the
 // schedule -> decode -> combine chain so that launch latency and prologues overlap the previous kernel.
+// `cluster` > 1 launches thread-block clusters of that many consecutive CTAs (the grid must be a multiple of it).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+cudaError_t launch_dependent_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cluster,
+                                     Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = 1;
+  if (cluster > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return launch_dependent_cluster(kernel, grid, block, smem, st, 1u, static_cast<Args&&>(args)...);
 }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -191,8 +222,8 @@ int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
   size_t need = 0;
   for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8}) {
     mla::Problem pb;
-    const int hpc = heads_per_cta(heads, prec);
-    if (problem_of(batch, heads, 1, num_splits, schedule_units(d->sm_count, hpc), hpc, &pb)) return -1;
+    const int hpc = heads_per_cta(heads, prec, *d);
+    if (problem_of(batch, heads, 1, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
     const size_t n = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total;
     need = n > need ? n : need;
   }
@@ -219,17 +250,18 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   DeviceInfo* d;
   if (device_info(&d)) return 1;
   mla::Problem pb;
-  const int hpc = heads_per_cta(heads, precision);
-  if (problem_of(batch, heads, max_kv_len, num_splits, schedule_units(d->sm_count, hpc), hpc, &pb)) return 1;
+  const int hpc = heads_per_cta(heads, precision, *d);
+  if (problem_of(batch, heads, max_kv_len, num_splits, schedule_units(*d, hpc), hpc, &pb)) return 1;
   if (batch == 0) return 0;
   const mla::WsLayout L = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta);
   MLA_CHECK(workspace_bytes >= int64_t(L.total), "workspace too small: %lld bytes given, %lld needed", (long long)workspace_bytes,
             (long long)L.total);
 
   CUtensorMap ckv_map, sf_map, kpe_map;
-  if (make_row_map(ckv_cache, num_pages * page_size, 256, 128, page_size, CU_TENSOR_MAP_SWIZZLE_128B, &ckv_map)) return 1;
-  if (make_row_map(ckv_sf_cache, num_pages * page_size, 32, 32, page_size, CU_TENSOR_MAP_SWIZZLE_32B, &sf_map)) return 1;
-  if (make_row_map(kpe_cache, num_pages * page_size, 64, 64, page_size, CU_TENSOR_MAP_SWIZZLE_64B, &kpe_map)) return 1;
+  const int slot_rows = hpc == 128 ? mla::kHmRows : mla::HALF;  // tokens per staging slot of the kernel that will run
+  if (make_row_map(ckv_cache, num_pages * page_size, 256, 128, page_size, slot_rows, CU_TENSOR_MAP_SWIZZLE_128B, &ckv_map)) return 1;
+  if (make_row_map(ckv_sf_cache, num_pages * page_size, 32, 32, page_size, slot_rows, CU_TENSOR_MAP_SWIZZLE_32B, &sf_map)) return 1;
+  if (make_row_map(kpe_cache, num_pages * page_size, 64, 64, page_size, slot_rows, CU_TENSOR_MAP_SWIZZLE_64B, &kpe_map)) return 1;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* header = reinterpret_cast<int*>(ws + L.header);
@@ -247,7 +279,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
   P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
   P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads;
-  P.sf_swz_mask = page_size >= mla::HALF ? 1u : 0u, P.kpe_swz_mask = page_size >= mla::HALF ? 3u : 0u;
+  P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
 #ifdef MLA_TRACE
@@ -255,10 +287,9 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
 #endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
-  MLA_CUDA(launch_dependent(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)),
-                            dim3(hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads),
-                            decode_smem(precision, hpc), st,
-                            ckv_map, sf_map, kpe_map, P));
+  MLA_CUDA(launch_dependent_cluster(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)),
+                                    dim3(hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads), decode_smem(precision, hpc), st,
+                                    unsigned(ctas_per_unit(hpc)), ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 
   // few rows: four thread groups share a row's partials; many rows: one group per row keeps the CTAs small

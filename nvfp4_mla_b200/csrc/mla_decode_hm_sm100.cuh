@@ -9,10 +9,13 @@
 //   PV   : O[head, chan]  += P[head, token] . V     A = P (E4M3) from tensor memory, written there by the softmax threads,
 //                                                   B = the same K/V tile read MN-major, N = 256 channels, K = 32 tokens
 // One dequantised copy of a token in shared memory feeds both MMAs; nothing of K or V passes through tensor memory.
-// O for 128 heads x 512 channels would need all 512 tensor-memory columns, so a PAIR of CTAs shares a request: both
-// compute the full scores, CTA `cg` of the pair accumulates channels [256 cg, 256 cg + 256). The pair gets the same
-// segments from the schedule (which is run over pairs) and writes one partial slot, so the combine kernel is unchanged.
-// The two CTAs are independent (no cluster); the second reader of a cache line finds it in L2.
+// O for 128 heads x 512 channels would need all 512 tensor-memory columns, so a PAIR of CTAs (a cluster of two) shares
+// a request: both compute the full scores, CTA `cg` of the pair accumulates channels [256 cg, 256 cg + 256). The pair
+// gets the same segments from the schedule (which is run over pairs) and writes one partial slot, so the combine
+// kernel is unchanged. The conversion is shared: CTA `cg` loads and dequantises tokens [32 cg, 32 cg + 32) of every
+// 64-token tile, writes them into its own K/V tile and sends the same bytes to its peer's tile with bulk copies through
+// distributed shared memory, which count as transaction bytes on the peer's "tile converted" barrier. A tile buffer
+// is reused when the PV of both CTAs has finished with it (a relay warp forwards the local completion to the peer).
 //
 // Tensor memory (512 columns): Q latent 0..127 | S buffer 0: 128..191 | S buffer 1: 192..255 | O: 256..511.
 // P of a tile overwrites the first 16 columns of the S buffer it was computed from.
@@ -32,19 +35,26 @@ namespace mla {
 constexpr int kHmThreads = 640;
 constexpr int kHmHeads = 128;      // heads per CTA pair = MMA M
 constexpr int kHmTile = HALF;      // tokens per tile = one staging slot
-constexpr int kHmKvBufs = 3;
+constexpr int kHmRows = kHmTile / 2;  // token rows one CTA of the pair loads and converts per tile
+constexpr int kHmKvBufs = 4;
 constexpr int kHmPanelBytes = kHmTile * 128;  // one 128-channel panel of the E4M3 K/V tile
+// staging slot of kHmRows tokens: ckv low halves | ckv high halves | block scales | rope
+constexpr int kHmRawCkvHi = kHmRows * 128, kHmRawSf = 2 * kHmRows * 128, kHmRawKpe = kHmRawSf + kHmRows * 32;
+constexpr int kHmRawSlotBytes = kHmRows * TOKEN_BYTES;
+constexpr uint32_t kHmPeerBytes = 8 * 2048 + 2 * 2048;  // what the peer sends per tile: 8 latent + 2 rope regions of 2 KB
+static_assert(kHmRawSlotBytes % 1024 == 0 && kHmRawSf % 256 == 0 && kHmRawKpe % 512 == 0, "staging slot alignment");
 
 template <int RAW_SLOTS>
 struct HmSmem {
   alignas(1024) uint8_t kv[kHmKvBufs][5][kHmPanelBytes];  // panels 0..3: latent channels, panel 4: rope (64 of 128 bytes per row)
   alignas(1024) uint8_t qpe[kHmHeads * 128];              // rope part of Q, E4M3, row = head (64 of 128 bytes used)
-  alignas(1024) uint8_t raw[RAW_SLOTS][kRawSlotBytes];
+  alignas(1024) uint8_t raw[RAW_SLOTS][kHmRawSlotBytes];
   Seg segs[kSegBatch];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
-  uint64_t kv_full[kHmKvBufs];   // tile converted (8 convert warps)
-  uint64_t kv_free[kHmKvBufs];   // PV of the tile (hence its QK^T too) has finished reading the buffer
+  uint64_t kv_full[kHmKvBufs];   // tile converted: 8 local convert warps + kHmPeerBytes from the peer CTA
+  uint64_t kv_free[kHmKvBufs];   // PV of the tile (hence its QK^T too) has finished reading the buffer in BOTH CTAs (2 arrivals)
+  uint64_t pv_local[kHmKvBufs];  // this CTA's PV of the tile is complete (relay warp forwards it to both kv_free)
   uint64_t s_full[2];            // QK^T of the tile complete
   uint64_t p_full[2];            // P written to tensor memory (8 softmax warps)
   uint64_t pv_done[2];           // PV of the tile complete: O may be rescaled, the S/P buffer reused
@@ -63,14 +73,81 @@ struct HmCols {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
-// role: dequantise (8 warps). Warp cw: panel cw % 4 (128 channels), token rows 32 (cw / 4) .. + 31; thread = one row of
-// one panel: 64 packed bytes in, 128 E4M3 bytes out, plus a 16-byte piece of the row's rope bytes.
+// role: TMA producer: this CTA's kHmRows token rows of every tile
 // ---------------------------------------------------------------------------------------------------------------
 template <int RAW_SLOTS>
-__device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+__device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, const CUtensorMap* ckv_map,
+                                                 const CUtensorMap* sf_map, const CUtensorMap* kpe_map, int n_segs, uint32_t& it, int cg) {
   const int lane = ptx::lane_id();
-  const int cw = (threadIdx.x >> 5) - 8, p = cw & 3, r = (cw >> 2) * 32 + lane;
-  const uint32_t swz = uint32_t(r & 7) << 4;
+  const int ps = 1 << P.page_shift;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    const int* pt = P.page_table + (long long)seg.b * P.pt_stride;
+    for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
+      const int slot = it % RAW_SLOTS;
+      const uint32_t use = it / RAW_SLOTS;
+      bool ok = MLA_WAIT(P, 0, ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag));
+      if (!__all_sync(~0u, ok)) return;
+      const int tok = seg.tok0 + t * kHmTile + kHmRows * cg;
+      int nvalid = seg.tok_end - tok;
+      nvalid = nvalid < 0 ? 0 : (nvalid > kHmRows ? kHmRows : nvalid);
+      uint8_t* dst = s.raw[slot];
+      uint64_t* bar = &s.raw_full[slot];
+      if (nvalid == 0) {
+        if (lane == 0) ptx::mbar_arrive(bar);
+      } else if (ps >= kHmRows) {
+        if (lane == 0) {
+          const int page = pt[tok >> P.page_shift];
+          const int row = (page << P.page_shift) + (tok & (ps - 1));
+          ptx::mbar_arrive_expect_tx(bar, kHmRows * TOKEN_BYTES);
+          ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kHmRawCkvHi, ckv_map, 128, row, bar);
+          ptx::tma_load_2d(dst + kHmRawSf, sf_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kHmRawKpe, kpe_map, 0, row, bar);
+          const int tok_pf = tok + 4 * kHmTile;  // L2 prefetch a few tiles ahead
+          if (tok_pf < seg.tok_end) {
+            const int page2 = pt[tok_pf >> P.page_shift];
+            const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
+            ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
+            ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+          }
+        }
+      } else {
+        // small pages: one box per page that holds a valid token, lanes share the pages; scales and rope arrive unswizzled
+        const int npages = (nvalid + ps - 1) >> P.page_shift;
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(npages) * ps * TOKEN_BYTES);
+        __syncwarp();
+        for (int pi = lane; pi < npages; pi += 32) {
+          const int page = pt[(tok >> P.page_shift) + pi];
+          const int row = page << P.page_shift, r0 = pi << P.page_shift;
+          ptx::tma_load_2d(dst + r0 * 128, ckv_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kHmRawCkvHi + r0 * 128, ckv_map, 128, row, bar);
+          ptx::bulk_load(dst + kHmRawSf + r0 * 32, P.sf + (long long)row * 32, ps * 32, bar);
+          ptx::bulk_load(dst + kHmRawKpe + r0 * 64, P.kpe + (long long)row * 64, ps * 64, bar);
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: dequantise (8 warps) this CTA's 32 token rows of every tile, into its own tile and the peer's. Warp cw: panel
+// cw % 4 (128 channels), rows 16 (cw / 4) .. + 15 of the CTA's 32; two threads per row (64 channels each). A warp's
+// output is 16 consecutive 128-byte rows of one panel, 2 KB, which one bulk copy forwards to the peer. The warps of
+// panel 0 also move their rows' rope bytes.
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const DecodeParams& P, int n_segs, uint32_t& it, int cg) {
+  const int lane = ptx::lane_id();
+  const int cw = (threadIdx.x >> 5) - 8, p = cw & 3, hh = lane & 1;
+  const int r = (cw >> 2) * 16 + (lane >> 1);  // row in the staging slot
+  const int R = kHmRows * cg + r;              // row in the tile
+  const uint32_t swz = uint32_t(r & 7) << 4;   // = (R & 7) << 4
+  const uint32_t peer = uint32_t(cg ^ 1);
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
@@ -79,34 +156,36 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
       if (!__all_sync(~0u, ok)) return;
       if (threadIdx.x == 256) MLA_TRACE_AT(P, 0, it);
       const uint8_t* raw = s.raw[slot];
-      const bool valid = seg.tok0 + t * kHmTile + r < seg.tok_end;
-      // the 8 block scales of this panel row, the 64 packed bytes, 16 bytes of rope
-      const uint2 sf8 = *reinterpret_cast<const uint2*>(raw + kRawSf + r * 32 + ((uint32_t(p >> 1) ^ ((r >> 2) & P.sf_swz_mask)) << 4) +
-                                                        (p & 1) * 8);
-      const uint8_t* half_row = raw + (p >> 1) * kRawCkvHi + r * 128;
-      uint4 w[4];
+      const bool valid = seg.tok0 + t * kHmTile + R < seg.tok_end;
+      const bool full = seg.tok0 + (t + 1) * kHmTile <= seg.tok_end;  // warp-uniform: a live tile skips the masking
+      // the 4 block scales of this thread's 64 channels, their 32 packed bytes, and (panel 0) 32 bytes of rope
+      const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(raw + kHmRawSf + r * 32 + ((uint32_t(p >> 1) ^ ((r >> 2) & P.sf_swz_mask)) << 4) +
+                                                              (p & 1) * 8 + 4 * hh);
+      const uint8_t* half_row = raw + (p >> 1) * kHmRawCkvHi + r * 128;
+      uint4 w[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(half_row + ((uint32_t((p & 1) * 4 + i) << 4) ^ swz));
-      const uint4 rope = *reinterpret_cast<const uint4*>(raw + kRawKpe + r * 64 + ((uint32_t(p) ^ ((r >> 1) & P.kpe_swz_mask)) << 4));
+      for (int i = 0; i < 2; ++i) w[i] = *reinterpret_cast<const uint4*>(half_row + ((uint32_t((p & 1) * 4 + 2 * hh + i) << 4) ^ swz));
+      uint4 rope[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      if (p == 0) {
+        const uint32_t kswz = (r >> 1) & P.kpe_swz_mask;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) rope[i] = *reinterpret_cast<const uint4*>(raw + kHmRawKpe + r * 64 + ((uint32_t(2 * hh + i) ^ kswz) << 4));
+      }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
-      // the buffer's previous tile (it - kHmKvBufs) must have been consumed
+      // the buffer's previous tile (it - kHmKvBufs) must have been consumed by the PV of both CTAs
       ok = it < kHmKvBufs || MLA_WAIT(P, 2 | (256 << 8), ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag));
       if (!__all_sync(~0u, ok)) return;
-      uint8_t* out_row = s.kv[kb][p] + r * 128;
-      const uint32_t words[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
-                                  w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
-      // rows past the end of the request become zeros (a live tile skips the masking: `full` is warp-uniform)
-      const bool full = seg.tok0 + (t + 1) * kHmTile <= seg.tok_end;
-      const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
+      uint8_t* out_row = s.kv[kb][p] + R * 128;
+      const uint32_t words[8] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w};
+      const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;  // rows past the end of the request become zeros
 #pragma unroll
-      for (int c2 = 0; c2 < 4; ++c2) {  // two 16-byte chunks (= two scale blocks) per trip
-        const uint32_t sfw = c2 < 2 ? sf8.x : sf8.y;
-        uint32_t s2 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> (16 * (c2 & 1))));  // (scale of chunk 2 c2, of chunk 2 c2 + 1)
-        s2 = ptx::hmul2(s2, 0x30003000u);                                        // x 1/8, exact
+      for (int c2 = 0; c2 < 2; ++c2) {  // two 16-byte chunks (= two scale blocks) per trip
+        uint32_t s2 = ptx::e4m3x2_to_f16x2(uint16_t(sf4 >> (16 * c2)));  // (scale of chunk 2 c2, of chunk 2 c2 + 1)
+        s2 = ptx::hmul2(s2, 0x30003000u);                                  // x 1/8, exact
         const uint32_t sc[2] = {__byte_perm(s2, s2, 0x1010), __byte_perm(s2, s2, 0x3232)};
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {  // 16-byte chunk c = channels [16c, 16c + 16) of the panel
+        for (int k = 0; k < 2; ++k) {  // chunk c of this thread = channels [64 hh + 16 c, + 16) of the panel
           const int c = 2 * c2 + k;
           uint32_t o[4];
 #pragma unroll
@@ -117,16 +196,49 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
             o[2 * j + 1] = ptx::f16x4_to_e4m3x4(ptx::hmul2(e[2], sc[k]), ptx::hmul2(e[3], sc[k]));
           }
           if (!full) o[0] &= vmask, o[1] &= vmask, o[2] &= vmask, o[3] &= vmask;
-          *reinterpret_cast<uint4*>(out_row + ((uint32_t(c) << 4) ^ swz)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(out_row + ((uint32_t(4 * hh + c) << 4) ^ swz)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
-      // rope bytes are E4M3 already: chunk p of the row's 64 bytes
-      *reinterpret_cast<uint4*>(s.kv[kb][4] + r * 128 + ((uint32_t(p) << 4) ^ swz)) =
-          valid ? rope : make_uint4(0, 0, 0, 0);
+      if (p == 0) {  // rope bytes are E4M3 already: chunks 2 hh, 2 hh + 1 of the row's 64 bytes
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<uint4*>(s.kv[kb][4] + R * 128 + ((uint32_t(2 * hh + i) << 4) ^ swz)) = valid ? rope[i] : make_uint4(0, 0, 0, 0);
+      }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.kv_full[kb]);
+      if (lane == 0) {
+        // the peer's tile gets the same bytes; they complete on its kv_full as transaction bytes
+        const uint8_t* src = s.kv[kb][p] + (kHmRows * cg + (cw >> 2) * 16) * 128;
+        const uint32_t peer_bar = ptx::map_to_cta(&s.kv_full[kb], peer);
+        ptx::bulk_copy_to_cta(ptx::map_to_cta(src, peer), src, 2048, peer_bar);
+        if (p == 0) {
+          const uint8_t* rsrc = s.kv[kb][4] + (kHmRows * cg + (cw >> 2) * 16) * 128;
+          ptx::bulk_copy_to_cta(ptx::map_to_cta(rsrc, peer), rsrc, 2048, peer_bar);
+        }
+        if (cw == 0) ptx::mbar_arrive_expect_tx(&s.kv_full[kb], kHmPeerBytes);  // what the peer will send for this tile
+        else ptx::mbar_arrive(&s.kv_full[kb]);
+      }
       if (threadIdx.x == 256) MLA_TRACE_AT(P, 7, it);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: relay (1 warp): when this CTA's PV of a tile is complete, release the tile buffer in both CTAs
+// ---------------------------------------------------------------------------------------------------------------
+template <int RAW_SLOTS>
+__device__ __forceinline__ void hm_relay_role(HmSmem<RAW_SLOTS>& s, int n_segs, uint32_t& it, int cg) {
+  const int lane = ptx::lane_id();
+  for (int si = 0; si < n_segs; ++si) {
+    const int ntiles = 2 * s.segs[si].ntiles;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t kb = it % kHmKvBufs;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.pv_local[kb], (it / kHmKvBufs) & 1, &s.abort_flag))) return;
+      if (lane == 0) {
+        ptx::mbar_arrive(&s.kv_free[kb]);
+        ptx::mbar_arrive_cta(ptx::map_to_cta(&s.kv_free[kb], uint32_t(cg ^ 1)));
+      }
+      __syncwarp();
     }
   }
 }
@@ -188,7 +300,7 @@ __device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodePar
         for (int ks = 0; ks < 2; ++ks)
           ptx::mma_f8_ts(tm + HmCols::O, tm + HmCols::s(buf) + 8 * ks, v_desc + ((ks * 32 * 128) >> 4), idesc, (t | ks) != 0);
         ptx::mma_commit(&s.pv_done[buf]);
-        ptx::mma_commit(&s.kv_free[kb]);
+        ptx::mma_commit(&s.pv_local[kb]);
       }
       __syncwarp();
     }
@@ -284,6 +396,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
         ptx::tmem_ld32(tm_lane + HmCols::s(buf) + 32 * half, sr);
         ptx::tmem_wait_ld();
       }
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       if (!ok || nvalid < 32) {  // tail tile: masked tokens get the score -inf
 #pragma unroll
         for (int j = 0; j < 32; ++j) sr[j] = (ok && j < nvalid) ? sr[j] : 0xFF800000u;
@@ -321,6 +434,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
           ptx::tmem_wait_st();
         }
       }
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
       // P = 2^(s qa - m) as E4M3 into this warp's 8 of the first 16 columns of the S buffer (the scores are in registers)
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       uint32_t pk[8];
@@ -336,8 +450,10 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       // The other warp of the pair may still be reading its scores from columns 32.. of this buffer: P occupies
       // columns 0..15 only, and columns 0..31 are this pair's lower warp's scores, which it has read (half 0) or which
       // the barrier above ordered (half 1 stores after the vote that half 0 joined after its load).
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
       ptx::tmem_st8(tm_lane + HmCols::s(buf) + 8 * half, pk);
       ptx::tmem_wait_st();
+      if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
@@ -378,7 +494,7 @@ __device__ __forceinline__ void hm_run_role(HmSmem<RAW_SLOTS>& s, const DecodePa
                                             const CUtensorMap* sf_map, const CUtensorMap* kpe_map) {
   const int pair = blockIdx.x >> 1, cg = blockIdx.x & 1;
   const int2 range = P.cta_range[pair];
-  uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
+  uint32_t it = 0, seg_count = 0;  // every role advances its own copies identically
   for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
     const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
     if (ROLE == kRoleSoftmax && int(threadIdx.x) < n_segs) {
@@ -388,9 +504,10 @@ __device__ __forceinline__ void hm_run_role(HmSmem<RAW_SLOTS>& s, const DecodePa
     }
     __syncthreads();
     if (ROLE == kRoleSoftmax) hm_softmax_role<RAW_SLOTS>(s, P, n_segs, it, cg);
-    if (ROLE == kRoleConvert) hm_convert_role<RAW_SLOTS>(s, P, n_segs, it);
+    if (ROLE == kRoleConvert) hm_convert_role<RAW_SLOTS>(s, P, n_segs, it, cg);
     if (ROLE == kRoleQk) hm_qk_role<RAW_SLOTS>(s, P, n_segs, it, seg_count);
-    if (ROLE == kRoleProducer) producer_role<RAW_SLOTS>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
+    if (ROLE == kRoleProducer) hm_producer_role<RAW_SLOTS>(s, P, ckv_map, sf_map, kpe_map, n_segs, it, cg);
+    if (ROLE == kRoleIdle) hm_relay_role<RAW_SLOTS>(s, n_segs, it, cg);
     if (ROLE == kRolePv) hm_pv_role<RAW_SLOTS>(s, P, n_segs, it, cg);
     __syncthreads();
     if (s.abort_flag) break;
@@ -408,7 +525,8 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 8);
-    for (int i = 0; i < kHmKvBufs; ++i) ptx::mbar_init(&s.kv_full[i], 8), ptx::mbar_init(&s.kv_free[i], 1);
+    for (int i = 0; i < kHmKvBufs; ++i)
+      ptx::mbar_init(&s.kv_full[i], 8), ptx::mbar_init(&s.kv_free[i], 2), ptx::mbar_init(&s.pv_local[i], 1);
     for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.p_full[i], 8), ptx::mbar_init(&s.pv_done[i], 1);
     ptx::mbar_init(&s.q_full, 8);
     s.abort_flag = 0;
@@ -421,7 +539,7 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   }
   ptx::grid_launch_dependents();
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  ptx::cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
   ptx::tc_fence_after_sync();
   ptx::grid_dependency_wait();
 
@@ -444,7 +562,7 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   }
 
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  ptx::cluster_sync();  // neither CTA leaves while the other may still write to its shared memory or signal its barriers
   if (warp == 16) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }

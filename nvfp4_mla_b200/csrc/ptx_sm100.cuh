@@ -124,6 +124,36 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// thread-block clusters: distributed shared memory between the CTAs of one cluster (same GPU)
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the peer CTA's copy of a shared-memory location of this CTA
+__device__ __forceinline__ uint32_t map_to_cta(const void* local, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(cta_rank));
+  return r;
+}
+// all threads of all CTAs of the cluster; orders shared-memory accesses (incl. mbarrier initialisation) before / after
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bulk copy from this CTA's shared memory into a peer CTA's (asynchronous proxy on both ends): `bytes` (multiple of 16,
+// both addresses 16-byte aligned) are counted on the PEER's mbarrier as completed transaction bytes.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, const void* src_local, uint32_t bytes, uint32_t mbar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(smem_u32(src_local)), "r"(bytes), "r"(mbar_cluster_addr)
+               : "memory");
+}
+// arrive on a peer CTA's mbarrier (address from map_to_cta); this thread's earlier writes are released to the cluster
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t mbar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(mbar_cluster_addr) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // tensor memory
 // ---------------------------------------------------------------------------------------------------------------
 // A TMEM address is (lane << 16) | column. A warp may touch only lanes [32 * (warp_id % 4), +32).

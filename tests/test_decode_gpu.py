@@ -248,3 +248,49 @@ def test_config1_shape_streamed_reference():
     o_split = mla.decode_partial(*c.args(), max_kv_len=8192, num_splits=5)[0]
     assert (o_split - o32).abs().max().item() <= 1e-3   # property: the result does not depend on the split
     check_status()
+
+
+HM_CASES = [  # the 128-head 8-bit kernel (heads as M, CTA pairs): lengths around its 64-token tile, 256 heads, empty requests
+    ([1, 31, 32, 33, 63, 64, 65, 127, 128, 129], 64, 128),
+    ([0, 700, 0, 2050], 32, 128),
+    ([300, 5000], 16, 256),
+    ([9000], 128, 128),
+    ([40, 3], 4, 128),
+]
+
+
+@pytest.mark.parametrize("num_splits", [0, 1, 7])
+@pytest.mark.parametrize("kv_lens,page_size,heads", HM_CASES)
+def test_decode_fp8_128_heads(num_splits, kv_lens, page_size, heads):
+    c = SyntheticCache(kv_lens, page_size, heads, 2.0 ** -9, 2.0 ** -6, seed=3 + len(kv_lens), keep_bf16=True).to("cuda")
+    out = mla.decode(*c.args(), max_kv_len=c.max_kv_len, num_splits=num_splits, precision="fp8")
+    out16 = mla.decode(*c.args(), max_kv_len=c.max_kv_len, num_splits=num_splits)
+    check_status()
+    assert not out.isnan().any()
+    want, _ = oracle_reference(c)
+    got = out.float().cpu().numpy()
+    live = [b for b, L in enumerate(kv_lens) if L > 0]
+    for b, L in enumerate(kv_lens):
+        if L == 0:
+            assert (got[b] == 0).all()
+    assert O.rel_l2(got[live], want[live]) < 0.08
+    ref = c.reference_bf16().cpu().numpy()
+    assert O.rel_l2(got[live], ref[live]) < 1.2 * O.rel_l2(out16.float().cpu().numpy()[live], ref[live])
+
+
+def test_cuda_graph_replay_fp8_128_heads():
+    """The 128-head kernel launches clusters of two CTAs with a programmatic dependency: it must capture and replay."""
+    c = SyntheticCache([1500, 2048], 64, 128, 0.5, 2.0, seed=12, device="cuda")  # replayed with shorter lengths below
+    args = c.args()
+    mla.decode(*args, max_kv_len=2048, precision="fp8")  # set-up outside capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = mla.decode(*args, max_kv_len=2048, precision="fp8")
+    c.kv_lens.copy_(torch.tensor([700, 2000], dtype=torch.int32))
+    g.replay()
+    torch.cuda.synchronize()
+    c.kv_lens_list = [700, 2000]
+    want, _ = oracle_reference(c)
+    assert O.rel_l2(out.float().cpu().numpy(), want) < 0.08
+    check_status()
