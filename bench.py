@@ -329,6 +329,7 @@ def main():
         qsrc = SyntheticCache([ps] * B, ps, H, 1.0, 1.0, seed=7, device=dev)
         cache.q_nope, cache.q_pe = qsrc.q_nope, qsrc.q_pe
         config["parallelism"] = f"sequence-sharded over {world} GPU(s): local split-KV decode, all-gather of (o, lse), merge"
+        config["workload"] = config["workload"].replace(f"B={B} per GPU", f"B={B} in total (queries replicated, each rank holds 1/{world} of every context)")
         kv_len_local = local_len
     else:
         cache = SyntheticCache(request_lengths(kv_len, B, rank), ps, H, None, None, seed=rank, device=dev)
@@ -449,15 +450,16 @@ def main():
     peak, peak_kind = measured_peak()
     achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
     tokens = kv_bytes // TOKEN_BYTES
+    kernel_name = "mla_decode_hm_kernel" if (H % 128 == 0 and precision == "fp8") else "mla_decode_kernel"
     if H >= 128:  # 2176 flop per token and head: the tensor pipe is the bound, the HBM figure becomes secondary
         tpeak, tkind = measured_tensor_peak(precision)
         tflops = 2176.0 * H * tokens / (kernel_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": tflops, "peak": tpeak, "unit": "TFLOP/s", "frac": tflops / tpeak,
-                    "peak_kind": tkind, "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
+                    "peak_kind": tkind, "kernel": kernel_name, "kernel_ms": kernel_ms,
                     "algorithmic_flops_per_launch": 2176.0 * H * tokens, "hbm_gbs": achieved, "traffic": None}
     else:
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "peak_kind": f"of {peak_kind}", "kernel": "mla_decode_kernel", "kernel_ms": kernel_ms,
+                    "peak_kind": f"of {peak_kind}", "kernel": kernel_name, "kernel_ms": kernel_ms,
                     "algorithmic_bytes_per_launch": kv_bytes,
                     "traffic": (NCU_TRAFFIC_BYTES_PER_TOKEN * tokens) if NCU_TRAFFIC_BYTES_PER_TOKEN else None}
     value = kv_bytes_all / (ms_step * 1e-3) / 1e12
