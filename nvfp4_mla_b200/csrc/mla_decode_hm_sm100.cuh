@@ -441,10 +441,8 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        // half of the exponentials on the special-function unit, half as a polynomial on the FMA pipe (the unit alone
-        // would take 8 cycles per exponential and warp: 512 cycles per tile and sub-partition)
-        const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c]), qa, neg_m)), p1 = ptx::ex2_poly(fmaf(__uint_as_float(sr[4 * c + 1]), qa, neg_m));
-        const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 2]), qa, neg_m)), p3 = ptx::ex2_poly(fmaf(__uint_as_float(sr[4 * c + 3]), qa, neg_m));
+        const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c]), qa, neg_m)), p1 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 1]), qa, neg_m));
+        const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 2]), qa, neg_m)), p3 = ptx::ex2(fmaf(__uint_as_float(sr[4 * c + 3]), qa, neg_m));
         ls[0] += p0, ls[1] += p1, ls[2] += p2, ls[3] += p3;
         pk[c] = ptx::pack_e4m3x4(p0, p1, p2, p3);
       }

@@ -348,20 +348,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {  // one instr
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-// 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative error
-// 1.6e-4), 2^n by adding n to the exponent bits. For x <= 10 or so; x below -126 (including -inf) gives 2^-126.
-// The special-function unit retires one 32-thread ex2 every 8 cycles per SM sub-partition; this costs about as many
-// issue slots but on the FMA / integer pipes, so a softmax that splits its exponentials between the two runs them in
-// parallel.
-__device__ __forceinline__ float ex2_poly(float x) {
-  const float xc = fmaxf(x, -126.f);
-  const float t = xc + 12582912.f;  // 1.5 * 2^23: the low mantissa bits of t hold round(xc) (two's complement)
-  const float f = xc - (t - 12582912.f);
-  float p = fmaf(f, 0.05360212177038193f, 0.24237291514873505f);
-  p = fmaf(f, p, 0.6935023665428162f);
-  p = fmaf(f, p, 0.9999481439590454f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
