@@ -17,8 +17,11 @@
 // distributed shared memory, which count as transaction bytes on the peer's "tile converted" barrier. A tile buffer
 // is reused when the PV of both CTAs has finished with it (a relay warp forwards the local completion to the peer).
 //
-// Tensor memory (512 columns): Q latent 0..127 | S buffer 0: 128..191 | S buffer 1: 192..255 | O: 256..511.
-// P of a tile overwrites the first 16 columns of the S buffer it was computed from.
+// Tensor memory (512 columns): Q latent 0..127 | S: 128..191 | P buffers: 192..207, 208..223 | O: 256..511.
+// One S buffer is enough: the softmax warps read a tile's scores into registers as their first step, so QK^T of tile
+// j + 1 waits only for that read (not for PV of any tile, which sits behind later QK^T in the in-order tensor pipe) and
+// runs while the softmax of tile j computes. P has two buffers of its own: PV of tile j reads one while the softmax of
+// tile j + 1 fills the other.
 // Softmax: thread = head (= tensor-memory lane), so the running max, the sum and the O rescale are thread-local; the
 // tcgen05.ld/st of a rescale are warp-wide, so a warp rescales when any of its heads needs it.
 // Numerics (8-bit mode): Q rows are E4M3 with one scale per row covering both parts (the rope part is pre-multiplied
@@ -55,9 +58,10 @@ struct HmSmem {
   uint64_t kv_full[kHmKvBufs];   // tile converted: 8 local convert warps + kHmPeerBytes from the peer CTA
   uint64_t kv_free[kHmKvBufs];   // PV of the tile (hence its QK^T too) has finished reading the buffer in BOTH CTAs (2 arrivals)
   uint64_t pv_local[kHmKvBufs];  // this CTA's PV of the tile is complete (relay warp forwards it to both kv_free)
-  uint64_t s_full[2];            // QK^T of the tile complete
+  uint64_t s_full;               // QK^T of the tile complete (one phase per tile)
+  uint64_t s_free;               // the softmax warps have read the tile's scores (8 arrivals, one phase per tile)
   uint64_t p_full[2];            // P written to tensor memory (8 softmax warps)
-  uint64_t pv_done[2];           // PV of the tile complete: O may be rescaled, the S/P buffer reused
+  uint64_t pv_done[2];           // PV of the tile complete: O may be rescaled, the P buffer reused
   uint64_t q_full;               // query of the segment in place (8 softmax warps)
   float xch[2][kHmHeads];        // softmax pairs: per-head maxima exchanged between a quadrant's two warps
   float xl[2][kHmHeads];         // softmax pairs: the two halves of a head's softmax sum (segment epilogue)
@@ -68,8 +72,8 @@ template <int RAW_SLOTS>
 constexpr size_t hm_smem_bytes() { return sizeof(HmSmem<RAW_SLOTS>) + 1024; }
 
 struct HmCols {
-  static constexpr uint32_t QN = 0, S0 = 128, O = 256;
-  __host__ __device__ static constexpr uint32_t s(uint32_t buf) { return S0 + 64 * buf; }
+  static constexpr uint32_t QN = 0, S = 128, P0 = 192, O = 256;
+  __host__ __device__ static constexpr uint32_t p(uint32_t buf) { return P0 + 16 * buf; }
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -259,23 +263,25 @@ __device__ __forceinline__ void hm_qk_role(HmSmem<RAW_SLOTS>& s, const DecodePar
     ++seg_count;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1, kb = it % kHmKvBufs;
-      // PV of tile it - 2 read its P from this S buffer
-      if (!__all_sync(~0u, it < 2 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.pv_done[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
+      // the softmax warps have read the scores of tile it - 1
+      if (!__all_sync(~0u, it < 1 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.s_free, (it - 1) & 1, &s.abort_flag)))) return;
       if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.kv_full[kb], (it / kHmKvBufs) & 1, &s.abort_flag)))) return;
       ptx::tc_fence_after_sync();
+      if (leader) MLA_TRACE_AT(P, 12, it);
       if (leader) {
         const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][0]), 16, 1024);
 #pragma unroll 1
         for (int p = 0; p < 4; ++p) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)  // 32 channels per MMA: 8 tensor-memory columns of Q, 32 bytes of the K rows
-            ptx::mma_f8_ts(tm + HmCols::s(buf), tm + HmCols::QN + 32 * p + 8 * ks, k_desc + ((p * kHmPanelBytes + ks * 32) >> 4), idesc,
+            ptx::mma_f8_ts(tm + HmCols::S, tm + HmCols::QN + 32 * p + 8 * ks, k_desc + ((p * kHmPanelBytes + ks * 32) >> 4), idesc,
                            (p | ks) != 0);
         }
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks)
-          ptx::mma_f8_ss(tm + HmCols::s(buf), qpe_desc + ((ks * 32) >> 4), k_desc + ((4 * kHmPanelBytes + ks * 32) >> 4), idesc, 1);
-        ptx::mma_commit(&s.s_full[buf]);
+          ptx::mma_f8_ss(tm + HmCols::S, qpe_desc + ((ks * 32) >> 4), k_desc + ((4 * kHmPanelBytes + ks * 32) >> 4), idesc, 1);
+        ptx::mma_commit(&s.s_full);
+        MLA_TRACE_AT(P, 17, it);
       }
       __syncwarp();
     }
@@ -294,13 +300,15 @@ __device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodePar
       const uint32_t buf = it & 1, kb = it % kHmKvBufs;
       if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
       ptx::tc_fence_after_sync();
+      if (leader) MLA_TRACE_AT(P, 18, it);
       if (leader) {
         const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][2 * cg]), kHmPanelBytes, 1024);
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks)
-          ptx::mma_f8_ts(tm + HmCols::O, tm + HmCols::s(buf) + 8 * ks, v_desc + ((ks * 32 * 128) >> 4), idesc, (t | ks) != 0);
+          ptx::mma_f8_ts(tm + HmCols::O, tm + HmCols::p(buf) + 8 * ks, v_desc + ((ks * 32 * 128) >> 4), idesc, (t | ks) != 0);
         ptx::mma_commit(&s.pv_done[buf]);
         ptx::mma_commit(&s.pv_local[kb]);
+        MLA_TRACE_AT(P, 19, it);
       }
       __syncwarp();
     }
@@ -327,6 +335,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     if (seg.ntiles <= 0) continue;
     // ---- query of (request seg.b, head group seg.hg), this head's row: channels [256 half, +256), rope with half 1.
     // Every MMA that read the previous segment's query has completed (both warps consumed the scores of its last tile).
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 24, si);
     const long long row = (long long)seg.b * P.heads + (long long)seg.hg * kHmHeads + h;
     const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV) + 32 * half;
     const uint4* qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE);
@@ -340,15 +349,35 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       }
       return a;
     };
-    float a_loc = 0.f;
-#pragma unroll 8
-    for (int c = 0; c < 32; ++c) a_loc = amax8(qn[c], a_loc);
-    if (half) {
-      float ap = 0.f;
+    // largest magnitude of the row part: packed BF16 maxima (two values per instruction; a NaN operand is dropped by
+    // the maximum); the element-wise pass that also ignores infinities runs only if one turned up
+    auto amax_fast = [](const uint4* src, int n) {
+      __nv_bfloat162 m2 = __float2bfloat162_rn(0.f);
+#pragma unroll 1
+      for (int c0 = 0; c0 < n; c0 += 8) {  // eight independent 16-byte loads in flight per trip
+        uint4 v[8];
 #pragma unroll
-      for (int c = 0; c < KPE / 8; ++c) ap = amax8(qp[c], ap);
-      a_loc = fmaxf(a_loc, ap * ratio);
+        for (int c = 0; c < 8; ++c) v[c] = __ldg(src + c0 + c);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t wv[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t a = wv[j] & 0x7FFF7FFFu;
+            m2 = __hmax2(m2, *reinterpret_cast<const __nv_bfloat162*>(&a));
+          }
+        }
+      }
+      return fmaxf(__low2float(m2), __high2float(m2));
+    };
+    float a_loc = amax_fast(qn, 32), ap = half ? amax_fast(qp, KPE / 8) : 0.f;
+    if (!(a_loc < INFINITY) || !(ap < INFINITY)) {
+      a_loc = 0.f, ap = 0.f;
+      for (int c = 0; c < 32; ++c) a_loc = amax8(qn[c], a_loc);
+      if (half)
+        for (int c = 0; c < KPE / 8; ++c) ap = amax8(qp[c], ap);
     }
+    a_loc = fmaxf(a_loc, ap * ratio);
     s.xch[half][h] = a_loc;
     ptx::bar_sync(pair_bar, 64);
     const float amax = fmaxf(fmaxf(s.xch[0][h], s.xch[1][h]), 1e-30f);
@@ -362,10 +391,13 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
                             __uint_as_float(wv[3] << 16) * sc, __uint_as_float(wv[3] & 0xFFFF0000u) * sc);
     };
 #pragma unroll 1
-    for (int c0 = 0; c0 < 32; c0 += 8) {  // 64 channels = 16 tensor-memory columns per trip
+    for (int c0 = 0; c0 < 32; c0 += 8) {  // 64 channels = 64 bytes = 16 tensor-memory columns per trip
       uint32_t col[16];
+      uint4 v[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) e4m3x8(qn[c0 + c], inv_n, col[2 * c], col[2 * c + 1]);
+      for (int c = 0; c < 8; ++c) v[c] = __ldg(qn + c0 + c);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) e4m3x8(v[c], inv_n, col[2 * c], col[2 * c + 1]);
       ptx::tmem_st16(tm_lane + HmCols::QN + 64 * half + 2 * c0, col);
     }
     if (half) {
@@ -381,21 +413,27 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.q_full);
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 25, si);
 
     float m = -INFINITY, l = 0.f;  // m is identical in the head's two threads; l is this thread's share of the sum
     const int ntiles = 2 * seg.ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      const bool ok = MLA_WAIT(P, 8 | 32, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
+      bool ok = MLA_WAIT(P, 8 | 32, ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag));
+      // PV of tile it - 2 has read its P from the buffer this tile's P will overwrite (long done: it was issued two tiles ago)
+      ok = ok && (it < 2 || ptx::mbar_wait(&s.pv_done[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile) - 32 * half;  // this warp's columns at or beyond it are masked
       // raw scores of this head for this warp's 32 tokens; the score scale qa > 0 is applied inside the exponent
       uint32_t sr[32];
       if (ok) {
-        ptx::tmem_ld32(tm_lane + HmCols::s(buf) + 32 * half, sr);
+        ptx::tmem_ld32(tm_lane + HmCols::S + 32 * half, sr);
         ptx::tmem_wait_ld();
       }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&s.s_free);  // QK^T of tile it + 1 may overwrite the scores
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       if (!ok || nvalid < 32) {  // tail tile: masked tokens get the score -inf
 #pragma unroll
@@ -435,7 +473,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
         }
       }
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
-      // P = 2^(s qa - m) as E4M3 into this warp's 8 of the first 16 columns of the S buffer (the scores are in registers)
+      // P = 2^(s qa - m) as E4M3 into this warp's 8 of the tile's 16 P columns
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       uint32_t pk[8];
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
@@ -447,11 +485,8 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
         pk[c] = ptx::pack_e4m3x4(p0, p1, p2, p3);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // The other warp of the pair may still be reading its scores from columns 32.. of this buffer: P occupies
-      // columns 0..15 only, and columns 0..31 are this pair's lower warp's scores, which it has read (half 0) or which
-      // the barrier above ordered (half 1 stores after the vote that half 0 joined after its load).
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
-      ptx::tmem_st8(tm_lane + HmCols::s(buf) + 8 * half, pk);
+      ptx::tmem_st8(tm_lane + HmCols::p(buf) + 8 * half, pk);
       ptx::tmem_wait_st();
       if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
@@ -462,6 +497,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
 
     // ---- segment epilogue: wait for the last PV, add the two halves of the sum, write this warp's 128 of the head's
     // 256 channels of the normalised partial
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, si);
     const bool ok = ptx::mbar_wait(&s.pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);
     s.xl[half][h] = l;
     if (ptx::bar_red_or(pair_bar, 64, !ok)) return;
@@ -483,6 +519,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     if (cg == 0 && half == 0) P.lse_part[slot * kHmHeads + h] = lt > 0.f ? m + log2f(lt) : -INFINITY;
     ptx::tc_fence_before_sync();
     ptx::bar_sync(pair_bar, 64);  // s.xl and s.xch are reused by the next segment
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, si);
   }
 }
 
@@ -527,7 +564,8 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 8);
     for (int i = 0; i < kHmKvBufs; ++i)
       ptx::mbar_init(&s.kv_full[i], 8), ptx::mbar_init(&s.kv_free[i], 2), ptx::mbar_init(&s.pv_local[i], 1);
-    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.p_full[i], 8), ptx::mbar_init(&s.pv_done[i], 1);
+    ptx::mbar_init(&s.s_full, 1), ptx::mbar_init(&s.s_free, 8);
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.p_full[i], 8), ptx::mbar_init(&s.pv_done[i], 1);
     ptx::mbar_init(&s.q_full, 8);
     s.abort_flag = 0;
     ptx::fence_mbar_init();
