@@ -294,3 +294,29 @@ def test_cuda_graph_replay_fp8_128_heads():
     want, _ = oracle_reference(c)
     assert O.rel_l2(out.float().cpu().numpy(), want) < 0.08
     check_status()
+
+
+def test_fp8_128_heads_config3_sizes_streamed_reference():
+    """BASELINE config 3's shape on a slice of its batch (128 heads, ragged lengths up to 32K, calibrated scales, 8-bit
+    mode) against the streamed dequantise-then-attention reference, plus two size-independent properties at that size:
+    the output does not depend on `num_splits`-style re-cutting beyond rounding, and permuting the physical pages (with
+    the page table following) leaves it unchanged bit for bit."""
+    lens = [32768, 1024, 17000, 9999, 31, 24576]
+    c = SyntheticCache(lens, 64, 128, None, None, seed=21, device="cuda")
+    out = mla.decode(*c.args(), max_kv_len=32768, precision="fp8")
+    check_status()
+    assert not out.isnan().any()
+    want, _ = attention_paged_nvfp4(*c.args(), requests=[0, 2, 4])
+    assert rel_l2(out[[0, 2, 4]], want) < 0.08
+    out3 = mla.decode(*c.args(), max_kv_len=32768, num_splits=3, precision="fp8")
+    assert rel_l2(out3, out.float()) < 2e-2
+    # physical page permutation
+    P = c.ckv_cache.shape[0]
+    perm = torch.randperm(P, device="cuda")
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(P, device="cuda")
+    out_p = mla.decode(c.q_nope, c.q_pe, c.ckv_cache[perm].contiguous(), c.ckv_sf_cache.view(torch.uint8)[perm].contiguous().view(torch.float8_e4m3fn),
+                       c.kpe_cache.view(torch.uint8)[perm].contiguous().view(torch.float8_e4m3fn), inv[c.page_table.long()].int().contiguous(),
+                       c.kv_lens, SM_SCALE, c.ckv_scale, c.kpe_scale, max_kv_len=32768, precision="fp8")
+    assert torch.equal(out_p, out)
+    check_status()
