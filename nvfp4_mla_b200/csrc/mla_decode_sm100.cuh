@@ -216,12 +216,22 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
   if (ct < N) s.qamax[ct] = 0, s.qamax_pe[ct] = 0;
   ptx::bar_sync(2, 256);
   const long long row0 = (long long)seg.b * P.heads + (long long)seg.hg * N;
-  constexpr int CH = (CKV + KPE) / 8;  // 72 chunks of 8 channels per row
-  for (int i = ct; i < N * CH; i += 256) {
-    const int n = i / CH, c = i % CH;
-    const uint4 v = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
-                           : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  constexpr int CH = (CKV + KPE) / 8;              // 72 chunks of 8 channels per row
+  constexpr int PER = (N * CH + 255) / 256;        // chunks per thread: all loaded up front (one memory latency), kept for pass 2
+  uint4 q8[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = ct + 256 * k, n = i / CH, c = i % CH;
+    q8[k] = make_uint4(0, 0, 0, 0);
+    if (i < N * CH)
+      q8[k] = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
+                     : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
+  }
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = ct + 256 * k, n = i / CH, c = i % CH;
+    if (i >= N * CH) continue;
+    const uint32_t w[4] = {q8[k].x, q8[k].y, q8[k].z, q8[k].w};
     unsigned int m = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -231,11 +241,11 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
     if (m < 0x7F800000u) atomicMax(c < 64 || !P8 ? &s.qamax[n] : &s.qamax_pe[n], m);  // ignore inf / nan for the scale
   }
   ptx::bar_sync(2, 256);
-  for (int i = ct; i < N * CH; i += 256) {
-    const int n = i / CH, c = i % CH;
-    const uint4 v = c < 64 ? reinterpret_cast<const uint4*>(P.q_nope + (row0 + n) * CKV)[c]
-                           : reinterpret_cast<const uint4*>(P.q_pe + (row0 + n) * KPE)[c - 64];
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = ct + 256 * k, n = i / CH, c = i % CH;
+    if (i >= N * CH) continue;
+    const uint32_t w[4] = {q8[k].x, q8[k].y, q8[k].z, q8[k].w};
     if constexpr (!P8) {
       int e = int(s.qamax[n] >> 23) - 127;       // floor(log2(amax)); -127 for 0 / subnormal rows
       e = e < -100 ? -100 : e;
@@ -848,6 +858,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, 2 * si);
     bool ok = ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of the last tile
     if (ptx::bar_red_or(1, 128, !ok)) return;
     ptx::tc_fence_after_sync();
@@ -894,6 +905,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
     ptx::tc_fence_before_sync();
     ptx::bar_sync(1, 128);  // s.red is reused by the next segment
+    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, 2 * si + 1);
   }
 }
 
@@ -960,7 +972,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 0);
   ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
+  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 1);
 
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
@@ -984,6 +998,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 2);
   if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }
