@@ -33,15 +33,15 @@ sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
     # name: (batch, heads, kv_len, page_size, precision)
-    "c2_h16_b64_64k": (64, 16, 65536, 64, "bf16"),   # BASELINE config 2, the shape the metric is quoted on
-    "c1_h16_b32_8k": (32, 16, 8192, 64, "bf16"),     # BASELINE config 1
+    "c2_h16_b64_64k": (64, 16, 65536, 64, "bf16"),   # the headline configuration: the shape the metric is quoted on
+    "c1_h16_b32_8k": (32, 16, 8192, 64, "bf16"),     # a DeepSeek-V3 TP8 shard at 8K context
     "h16_b64_16k": (64, 16, 16384, 64, "bf16"),
     "h16_b8_64k": (8, 16, 65536, 64, "bf16"),        # small case for ncu captures (185 MB of KV, still larger than L2)
     "h128_b64_16k": (64, 128, 16384, 64, "bf16"),
-    # BASELINE config 3: ragged lengths drawn uniformly from [1024, 32768] (seeded, per rank), 8-bit mode; tensor-bound
+    # the compute-bound configuration: ragged lengths drawn uniformly from [1024, 32768] (seeded, per rank), 8-bit mode; tensor-bound
     "c3_h128_b64_ragged_fp8": (64, 128, (1024, 32768), 64, "fp8"),
     "h128_b32_16k_fp8": (32, 128, 16384, 64, "fp8"),  # small case for ncu captures of the 128-head shape
-    "c4_h128_b2_1m_seq": (2, 128, 1048576, 64, "bf16"),  # BASELINE config 4: sequence-sharded, strong scaling
+    "c4_h128_b2_1m_seq": (2, 128, 1048576, 64, "bf16"),  # the long-context configuration: sequence-sharded, strong scaling
 }
 SEQUENCE_SHARDED = {"c4_h128_b2_1m_seq"}
 TOKEN_BYTES = 352

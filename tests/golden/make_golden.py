@@ -1,8 +1,8 @@
 """Regenerates tests/golden/*.npz from the reference project's own torch path.
 
-Run in a container that has the reference checked out (default /root/reference, or $NVFP4_MLA_REFERENCE):
+Run where the reference project is checked out, with $NVFP4_MLA_REFERENCE pointing at it:
 
-    python tests/golden/make_golden.py
+    NVFP4_MLA_REFERENCE=<path to elwhyjay/nvfp4-mla> python tests/golden/make_golden.py
 
 Inputs come from nvfp4_mla_b200.testing.SyntheticCache on the CPU (bit-reproducible from the seed); outputs are
 what the reference's nvfp4_mla.testing.dequantize / attention return for them on CPU tensors. Small cases store
@@ -18,7 +18,9 @@ import torch
 
 HERE = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
-sys.path.insert(0, os.environ.get("NVFP4_MLA_REFERENCE", "/root/reference"))
+if "NVFP4_MLA_REFERENCE" not in os.environ:
+    raise SystemExit("set NVFP4_MLA_REFERENCE to a checkout of the reference project")
+sys.path.insert(0, os.environ["NVFP4_MLA_REFERENCE"])
 
 import nvfp4_mla.testing as ref  # noqa: E402  (the reference; needs flashinfer importable, no GPU)
 from nvfp4_mla_b200.testing import SyntheticCache  # noqa: E402
@@ -26,7 +28,7 @@ from nvfp4_mla_b200.testing import SyntheticCache  # noqa: E402
 # name -> (kv_lens, page_size, heads, ckv_scale, kpe_scale, seed, store_inputs, head_stride, chan_stride)
 CASES = {
     "tiny":        ([21, 9], 8, 16, 0.37, 3.1, 1, True, 1, 1),
-    "config0":     ([1000, 3000], 64, 16, None, None, 0, False, 1, 1),          # BASELINE config 0 (calibrated)
+    "config0":     ([1000, 3000], 64, 16, None, None, 0, False, 1, 1),          # the CPU-runnable reference configuration (calibrated scales)
     "ps1_len1":    ([1], 1, 16, 0.5, 2.0, 2, True, 1, 1),
     "off_page":    ([17, 1, 64, 65], 16, 16, 0.5, 2.0, 3, False, 1, 1),
     "mixed":       ([1000, 4097, 3, 64], 64, 16, 0.5, 2.0, 4, False, 1, 2),

@@ -297,7 +297,7 @@ def test_cuda_graph_replay_fp8_128_heads():
 
 
 def test_fp8_128_heads_config3_sizes_streamed_reference():
-    """BASELINE config 3's shape on a slice of its batch (128 heads, ragged lengths up to 32K, calibrated scales, 8-bit
+    """The compute-bound configuration's shape on a slice of its batch (128 heads, ragged lengths up to 32K, calibrated scales, 8-bit
     mode) against the streamed dequantise-then-attention reference, plus two size-independent properties at that size:
     the output does not depend on `num_splits`-style re-cutting beyond rounding, and permuting the physical pages (with
     the page table following) leaves it unchanged bit for bit."""
