@@ -4,7 +4,12 @@
 //   code = nearest E2M1 (ties to the even mantissa, magnitudes above 6 saturate) of x / (float(sf) * ckv_scale),
 //   0 where the scale is 0; two codes per byte, low nibble = even channel;
 //   rope: e4m3_rn(kpe / kpe_scale), saturating.
-// Every step is one fp32 IEEE operation in that order, so the bytes are reproducible on a CPU bit for bit.
+// Every step is defined as one fp32 IEEE operation in that order, so the bytes are reproducible on a CPU bit for bit.
+// The 512 divisions per token would make the kernel instruction-bound, so the codes are first computed from
+// x * (1 / scale): that product is within 2^-22 (relative) of the correctly rounded quotient, and the code is a
+// monotone step function of the magnitude, so if the products shrunk and grown by 2^-21 get the same code, the
+// quotient gets it too; a value that sits that close to a rounding boundary (exact ties included, which BF16 inputs hit
+// in a few percent of the scale blocks) is redone with a real division.
 //
 // HBM-bound: 1152 bytes in, 352 bytes out per token. One warp per token per trip; lane l owns scale block l
 // (channels 16l .. 16l+15: two 16-byte loads, one 8-byte store, the warp writes the token's 256 packed bytes as one
@@ -21,6 +26,17 @@ constexpr int kQuantThreads = 256;
 __device__ __forceinline__ uint32_t f32x2_to_e4m3x2_sat(float lo, float hi) {  // lo -> low byte
   uint16_t d;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// eight floats -> eight E2M1 codes (round to nearest even, saturating), value 0 in the lowest nibble
+__device__ __forceinline__ uint32_t e2m1x8(const float (&y)[8]) {
+  uint32_t d;
+  asm("{\n.reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\ncvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\ncvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n}"
+      : "=r"(d)
+      : "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]), "f"(y[7]));
   return d;
 }
 __device__ __forceinline__ uint32_t e2m1_code(float y) {
@@ -73,10 +89,26 @@ mla_quantize_append_kernel(const __nv_bfloat16* __restrict__ ckv, const __nv_bfl
     const uint32_t sf8 = f32x2_to_e4m3x2_sat(__fdiv_rn(__fdiv_rn(amax, 6.0f), ckv_scale), 0.f) & 0xFFu;
     const float sf = __fmul_rn(e4m3_value(uint8_t(sf8)), ckv_scale);
     uint32_t lo = 0, hi = 0;
+    if (sf > 0.f) {
+      const float r = __frcp_rn(sf), down = 1.f - 0x1p-21f, up = 1.f + 0x1p-21f;
+      float yd[16], yu[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      lo |= e2m1_code(sf > 0.f ? __fdiv_rn(x[j], sf) : 0.f) << (4 * j);
-      hi |= e2m1_code(sf > 0.f ? __fdiv_rn(x[8 + j], sf) : 0.f) << (4 * j);
+      for (int j = 0; j < 16; ++j) {
+        const float q0 = x[j] * r;
+        yd[j] = q0 * down, yu[j] = q0 * up;
+      }
+      lo = e2m1x8(reinterpret_cast<const float(&)[8]>(yd[0])), hi = e2m1x8(reinterpret_cast<const float(&)[8]>(yd[8]));
+      const uint32_t dlo = lo ^ e2m1x8(reinterpret_cast<const float(&)[8]>(yu[0]));
+      const uint32_t dhi = hi ^ e2m1x8(reinterpret_cast<const float(&)[8]>(yu[8]));
+      if (dlo | dhi) {
+        // some values are within 2^-21 of a rounding boundary (BF16 inputs land on exact ties often): for those the
+        // defining computation decides
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if ((dlo >> (4 * j)) & 15u) lo = (lo & ~(15u << (4 * j))) | (e2m1_code(__fdiv_rn(x[j], sf)) << (4 * j));
+          if ((dhi >> (4 * j)) & 15u) hi = (hi & ~(15u << (4 * j))) | (e2m1_code(__fdiv_rn(x[8 + j], sf)) << (4 * j));
+        }
+      }
     }
     *reinterpret_cast<uint2*>(ckv_cache + row * (CKV / 2) + 8 * lane) = make_uint2(lo, hi);
     sf_cache[row * (CKV / 16) + lane] = uint8_t(sf8);
