@@ -215,19 +215,21 @@ int nvfp4_mla_version(void) { return 100; }
 
 const char* nvfp4_mla_last_error(void) { return g_error; }
 
-int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
+// workspace of one precision mode (the modes may group the heads differently); negative on error
+static int64_t workspace_bytes_of(int batch, int heads, int num_splits, int precision) {
   DeviceInfo* d;
   if (device_info(&d)) return -1;
-  // the size covers either precision mode (they may group the heads differently)
-  size_t need = 0;
-  for (int prec : {NVFP4_MLA_PRECISION_BF16, NVFP4_MLA_PRECISION_FP8}) {
-    mla::Problem pb;
-    const int hpc = heads_per_cta(heads, prec, *d);
-    if (problem_of(batch, heads, 1, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
-    const size_t n = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total;
-    need = n > need ? n : need;
-  }
-  return int64_t(need);
+  mla::Problem pb;
+  const int hpc = heads_per_cta(heads, precision, *d);
+  if (problem_of(batch, heads, 1, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
+  return int64_t(mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total);
+}
+
+int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
+  // the size covers either precision mode
+  const int64_t a = workspace_bytes_of(batch, heads, num_splits, NVFP4_MLA_PRECISION_BF16);
+  const int64_t b = workspace_bytes_of(batch, heads, num_splits, NVFP4_MLA_PRECISION_FP8);
+  return a < 0 || b < 0 ? -1 : (a > b ? a : b);
 }
 
 int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
@@ -339,7 +341,9 @@ int nvfp4_mla_decode_static(const void* q_nope, const void* q_pe, const uint8_t*
                             float ckv_scale, float kpe_scale, int max_kv_len, int num_splits, int precision, void* out,
                             float* out_f32, float* lse, void* stream) {
   g_error[0] = 0;
-  const int64_t need = nvfp4_mla_decode_workspace_bytes(batch, heads, num_splits);
+  MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16 || precision == NVFP4_MLA_PRECISION_FP8,
+            "precision must be 0 (bf16) or 1 (fp8), got %d", precision);
+  const int64_t need = workspace_bytes_of(batch, heads, num_splits, precision);  // of the mode that will run
   if (need < 0) return 1;  // message already set
   MLA_CHECK(need <= int64_t(kStaticScratchBytes),
             "problem too large for the built-in scratch: batch %d x heads %d x num_splits %d needs %lld bytes, the library holds "
