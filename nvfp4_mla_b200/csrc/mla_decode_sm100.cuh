@@ -544,11 +544,10 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[j >> 1]) : 0u;
       } else {  // the FP16 product is exact; the only rounding is the conversion to E4M3
-        uint32_t b[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) b[i] = ptx::f16x2_to_e4m3x2(ptx::hmul2(e[i], sc[j >> 1]));
-        h[2 * j] = valid ? (b[0] | (b[1] << 16)) : 0u;
-        h[2 * j + 1] = valid ? (b[2] | (b[3] << 16)) : 0u;
+        const uint32_t b01 = ptx::f16x4_to_e4m3x4(ptx::hmul2(e[0], sc[j >> 1]), ptx::hmul2(e[1], sc[j >> 1]));
+        const uint32_t b23 = ptx::f16x4_to_e4m3x4(ptx::hmul2(e[2], sc[j >> 1]), ptx::hmul2(e[3], sc[j >> 1]));
+        h[2 * j] = valid ? b01 : 0u;
+        h[2 * j + 1] = valid ? b23 : 0u;
       }
     }
     // publish the previous chunk (rope for g = 0): its store has been in flight during the arithmetic above
