@@ -206,7 +206,10 @@ int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, 
 
 #ifdef MLA_TRACE
 namespace { long long* g_trace = nullptr; }
-extern "C" NVFP4_MLA_API void nvfp4_mla_set_trace(long long* device_buffer) { g_trace = device_buffer; }
+extern "C" NVFP4_MLA_API void nvfp4_mla_set_trace(long long* device_buffer) {
+  g_trace = device_buffer;
+  cudaMemcpyToSymbol(mla::d_trace_ptr, &device_buffer, sizeof(device_buffer));
+}
 #endif
 
 extern "C" {
@@ -280,7 +283,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   mla::DecodeParams P;
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
   P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
-  P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads;
+  P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads, P.heads_per_cta = hpc;
   P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;

@@ -88,7 +88,27 @@ __device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const Dec
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
     const int* pt = P.page_table + (long long)seg.b * P.pt_stride;
+    // page ids of a window of 32 tiles, one per lane and load (see producer_role)
+    constexpr int kAhead = 4;  // tiles between a load and its L2 prefetch
+    int win0 = 0, win_page = 0;
+    auto load_window = [&](int t0) {
+      win0 = t0;
+      const int tokl = seg.tok0 + (t0 + lane) * kHmTile + kHmRows * cg;
+      win_page = tokl < seg.tok_end ? pt[tokl >> P.page_shift] : 0;
+    };
+    if (ps >= kHmRows) load_window(0);
+    const int t_query = 2 * seg.ntiles > 6 ? 2 * seg.ntiles - 6 : 0;  // a few tiles before the end
     for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
+      if (t == t_query)  // the next segment's query rows (128 x 1152 bytes, contiguous per part) into L2: early enough to
+        for (int sj = si + 1; sj < n_segs; ++sj) {  // be there when the softmax warps load them, late enough to still be
+          const Seg nx = s.segs[sj];
+          if (nx.ntiles <= 0) continue;
+          const long long row0 = (long long)nx.b * P.heads + (long long)nx.hg * kHmHeads;
+          for (int i = lane; i < kHmHeads * 9; i += 32)
+            ptx::prefetch_l2(i < kHmHeads * 8 ? reinterpret_cast<const char*>(P.q_nope + row0 * CKV) + i * 128
+                                              : reinterpret_cast<const char*>(P.q_pe + row0 * KPE) + (i - kHmHeads * 8) * 128);
+          break;
+        }
       const int slot = it % RAW_SLOTS;
       const uint32_t use = it / RAW_SLOTS;
       bool ok = MLA_WAIT(P, 0, ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag));
@@ -101,17 +121,18 @@ __device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const Dec
       if (nvalid == 0) {
         if (lane == 0) ptx::mbar_arrive(bar);
       } else if (ps >= kHmRows) {
+        if (t + kAhead >= win0 + 32) load_window(t);
+        const int page = __shfl_sync(~0u, win_page, t - win0);
+        const int page2 = __shfl_sync(~0u, win_page, t + kAhead - win0);
         if (lane == 0) {
-          const int page = pt[tok >> P.page_shift];
           const int row = (page << P.page_shift) + (tok & (ps - 1));
           ptx::mbar_arrive_expect_tx(bar, kHmRows * TOKEN_BYTES);
           ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kHmRawCkvHi, ckv_map, 128, row, bar);
           ptx::tma_load_2d(dst + kHmRawSf, sf_map, 0, row, bar);
           ptx::tma_load_2d(dst + kHmRawKpe, kpe_map, 0, row, bar);
-          const int tok_pf = tok + 4 * kHmTile;  // L2 prefetch a few tiles ahead
+          const int tok_pf = tok + kAhead * kHmTile;  // L2 prefetch a few tiles ahead
           if (tok_pf < seg.tok_end) {
-            const int page2 = pt[tok_pf >> P.page_shift];
             const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
             ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
             ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
@@ -340,6 +361,12 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV) + 32 * half;
     const uint4* qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE);
     const float ratio = P.kpe_scale / (8.f * P.ckv_scale);  // rope scores in units of the latent ones
+    // This thread's part of the row is four 128-byte lines (+ one of rope): ask for all of them at once, so that the two
+    // passes below pay at most one trip to memory instead of one per batch of loads (the producer warp has asked for the
+    // rows of every segment but the first a few tiles ahead).
+#pragma unroll
+    for (int l = 0; l < 4; ++l) ptx::prefetch_l2(reinterpret_cast<const char*>(qn) + 128 * l);
+    if (half) ptx::prefetch_l2(qp);
     auto amax8 = [](const uint4& v, float a) {
       const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -575,11 +602,11 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
-  ptx::grid_launch_dependents();
   ptx::tc_fence_before_sync();
   ptx::cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
   ptx::tc_fence_after_sync();
   ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();  // after the wait: the combine kernel reads the schedule kernel's output as soon as it starts
 
   // 640 threads are launched with 96 registers each (65536 / 640 rounded down to a multiple of 8); that allocation is
   // the pool the role budgets must fit in, warp group by warp group (4 warps each): 2 softmax, 2 convert, 1 issue.

@@ -45,10 +45,13 @@ constexpr int kTmemCols = 512;
 // Optional timeline tracing (compiled in with -DMLA_TRACE): CTA 0 records clock64() at pipeline events of its first
 // kTraceTiles tiles into trace[event][tile].
 #ifdef MLA_TRACE
+#ifndef MLA_TRACE_CTA
+#define MLA_TRACE_CTA 0  // the CTA whose pipeline events are recorded
+#endif
 constexpr int kTraceTiles = 64, kTraceEvents = 32;
 #define MLA_TRACE_AT(P, ev, tile)                                                             \
   do {                                                                                        \
-    if ((P).trace && blockIdx.x == 0 && (tile) < mla::kTraceTiles) (P).trace[(ev) * mla::kTraceTiles + (tile)] = clock64(); \
+    if ((P).trace && blockIdx.x == MLA_TRACE_CTA && (tile) < mla::kTraceTiles) (P).trace[(ev) * mla::kTraceTiles + (tile)] = clock64(); \
   } while (0)
 // wait-time accounting: MLA_WAIT(P, slot, expr) evaluates the (waiting) expression and adds the cycles it took to
 // trace[31][slot] (CTA 0 only; meant to be used by one thread per role)
@@ -56,7 +59,7 @@ constexpr int kTraceTiles = 64, kTraceEvents = 32;
   ([&] {                                                                                            \
     const long long t0_ = clock64();                                                                \
     const bool r_ = (expr);                                                                         \
-    if ((P).trace && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && ((slot) < 32 || threadIdx.x == ((slot) >> 8)))                   \
+    if ((P).trace && blockIdx.x == MLA_TRACE_CTA && (threadIdx.x & 31) == 0 && ((slot) < 32 || threadIdx.x == ((slot) >> 8)))                   \
       atomicAdd(reinterpret_cast<unsigned long long*>((P).trace + 31 * mla::kTraceTiles + ((slot) & 31)), (unsigned long long)(clock64() - t0_)); \
     return r_;                                                                                      \
   }())
@@ -84,7 +87,7 @@ struct DecodeParams {
   // so that 32 threads reading the same chunk of 32 consecutive rows touch every bank once. Smaller pages arrive
   // through linear bulk copies (a box of fewer than 128 bytes cannot be a TMA tile destination): masks 0.
   uint32_t sf_swz_mask, kpe_swz_mask;
-  int heads;
+  int heads, heads_per_cta;
   float sm_scale_log2, ckv_scale, kpe_scale;
   const int2* cta_range;
   const Seg* segs;
@@ -967,12 +970,21 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
-  ptx::grid_launch_dependents();  // the combine kernel may be scheduled; it waits for this grid before reading partials
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 0);
+#ifdef MLA_TRACE
+  if (threadIdx.x == 0 && P.trace && blockIdx.x < 256) {  // rows 32..: per-CTA start / end / segment slots, global timer
+    long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    P.trace[32 * kTraceTiles + 4 * blockIdx.x] = gt;
+  }
+#endif
   ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
+  // The combine kernel may be scheduled from here on: it reads the schedule at once (settled, as this grid has just
+  // seen) and waits for this grid before it reads partials.
+  ptx::grid_launch_dependents();
   if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 1);
 
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
@@ -998,6 +1010,15 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 2);
+#ifdef MLA_TRACE
+  if (threadIdx.x == 0 && P.trace && blockIdx.x < 256) {
+    long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    P.trace[32 * kTraceTiles + 4 * blockIdx.x + 1] = gt;
+    const int2 rg = P.cta_range[blockIdx.x];
+    P.trace[32 * kTraceTiles + 4 * blockIdx.x + 2] = rg.y - rg.x;
+  }
+#endif
   if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }

@@ -11,6 +11,19 @@
 
 namespace mla {
 
+#ifdef MLA_TRACE
+__device__ long long* d_trace_ptr;  // timeline tracing: slots 48.. of row 31 hold global-timer stamps of the helper kernels
+__device__ __forceinline__ void trace_stamp(int slot, bool max_of_all) {
+  if (!d_trace_ptr) return;
+  long long gt;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+  if (max_of_all) atomicMax(reinterpret_cast<unsigned long long*>(d_trace_ptr + 31 * 64 + slot), (unsigned long long)gt);
+  else d_trace_ptr[31 * 64 + slot] = gt;
+}
+#define MLA_STAMP(slot, all) trace_stamp(slot, all)
+#else
+#define MLA_STAMP(slot, all) do {} while (0)
+#endif
 constexpr int kSchedThreads = 1024;
 constexpr int kSchedMaxBZ = 8192;  // batch * splits the single-block scan holds in shared memory
 
@@ -21,6 +34,7 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
   __shared__ int total_bz;
   ptx::grid_launch_dependents();  // the decode kernel may start its prologue; it waits for this grid before reading
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) MLA_STAMP(48, false);
   const int BZ = pb.batch * pb.splits;
   if (BZ > kSchedMaxBZ) {
     if (tid == 0) header[0] = kBadSchedule;
@@ -126,6 +140,8 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
       segs[c + w] = s;
     }
   }
+  __syncthreads();
+  if (tid == 0) MLA_STAMP(49, false);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -162,6 +178,15 @@ template <int GROUPS, class LseOf, class OOf>
 __device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, long long row, void* out_bf16,
                                           float* out_f32, float* lse_out, float* weights, float4* partial) {
   const int lane = threadIdx.x & 31, grp = threadIdx.x >> 7, t = threadIdx.x & 127;
+  // The first batch of rows is requested before the weights are known (they need the lse values, another round trip to
+  // memory): a row with a handful of partials, the common case, then costs one memory latency instead of two. A partial
+  // of weight 0 may hold anything, so its values are dropped by a select, not multiplied away.
+  float4 v0[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = grp + j * GROUPS;
+    v0[j] = i < n_parts ? reinterpret_cast<const float4*>(o_of(i))[t] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   float M = -INFINITY;
   for (int i = lane; i < n_parts; i += 32) M = fmaxf(M, lse_of(i));
   M = warp_max(M);
@@ -174,7 +199,15 @@ __device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, l
   den = warp_sum(den);
   __syncthreads();
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int i0 = grp; i0 < n_parts; i0 += 8 * GROUPS) {
+  auto add = [&](float w, const float4& v) {
+    if (w != 0.f) acc.x += w * v.x, acc.y += w * v.y, acc.z += w * v.z, acc.w += w * v.w;
+  };
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = grp + j * GROUPS;
+    add(i < n_parts ? weights[i] : 0.f, v0[j]);
+  }
+  for (int i0 = grp + 8 * GROUPS; i0 < n_parts; i0 += 8 * GROUPS) {
     float4 v[8];
     float w[8];
 #pragma unroll
@@ -184,7 +217,7 @@ __device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, l
       v[j] = w[j] != 0.f ? reinterpret_cast<const float4*>(o_of(i))[t] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc.x += w[j] * v[j].x, acc.y += w[j] * v[j].y, acc.z += w[j] * v[j].z, acc.w += w[j] * v[j].w;
+    for (int j = 0; j < 8; ++j) add(w[j], v[j]);
   }
   if (GROUPS > 1) {
     if (grp > 0) partial[(grp - 1) * 128 + t] = acc;
@@ -213,7 +246,9 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
   __shared__ int n_parts_s;
   __shared__ float weights[kCombineMaxParts];
   __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
-  ptx::grid_dependency_wait();  // launched as a programmatic dependent of the decode kernel
+  if (blockIdx.x == 0 && threadIdx.x == 0) MLA_STAMP(50, false);
+  // Launched as a programmatic dependent of the decode kernel, which lets its dependents start only after it has seen
+  // the schedule kernel complete: the schedule's output (item_range) may be read at once, the partials only after the wait.
   const long long row = blockIdx.x;
   const int b = int(row / pb.heads), h = int(row % pb.heads);
   const int N = pb.heads_per_cta, hg = h / N, n = h % N;
@@ -244,9 +279,12 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
   }
   __syncthreads();
   const int n_parts = n_parts_s;
+  ptx::grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) MLA_STAMP(51, false);
   merge_row<GROUPS>(
       n_parts, [&](int i) { return lse_part[(long long)slots[i] * N + n]; },
       [&](int i) { return o_part + ((long long)slots[i] * N + n) * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
+  if (threadIdx.x == 0) MLA_STAMP(52, true);
 }
 
 // Dense partials [parts, rows, 512] / [parts, rows]: the merge a caller runs on (o, lse) pairs gathered from
