@@ -363,7 +363,6 @@ def main():
         out = decode_fn(*dargs, **kw)
     sync_all()
     lib = _lib.load()
-    _lib.check(lib.nvfp4_mla_profile_begin(args.steps))
     if sampler:
         sampler.mark("timed_begin")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -372,22 +371,32 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if kv_bytes < (256 << 20) else None
     config["l2"] = ("inputs larger than L2 (126 MB), no flush" if flush is None else
                     "256 MB written between timed steps (inputs smaller than 2 x L2); each step timed by its own event pair")
-    if flush is None:
-        ev0.record()
-        for _ in range(args.steps):
-            out = decode_fn(*dargs, **kw)
-        ev1.record()
-        sync_all()
-        total_ms = ev0.elapsed_time(ev1)
-    else:
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    pairs = None if flush is None else [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                                        for _ in range(args.steps)]
+
+    def timed_pass():
+        """K steps of the hot path; returns (total ms over the steps, last output)."""
+        if flush is None:
+            ev0.record()
+            for _ in range(args.steps):
+                o = decode_fn(*dargs, **kw)
+            ev1.record()
+            sync_all()
+            return ev0.elapsed_time(ev1), o
         for a, b in pairs:
             flush.zero_()
             a.record()
-            out = decode_fn(*dargs, **kw)
+            o = decode_fn(*dargs, **kw)
             b.record()
         sync_all()
-        total_ms = sum(a.elapsed_time(b) for a, b in pairs)
+        return sum(a.elapsed_time(b) for a, b in pairs), o
+
+    # Pass 1, the reported step time: the call as a user makes it (its three kernels chained by programmatic dependent
+    # launch). Pass 2, the same K steps with the library's own event pair around the decode kernel (the roofline's
+    # duration): those events sit between the kernels and undo the chaining, so this pass is not the one reported.
+    total_ms, out = timed_pass()
+    _lib.check(lib.nvfp4_mla_profile_begin(args.steps))
+    timed_pass()
     if sampler:
         sampler.mark("timed_end")
     kern_ms = (ctypes.c_float * args.steps)()

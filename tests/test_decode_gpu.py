@@ -105,6 +105,26 @@ def test_combine_vs_oracle():
     assert out16.dtype == torch.bfloat16 and np.abs(out16.float().cpu().numpy() - want).max() < 2e-2
 
 
+@pytest.mark.parametrize("parts,rows_shape", [(3, (2, 16)), (9, (40, 16)), (70, (2, 16)), (70, (40, 16))])
+def test_combine_ignores_empty_partials(parts, rows_shape):
+    """A partial of weight 0 (lse = -inf) may hold anything, NaN included: it must not reach the result. Covers the rows
+    requested before the weights are known (the first eight per thread group) and the later batches, for few rows
+    (four thread groups per row) and many (one group)."""
+    rng = np.random.default_rng(parts)
+    o = rng.standard_normal((parts, *rows_shape, 512)).astype(np.float32)
+    lse = (rng.standard_normal((parts, *rows_shape)) * 4).astype(np.float32)
+    dead = rng.random((parts, *rows_shape)) < 0.3
+    dead[0] = False  # every row keeps at least one live partial
+    lse[dead] = -np.inf
+    want, want_lse = O.combine(np.where(dead[..., None], 0.0, o).astype(np.float32), lse)
+    o[dead] = np.nan
+    out, got_lse = mla.combine(torch.from_numpy(o).cuda(), torch.from_numpy(lse).cuda(), torch.float32, return_lse=True)
+    got = out.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert np.abs(got - want).max() < 1e-5
+    assert np.abs(got_lse.cpu().numpy() - want_lse).max() < 1e-5
+
+
 @pytest.mark.parametrize("num_splits", [0, 1, 3, 7])
 @pytest.mark.parametrize("kv_lens,page_size,heads", CASES)
 def test_decode(num_splits, kv_lens, page_size, heads):
