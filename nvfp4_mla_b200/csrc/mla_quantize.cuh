@@ -8,8 +8,8 @@
 // The 512 divisions per token would make the kernel instruction-bound, so the codes are first computed from
 // x * (1 / scale): that product is within 2^-22 (relative) of the correctly rounded quotient, and the code is a
 // monotone step function of the magnitude, so if the products shrunk and grown by 2^-21 get the same code, the
-// quotient gets it too; a value that sits that close to a rounding boundary (exact ties included, which BF16 inputs hit
-// in a few percent of the scale blocks) is redone with a real division.
+// quotient gets it too; a value that sits that close to a rounding boundary is settled on its own: an exact tie (which
+// BF16 inputs hit in a few percent of the scale blocks) by one fused multiply-add, anything else by a real division.
 //
 // HBM-bound: 1152 bytes in, 352 bytes out per token. One warp per token per trip; lane l owns scale block l
 // (channels 16l .. 16l+15: two 16-byte loads, one 8-byte store, the warp writes the token's 256 packed bytes as one
@@ -56,6 +56,7 @@ mla_quantize_append_kernel(const __nv_bfloat16* __restrict__ ckv, const __nv_bfl
                            long long num_pages, int page_shift, const int* __restrict__ kv_indices,
                            const int* __restrict__ kv_indptr, int batch, float ckv_scale, float kpe_scale, int* status) {
   const int lane = threadIdx.x & 31;
+  constexpr float kDown = 1.f - 0x1p-21f, kUp = 1.f + 0x1p-21f;
   const long long warp0 = (long long)blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5);
   const long long stride = (long long)gridDim.x * (kQuantThreads / 32);
   for (long long t = warp0; t < nnz; t += stride) {
@@ -90,7 +91,7 @@ mla_quantize_append_kernel(const __nv_bfloat16* __restrict__ ckv, const __nv_bfl
     const float sf = __fmul_rn(e4m3_value(uint8_t(sf8)), ckv_scale);
     uint32_t lo = 0, hi = 0;
     if (sf > 0.f) {
-      const float r = __frcp_rn(sf), down = 1.f - 0x1p-21f, up = 1.f + 0x1p-21f;
+      const float r = __frcp_rn(sf), down = kDown, up = kUp;
       float yd[16], yu[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -100,15 +101,23 @@ mla_quantize_append_kernel(const __nv_bfloat16* __restrict__ ckv, const __nv_bfl
       lo = e2m1x8(reinterpret_cast<const float(&)[8]>(yd[0])), hi = e2m1x8(reinterpret_cast<const float(&)[8]>(yd[8]));
       const uint32_t dlo = lo ^ e2m1x8(reinterpret_cast<const float(&)[8]>(yu[0]));
       const uint32_t dhi = hi ^ e2m1x8(reinterpret_cast<const float(&)[8]>(yu[8]));
-      if (dlo | dhi) {
-        // some values are within 2^-21 of a rounding boundary (BF16 inputs land on exact ties often): for those the
-        // defining computation decides
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if ((dlo >> (4 * j)) & 15u) lo = (lo & ~(15u << (4 * j))) | (e2m1_code(__fdiv_rn(x[j], sf)) << (4 * j));
-          if ((dhi >> (4 * j)) & 15u) hi = (hi & ~(15u << (4 * j))) | (e2m1_code(__fdiv_rn(x[8 + j], sf)) << (4 * j));
+      // Some values are within 2^-21 of a rounding boundary: for those the defining computation decides. Nearly all of
+      // them are exact ties (BF16 inputs over a scale of a few bits): every boundary has at most three significant
+      // bits, so the candidate T is the product rounded to three bits, and T * sf == |x| (one fused multiply-add,
+      // exact in sign and in zero) proves that x / sf is T itself; only the rest take the division. The loop visits
+      // the flagged values alone (the value is read again from memory: the registers cannot be indexed).
+      auto settle = [&](uint32_t codes, uint32_t diff, int base) {
+        while (diff) {
+          const int j = (__ffs(diff) - 1) >> 2;
+          diff &= ~(15u << (4 * j));
+          const float xv = __bfloat162float(ckv[t * CKV + 16 * lane + base + j]);
+          const float tie = __uint_as_float((__float_as_uint(fabsf(xv) * r) + 0x00100000u) & 0xFFE00000u);
+          const float q = __fmaf_rn(tie, sf, -fabsf(xv)) == 0.f ? copysignf(tie, xv) : __fdiv_rn(xv, sf);
+          codes = (codes & ~(15u << (4 * j))) | (e2m1_code(q) << (4 * j));
         }
-      }
+        return codes;
+      };
+      lo = settle(lo, dlo, 0), hi = settle(hi, dhi, 8);
     }
     *reinterpret_cast<uint2*>(ckv_cache + row * (CKV / 2) + 8 * lane) = make_uint2(lo, hi);
     sf_cache[row * (CKV / 16) + lane] = uint8_t(sf8);
