@@ -250,13 +250,90 @@ def bench_writer(args):
         "clocks": sampler.stop()}))
 
 
+def bench_dequant(args):
+    """`--workload dequant_1m`: one step = dequantise a cache of 1 048 576 tokens to BF16 with `dequantize` (the
+    reference's `nvfp4_mla.dequantize`, csrc/mla_decode.cu:1101-1132). HBM-bound: 352 bytes read + 1152 written per token."""
+    import numpy as np
+    import torch
+    import nvfp4_mla_b200 as mla
+    P, ps = 16384, 64
+    ntok, bytes_per_token = P * ps, TOKEN_BYTES + 1152
+    if args.impl == "reference" or not torch.cuda.is_available():
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import mla_oracle as O
+        n = 256  # pages
+        rng = np.random.default_rng(0)
+        ckv = rng.integers(0, 256, (n, ps, 256), dtype=np.uint8)
+        sf = rng.integers(0, 0x7F, (n, ps, 32), dtype=np.uint8)
+        kpe = rng.integers(0, 0x7F, (n, ps, 64), dtype=np.uint8)
+        t0 = time.perf_counter()
+        O.dequantize(ckv, sf, kpe, 2.0 ** -9, 2.0 ** -6)
+        dt = time.perf_counter() - t0
+        val = n * ps * bytes_per_token / dt / 1e9
+        print(json.dumps({"impl": "reference", "metric": "nvfp4_mla_dequantize_bandwidth", "value": val, "unit": "GB/s", "n_gpus": 1,
+                          "steps": 1, "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": "dequant_1m"},
+                          "cpu_baseline": {"value": val, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                           "sample": f"{n * ps} tokens, numpy dequantize of the oracle"},
+                          "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    ckv = torch.randint(0, 256, (P, ps, 256), generator=g, device=dev, dtype=torch.uint8)
+    sf = torch.randint(0, 0x7F, (P, ps, 32), generator=g, device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    kpe = torch.randint(0, 0x7F, (P, ps, 64), generator=g, device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn)
+
+    def step():
+        return mla.dequantize(ckv, sf, kpe, 2.0 ** -9, 2.0 ** -6)
+    steps = min(args.steps, 200)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.mark("load_begin"), sampler.mark("timed_begin")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = step()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.mark("timed_end")
+    ms = e0.elapsed_time(e1) / steps
+    # end to end: the cache comes from pinned host memory every step, a device-to-host read of one page's values ends it
+    host = [t.view(torch.uint8).cpu().pin_memory() for t in (ckv, sf, kpe)]
+    page = torch.empty(ps, 512, dtype=torch.bfloat16).pin_memory()
+    e0.record()
+    for _ in range(3):
+        for d, h in zip((ckv, sf, kpe), host):
+            d.view(torch.uint8).copy_(h, non_blocking=True)
+        out = step()
+        page.copy_(out[0][0], non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / 3
+    peak, kind = measured_peak()
+    val = ntok * bytes_per_token / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "nvfp4_mla_dequantize_bandwidth", "value": val, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic, bf16 output",
+        "data": "synthetic",
+        "config": {"workload": f"dequant_1m: {ntok} tokens ({P} pages of {ps}), random bytes, BF16 output",
+                   "l2": "1.6 GB touched per step, larger than L2, no flush"},
+        "e2e": {"value": ntok * bytes_per_token / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": ntok * TOKEN_BYTES, "d2h_bytes_per_step": ps * 1024},
+        "gpu_launches": steps,
+        "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "peak_kind": f"of {kind}",
+                     "kernel": "mla_dequant_kernel", "algorithmic_bytes_per_launch": ntok * bytes_per_token, "traffic": None},
+        "clocks": sampler.stop()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS) + ["writer_1m"])
+    ap.add_argument("--workload", default="c2_h16_b64_64k", choices=sorted(WORKLOADS) + ["writer_1m", "dequant_1m"])
     ap.add_argument("--num-splits", type=int, default=0)
     ap.add_argument("--precision", default=None, choices=["bf16", "fp8"], help="override the workload's precision mode")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
@@ -265,6 +342,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.workload == "writer_1m":
         return bench_writer(args)
+    if args.workload == "dequant_1m":
+        return bench_dequant(args)
 
     import torch
     import torch.distributed as dist
