@@ -116,7 +116,10 @@ struct DecodeSmem {
   unsigned int qamax[N], qamax_pe[N];
   alignas(8) uint64_t raw_full[RAW_SLOTS];
   uint64_t raw_empty[RAW_SLOTS];
-  uint64_t k_full[5];                               // K chunk in tensor memory: 0..3 = latent panels {g, g+4}, 4 = rope
+  // K chunk in tensor memory: [tile parity][0..3 = latent panels {g, g+4}, 4 = rope], one phase per two tiles. Two sets,
+  // because in the 16-bit mode the convert warps publish the rope chunk and chunk 0 of tile it + 1 (which have their
+  // own columns) while QK^T may not yet have looked at tile it's barriers.
+  uint64_t k_full[2][5];
   uint64_t k_done;                                  // QK^T of the tile has finished reading K and Q^T (one phase per tile)
   uint64_t v_full[2];                               // V buffer b is written (one phase per tile that uses the buffer)
   // 16-bit mode (single V tile): per 128-channel block mb = panels {mb, mb + 4}, one phase per tile. PV of a tile chases
@@ -139,6 +142,15 @@ template <int N, bool P8> struct Cols {
   __host__ __device__ static constexpr uint32_t sn(uint32_t buf) { return S + buf * 2 * N; }      // latent part of the scores
   __host__ __device__ static constexpr uint32_t sp(uint32_t buf) { return S + buf * 2 * N + N; }  // rope part
   static_assert(O + 4 * N <= kTmemCols, "tensor memory overflow");
+  // 16-bit mode with 16 heads: 96 columns are left over. They give the rope chunk and the first latent chunk (panels
+  // 0 and 4) of ODD tiles a home of their own, so that the conversion of a tile can start before QK^T of the tile
+  // before it has finished with K (the wait moves from the first chunk to the second).
+  static constexpr bool kTwoHomes = !P8 && O + 4 * N + 3 * PANEL <= kTmemCols;
+  static constexpr uint32_t SPARE = O + 4 * N;
+  __host__ __device__ static constexpr uint32_t krope(uint32_t parity) { return kTwoHomes && parity ? SPARE : KROPE; }
+  __host__ __device__ static constexpr uint32_t kpanel(uint32_t p, uint32_t parity) {
+    return kTwoHomes && parity && (p & 3) == 0 ? SPARE + PANEL + (p >> 2) * PANEL : K + PANEL * p;
+  }
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -324,10 +336,9 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     const uint32_t kswz = (rr >> 1) & P.kpe_swz_mask;
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
-    // K of the previous tile may be overwritten once its QK^T has finished: the only wait on QK^T in the step
-    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
-    if (!__all_sync(~0u, ok)) return false;
-    ptx::tc_fence_after_sync();
+    // (no wait here: the rope chunk and chunk 0 of this tile have columns of their own, see Cols::kTwoHomes; the columns
+    // shared with the previous tile are first written at chunk 1, after the wait for that tile's QK^T)
+    static_assert(Cols<N, P8>::kTwoHomes, "the interleaved step relies on the second home of the rope chunk and chunk 0");
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
     uint32_t h[16];
 #pragma unroll
@@ -335,7 +346,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
       h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
     }
-    ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
+    ptx::tmem_st16(tm_lane + Cols<N, P8>::krope(it & 1) + 16 * hf, h);
     if (tr) MLA_TRACE_AT(P, 2, it);
   }
   uint32_t hb[W];  // a panel of tile it - 1 on its way from tensor memory to the V tile
@@ -368,7 +379,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       }
     }
     if (has_b && g > 0 && !store_v(g - 1)) return false;
-    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * p, hb);
+    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p, (it - 1) & 1), hb);
     auto convert_half = [&](int j0) {  // words j0 .. j0 + 3 of the panel -> h
 #pragma unroll
       for (int j = 0; j < 4; ++j) {  // word j0 + j = channels [8 (j0 + j), + 8) of the panel, scale block (j0 + j) / 2
@@ -396,7 +407,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+        ptx::mbar_arrive(&s.k_full[it & 1][g == 0 ? 4 : g - 1]);
         if (has_b && g > 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
       }
     } else if (has_b && g > 0) {
@@ -406,9 +417,14 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     }
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
-      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::K + W * p, h);
+      if (g == 1) {  // from here on the tile overwrites columns of the previous one: its QK^T must have finished
+        ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
+        if (!__all_sync(~0u, ok)) return false;
+        ptx::tc_fence_after_sync();
+      }
+      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
       convert_half(4);
-      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::K + W * p + W / 2, h);
+      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1) + W / 2, h);
       if (tr) MLA_TRACE_AT(P, 3 + g, it);
     }
   }
@@ -417,7 +433,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     ptx::tmem_wait_st();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][3]);
     if (tr) MLA_TRACE_AT(P, 7, it);
   }
   if (has_b) {
@@ -557,14 +573,14 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     ptx::tmem_wait_st();
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[g == 0 ? 4 : g - 1]);
+    if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][g == 0 ? 4 : g - 1]);
     if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
     if (tr) MLA_TRACE_AT(P, 3 + g, it);
   }
   ptx::tmem_wait_st();
   ptx::tc_fence_before_sync();
   __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.k_full[3]);
+  if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][3]);
   if (tr) MLA_TRACE_AT(P, 7, it);
   return true;
 }
@@ -640,19 +656,19 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       // softmax of tile it - 2 must have read this S^T buffer
       if (!__all_sync(~0u, it < 2 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
       // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
-      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[4], par, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[par][4], (it >> 1) & 1, &s.abort_flag)))) return;
       if (leader) MLA_TRACE_AT(P, 12, it);
       ptx::tc_fence_after_sync();
       if (leader) {
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks)
-          mma(tm + Cols<N, P8>::sp(buf), tm + Cols<N, P8>::KROPE + 8 * ks, q_desc + (q_off(8, ks) >> 4), ks > 0);
+          mma(tm + Cols<N, P8>::sp(buf), tm + Cols<N, P8>::krope(par) + 8 * ks, q_desc + (q_off(8, ks) >> 4), ks > 0);
       }
       // rolled loops (one panel per trip): fully unrolled, the operand sets would occupy ~100 registers of a warp
       // group that has given most of its registers away
 #pragma unroll 1
       for (int g = 0; g < 4; ++g) {
-        if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[g], par, &s.abort_flag)))) return;
+        if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[par][g], (it >> 1) & 1, &s.abort_flag)))) return;
         if (leader) MLA_TRACE_AT(P, 13 + g, it);
         ptx::tc_fence_after_sync();
         if (leader) {
@@ -661,7 +677,7 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
             const int p = g + 4 * half;
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
-              mma(tm + Cols<N, P8>::sn(buf), tm + Cols<N, P8>::K + W * p + 8 * ks, q_desc + (q_off(p, ks) >> 4), (g | half | ks) != 0);
+              mma(tm + Cols<N, P8>::sn(buf), tm + Cols<N, P8>::kpanel(p, par) + 8 * ks, q_desc + (q_off(p, ks) >> 4), (g | half | ks) != 0);
           }
           if (g == 3) ptx::mma_commit(&s.k_done), ptx::mma_commit(&s.s_full[buf]);
         }
@@ -954,7 +970,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
-    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 8);
+    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[0][i], 8), ptx::mbar_init(&s.k_full[1][i], 8);
     ptx::mbar_init(&s.k_done, 1);
     ptx::mbar_init(&s.v_full[0], 8), ptx::mbar_init(&s.v_full[1], 8);
     for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.vb_full[i], 8), ptx::mbar_init(&s.vb_free[i], 1);
