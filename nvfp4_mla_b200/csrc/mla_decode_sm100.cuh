@@ -120,7 +120,12 @@ struct DecodeSmem {
   // because in the 16-bit mode the convert warps publish the rope chunk and chunk 0 of tile it + 1 (which have their
   // own columns) while QK^T may not yet have looked at tile it's barriers.
   uint64_t k_full[2][5];
-  uint64_t k_done;                                  // QK^T of the tile has finished reading K and Q^T (one phase per tile)
+  // QK^T of the tile has finished reading K and Q^T. 16-bit mode: one barrier per tile parity, one phase per two
+  // tiles; 8-bit mode: one barrier, one phase per tile (each measured faster in its mode by 1-2 %).
+  uint64_t k_done[2];
+  static constexpr bool kDoneTwo = !P8;
+  __device__ __forceinline__ uint64_t* kdone_bar(uint32_t tile) { return &k_done[kDoneTwo ? tile & 1 : 0]; }
+  __device__ static __forceinline__ uint32_t kdone_phase(uint32_t tile) { return kDoneTwo ? (tile >> 1) & 1 : tile & 1; }
   uint64_t v_full[2];                               // V buffer b is written (one phase per tile that uses the buffer)
   // 16-bit mode (single V tile): per 128-channel block mb = panels {mb, mb + 4}, one phase per tile. PV of a tile chases
   // the copy block by block, and the copy of the next tile chases PV.
@@ -147,6 +152,8 @@ template <int N, bool P8> struct Cols {
   // before it has finished with K (the wait moves from the first chunk to the second).
   static constexpr bool kTwoHomes = !P8 && O + 4 * N + 3 * PANEL <= kTmemCols;
   static constexpr uint32_t SPARE = O + 4 * N;
+  // (In the 8-bit mode with 16 heads the whole of K would fit a second time; measured, it gains nothing: that kernel is
+  // paced by the conversion arithmetic, not by this wait.)
   __host__ __device__ static constexpr uint32_t krope(uint32_t parity) { return kTwoHomes && parity ? SPARE : KROPE; }
   __host__ __device__ static constexpr uint32_t kpanel(uint32_t p, uint32_t parity) {
     return kTwoHomes && parity && (p & 3) == 0 ? SPARE + PANEL + (p >> 2) * PANEL : K + PANEL * p;
@@ -418,7 +425,7 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
       if (g == 1) {  // from here on the tile overwrites columns of the previous one: its QK^T must have finished
-        ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
+        ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag));
         if (!__all_sync(~0u, ok)) return false;
         ptx::tc_fence_after_sync();
       }
@@ -469,7 +476,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
     const uint32_t swz_v = uint32_t(r & 7) << 4;
     uint32_t hb[2][W];
-    if (!MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * (4 * hf), hb[0]);
+    if (!MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(4 * hf, tb & 1), hb[0]);
     // the PV that last read this V buffer (tile tb - VB) must have finished
     ok = tb < VB || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
@@ -477,7 +484,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     for (int g = 0; g < 4; ++g) {
       const int p = g + 4 * hf;  // 64-channel panel; 16-bit mode: V panel p, 8-bit mode: half p % 2 of V panel p / 2
       ptx::tmem_wait_ld();
-      if (g < 3 && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::K + W * (p + 1), hb[(g + 1) & 1]);
+      if (g < 3 && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p + 1, tb & 1), hb[(g + 1) & 1]);
       const uint32_t* v = hb[g & 1];
       uint8_t* vrow = (P8 ? s.v16[vbuf][p >> 1] : s.v16[vbuf][p]) + r * 128;
 #pragma unroll
@@ -511,7 +518,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
     // K of the previous tile may be overwritten once its QK^T has finished (the copy above has already read it)
-    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(&s.k_done, prev, &s.abort_flag));
+    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag));
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
@@ -522,12 +529,12 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
         h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
         h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
       }
-      ptx::tmem_st16(tm_lane + Cols<N, P8>::KROPE + 16 * hf, h);
+      ptx::tmem_st16(tm_lane + Cols<N, P8>::krope(it & 1) + 16 * hf, h);
     } else {  // the rope bytes are E4M3 already
       uint32_t h[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) h[j] = valid ? rw[j] : 0u;
-      ptx::tmem_st8(tm_lane + Cols<N, P8>::KROPE + 8 * hf, h);
+      ptx::tmem_st8(tm_lane + Cols<N, P8>::krope(it & 1) + 8 * hf, h);
     }
     if (tr) MLA_TRACE_AT(P, 2, it);
   }
@@ -574,7 +581,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][g == 0 ? 4 : g - 1]);
-    if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::K + W * p, h);
+    if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
     if (tr) MLA_TRACE_AT(P, 3 + g, it);
   }
   ptx::tmem_wait_st();
@@ -599,7 +606,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
     // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
-    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_done, (it - 1) & 1, &s.abort_flag));
+    const bool ok = !dead && (it == 0 || ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag));
     if (ptx::bar_red_or(2, 256, !ok)) return;
     load_query<N, RAW_SLOTS, P8>(s, P, seg, cw * 32 + lane, seg_count & 3);
     ++seg_count;
@@ -679,7 +686,7 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
             for (int ks = 0; ks < KSTEPS; ++ks)
               mma(tm + Cols<N, P8>::sn(buf), tm + Cols<N, P8>::kpanel(p, par) + 8 * ks, q_desc + (q_off(p, ks) >> 4), (g | half | ks) != 0);
           }
-          if (g == 3) ptx::mma_commit(&s.k_done), ptx::mma_commit(&s.s_full[buf]);
+          if (g == 3) ptx::mma_commit(s.kdone_bar(it)), ptx::mma_commit(&s.s_full[buf]);
         }
       }
       if (leader) MLA_TRACE_AT(P, 17, it);
@@ -971,7 +978,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_SLOTS; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 4);
     for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[0][i], 8), ptx::mbar_init(&s.k_full[1][i], 8);
-    ptx::mbar_init(&s.k_done, 1);
+    ptx::mbar_init(&s.k_done[0], 1), ptx::mbar_init(&s.k_done[1], 1);
     ptx::mbar_init(&s.v_full[0], 8), ptx::mbar_init(&s.v_full[1], 8);
     for (int i = 0; i < 4; ++i) ptx::mbar_init(&s.vb_full[i], 8), ptx::mbar_init(&s.vb_free[i], 1);
     for (int i = 0; i < 2; ++i) {
