@@ -49,9 +49,9 @@ TOKEN_BYTES = 352
 # (README.md:194 and benchmarks/results/b200.csv:108 of the reference project).
 BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
 # DRAM bytes (read + write) per cached token of the decode kernel, from the committed ncu capture of a smaller case
-# (profiles/decode_kernel_h16_b8_64k_ncu_full.md: 209.0 MB for 524 288 tokens); traffic grows with the token count, so the
+# (profiles/decode_kernel_h16_b8_64k_ncu_full.md: 210.0 MB for 524 288 tokens); traffic grows with the token count, so the
 # benchmark scales it to its own workload.
-NCU_TRAFFIC_BYTES_PER_TOKEN = 399
+NCU_TRAFFIC_BYTES_PER_TOKEN = 401
 KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 
