@@ -14,6 +14,8 @@
 // to FP16 and writes it to tensor memory with tcgen05.st, chunk by chunk, so QK^T chases the conversion. Phase B,
 // once the previous tile's PV has released the V tile, copies the same FP16 values from tensor memory to the
 // swizzled V tile (tcgen05.ld + st.shared): the expensive arithmetic never waits for the V buffer.
+// In the 16-bit mode the rope chunk and the first latent chunk of odd tiles live in the 96 columns that K, S^T and O^T
+// leave over, so phase A of a tile starts while QK^T of the previous tile is still reading K.
 // FP16 holds e2m1 x e4m3 exactly (6 significant bits, 2^-10 .. 2688), so K and V are the cache's values bit for
 // bit; the query is converted to FP16 after an exact per-row power-of-two scaling that the score scale undoes.
 //
