@@ -327,6 +327,181 @@ def bench_dequant(args):
         "clocks": sampler.stop()}))
 
 
+LN2 = 0.6931471805599453
+
+
+def parity_check(mla, mdist, cache, dargs, kw, out, precision, seq, rank, world, dev):
+    """Outside the timed region: a sample of the step's output (first, middle and last request; 16 heads when there are
+    more) against the streamed dequantise-then-attention reference in torch on the GPU. 16-bit mode: max-abs <= 2e-2 and,
+    where the call returns it, natural-log LSE <= 1e-3; 8-bit mode: rel-L2 < 0.08. Sequence-sharded workloads: every
+    rank computes the reference over its own slice of the sampled request, the slices are merged with the exact
+    log-sum-exp weights on rank 0 and held against the merged output of the step. Returns a dict (rank 0 decides)."""
+    import torch
+    import torch.distributed as dist
+    from nvfp4_mla_b200.testing import attention_paged_nvfp4, rel_l2
+    B, H = cache.q_nope.shape[:2]
+    reqs = [B - 1] if seq else sorted({0, B // 2, B - 1})
+    heads = list(range(H)) if H <= 16 else list(range(3, H, H // 16))
+    a = list(dargs)
+    a[0], a[1] = cache.q_nope[:, heads].contiguous(), cache.q_pe[:, heads].contiguous()
+    want, want_lse = attention_paged_nvfp4(*a, requests=reqs)
+    lse_abs = None
+    if seq and world > 1:
+        ws = [torch.empty_like(want) for _ in range(world)]
+        ls = [torch.empty_like(want_lse) for _ in range(world)]
+        dist.all_gather(ws, want.contiguous())
+        dist.all_gather(ls, want_lse.contiguous())
+        ws, ls = torch.stack(ws).double(), torch.stack(ls).double()
+        tot = torch.logsumexp(ls, 0)
+        want = ((ls - tot).exp().unsqueeze(-1) * ws).sum(0).float()
+    elif precision == "bf16":
+        _, lse2 = mla.decode_partial(*dargs, **kw)
+        lse_abs = (lse2[reqs][:, heads] * LN2 - want_lse).abs().max().item()
+    got = out[reqs][:, heads].float()
+    max_abs, rel = (got - want).abs().max().item(), rel_l2(got, want)
+    if precision == "bf16":
+        ok = max_abs <= 2e-2 and rel < 4e-3 and (lse_abs is None or lse_abs <= 1e-3)
+    else:
+        ok = rel < 0.08
+    ok = ok and not bool(out.isnan().any())
+    return {"requests": reqs, "heads_sampled": len(heads), "max_abs": max_abs, "rel_l2": rel, "lse_abs": lse_abs, "ok": bool(ok),
+            "against": "streamed torch dequantise-then-attention on the GPU (the oracle's arithmetic), outside the timed region"}
+
+
+def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler, want_e2e=True):
+    """Generates the workload on this rank, runs warm-up + two timed passes (+ the end-to-end loop), returns a dict."""
+    import torch
+    import torch.distributed as dist
+    import nvfp4_mla_b200 as mla
+    from nvfp4_mla_b200 import _lib
+    from nvfp4_mla_b200 import dist as mdist
+    from nvfp4_mla_b200.testing import SM_SCALE, SyntheticCache
+
+    B, H, kv_len, ps, _ = WORKLOADS[workload]
+    seq = workload in SEQUENCE_SHARDED
+    if seq:
+        # every rank holds a contiguous 1/world slice of each request's pages (generated directly as the local slice:
+        # rank r's tokens are a seeded stream of their own), queries replicated
+        local_len = mdist.shard_sequence(kv_len, ps, world)[rank][2]
+        cache = SyntheticCache([local_len] * B, ps, H, 2.0 ** -9, 2.0 ** -6, seed=1000 + rank, device=dev)
+        qsrc = SyntheticCache([ps] * B, ps, H, 1.0, 1.0, seed=7, device=dev)
+        cache.q_nope, cache.q_pe = qsrc.q_nope, qsrc.q_pe
+        kv_len_local = local_len
+    else:
+        cache = SyntheticCache(request_lengths(kv_len, B, rank), ps, H, None, None, seed=rank, device=dev)
+        kv_len_local = kv_len[1] if isinstance(kv_len, tuple) else kv_len
+    kv_bytes = cache.kv_bytes
+    dargs = cache.args(SM_SCALE)
+    kw = dict(max_kv_len=kv_len_local, num_splits=args.num_splits, precision=precision)
+    if seq and world > 1:
+        merger = mdist.PartialMerger(B, H, dev)
+
+        def decode_fn(*a, **k):
+            return mdist.decode_sequence_sharded(*a, merger=merger, **k)
+    else:
+        decode_fn = mla.decode
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(warmup):
+        out = decode_fn(*dargs, **kw)
+    sync_all()
+    lib = _lib.load()
+    if sampler:
+        sampler.mark("timed_begin")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # Inputs larger than twice the L2 evict themselves between steps; smaller workloads get an L2 flush (a 256 MB
+    # write) before every step, and each step is then timed with its own event pair so that the flush is not counted.
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if kv_bytes < (256 << 20) else None
+    l2 = ("inputs larger than L2 (126 MB), no flush" if flush is None else
+          "256 MB written between timed steps (inputs smaller than 2 x L2); each step timed by its own event pair")
+    pairs = None if flush is None else [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                                        for _ in range(steps)]
+
+    def timed_pass(fn):
+        """K steps; returns (total ms over the steps, last output)."""
+        if flush is None:
+            ev0.record()
+            for _ in range(steps):
+                o = fn()
+            ev1.record()
+            sync_all()
+            return ev0.elapsed_time(ev1), o
+        for a, b in pairs:
+            flush.zero_()
+            a.record()
+            o = fn()
+            b.record()
+        sync_all()
+        return sum(a.elapsed_time(b) for a, b in pairs), o
+
+    # Pass 1, the reported step time: the call as a user makes it (its three kernels chained by programmatic dependent
+    # launch). Pass 2, the same K steps with the library's own event pair around the decode kernel (the roofline's
+    # duration): those events sit between the kernels and undo the chaining, so this pass is not the one reported.
+    total_ms, out = timed_pass(lambda: decode_fn(*dargs, **kw))
+    _lib.check(lib.nvfp4_mla_profile_begin(steps))
+    timed_pass(lambda: decode_fn(*dargs, **kw))
+    if sampler:
+        sampler.mark("timed_end")
+    kern_ms = (ctypes.c_float * steps)()
+    n_k = lib.nvfp4_mla_profile_end(kern_ms, steps)
+    if n_k < 0:
+        raise RuntimeError(lib.nvfp4_mla_last_error().decode())
+    res = {"workload": workload, "precision": precision, "B": B, "H": H, "kv_len": kv_len, "ps": ps, "seq": seq, "l2": l2,
+           "steps": steps, "kv_bytes": kv_bytes}
+    res["ms_step"] = max_over_ranks(total_ms / steps)
+    res["kernel_ms"] = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
+    if seq and world > 1:  # the local split-KV decode alone (no exchange, no merge): what the collective adds on top
+        local_ms, _ = timed_pass(lambda: mla.decode_partial(*dargs, **kw))
+        res["local_decode_ms"] = max_over_ranks(local_ms / steps)
+    if world > 1:
+        t = torch.tensor([float(kv_bytes)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        res["kv_bytes_all"] = float(t.item())
+    else:
+        res["kv_bytes_all"] = float(kv_bytes)
+    status = mla.workspace_status()
+    if status != 0:
+        raise SystemExit(f"decode failed: device-side status {status}")
+    res["parity_check"] = parity_check(mla, mdist, cache, dargs, kw, out, precision, seq, rank, world, dev)
+
+    if want_e2e:
+        # ---- end to end through the public API, per-step inputs from pinned host memory ------------------------
+        host = [t.cpu().pin_memory() for t in (cache.q_nope, cache.q_pe, cache.page_table, cache.kv_lens)]
+        devbuf = [torch.empty_like(t, device=dev) for t in host]
+        out_host = torch.empty(B, H, 512, dtype=torch.bfloat16).pin_memory()
+        res["h2d"] = sum(t.numel() * t.element_size() for t in host)
+        res["d2h"] = out_host.numel() * out_host.element_size()
+
+        def e2e_step():
+            for d, h in zip(devbuf, host):
+                d.copy_(h, non_blocking=True)
+            o = decode_fn(devbuf[0], devbuf[1], cache.ckv_cache, cache.ckv_sf_cache, cache.kpe_cache, devbuf[2], devbuf[3],
+                          SM_SCALE, cache.ckv_scale, cache.kpe_scale, **kw)
+            out_host.copy_(o, non_blocking=True)
+            return o
+
+        for _ in range(warmup):
+            e2e_step()
+        sync_all()
+        total_ms, _ = timed_pass(e2e_step)
+        res["e2e_ms"] = max_over_ranks(total_ms / steps)
+    del cache, out, flush
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -338,6 +513,8 @@ def main():
     ap.add_argument("--precision", default=None, choices=["bf16", "fp8"], help="override the workload's precision mode")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-seq-sharded", action="store_true",
+                    help="skip the sequence-sharded long-context pass that the default workload appends")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.workload == "writer_1m":
@@ -353,11 +530,16 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     B, H, kv_len, ps, precision = WORKLOADS[args.workload]
     precision = args.precision or precision
+    seq = args.workload in SEQUENCE_SHARDED
     config = {"workload": f"{args.workload}: B={B} per GPU, H={H}, kv_len={kv_len}, page_size={ps}, precision={precision}, "
                           f"seeded N(0,1) latent KV quantised to NVFP4 (calibrated global scales), shuffled page table",
               "parallelism": f"batch-sharded dp{world}, no collective", "num_splits": args.num_splits,
-              "l2": None,
+              "l2": "inputs larger than L2 (126 MB), no flush" if TOKEN_BYTES * B * (kv_len if isinstance(kv_len, int) else kv_len[0]) >= (256 << 20)
+                    else "256 MB written between timed steps (inputs smaller than 2 x L2); each step timed by its own event pair",
               "baseline": "reference SM100 tcgen05 kernel v3, 0.309 ms = 4.77 TB/s (published, B200)"}
+    if seq:
+        config["parallelism"] = f"sequence-sharded over {world} GPU(s): local split-KV decode, all-gather of (o, lse), merge"
+        config["workload"] = config["workload"].replace(f"B={B} per GPU", f"B={B} in total (queries replicated, each rank holds 1/{world} of every context)")
 
     if args.impl == "reference":
         # The reference's CPU path on this box's host cores; rank 0 alone works.
@@ -393,142 +575,20 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None  # started early: nvidia-smi takes a while to produce samples
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-
-    import nvfp4_mla_b200 as mla
-    from nvfp4_mla_b200 import _lib
-    from nvfp4_mla_b200.testing import SM_SCALE, SyntheticCache
-
-    seq = args.workload in SEQUENCE_SHARDED
-    if seq:
-        # every rank holds a contiguous 1/world slice of each request's pages (generated directly as the local slice:
-        # rank r's tokens are a seeded stream of their own), queries replicated
-        from nvfp4_mla_b200 import dist as mdist
-        local_len = mdist.shard_sequence(kv_len, ps, world)[rank][2]
-        cache = SyntheticCache([local_len] * B, ps, H, 2.0 ** -9, 2.0 ** -6, seed=1000 + rank, device=dev)
-        qsrc = SyntheticCache([ps] * B, ps, H, 1.0, 1.0, seed=7, device=dev)
-        cache.q_nope, cache.q_pe = qsrc.q_nope, qsrc.q_pe
-        config["parallelism"] = f"sequence-sharded over {world} GPU(s): local split-KV decode, all-gather of (o, lse), merge"
-        config["workload"] = config["workload"].replace(f"B={B} per GPU", f"B={B} in total (queries replicated, each rank holds 1/{world} of every context)")
-        kv_len_local = local_len
-    else:
-        cache = SyntheticCache(request_lengths(kv_len, B, rank), ps, H, None, None, seed=rank, device=dev)
-        kv_len_local = kv_len[1] if isinstance(kv_len, tuple) else kv_len
-    kv_bytes = cache.kv_bytes
-    dargs = cache.args(SM_SCALE)
-    kw = dict(max_kv_len=kv_len_local, num_splits=args.num_splits, precision=precision)
-    if seq:
-        def decode_fn(*a, **k):
-            return mdist.decode_sequence_sharded(*a, **k) if world > 1 else mla.decode(*a, **k)
-    else:
-        decode_fn = mla.decode
-
-    def sync_all():
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize(dev)
-
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-resident timing -------------------------------------------------------------------------------
     if sampler:
         sampler.mark("load_begin")
-    for _ in range(args.warmup):
-        out = decode_fn(*dargs, **kw)
-    sync_all()
-    lib = _lib.load()
-    if sampler:
-        sampler.mark("timed_begin")
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # Inputs larger than twice the L2 evict themselves between steps; smaller workloads get an L2 flush (a 256 MB
-    # write) before every step, and each step is then timed with its own event pair so that the flush is not counted.
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if kv_bytes < (256 << 20) else None
-    config["l2"] = ("inputs larger than L2 (126 MB), no flush" if flush is None else
-                    "256 MB written between timed steps (inputs smaller than 2 x L2); each step timed by its own event pair")
-    pairs = None if flush is None else [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                                        for _ in range(args.steps)]
 
-    def timed_pass():
-        """K steps of the hot path; returns (total ms over the steps, last output)."""
-        if flush is None:
-            ev0.record()
-            for _ in range(args.steps):
-                o = decode_fn(*dargs, **kw)
-            ev1.record()
-            sync_all()
-            return ev0.elapsed_time(ev1), o
-        for a, b in pairs:
-            flush.zero_()
-            a.record()
-            o = decode_fn(*dargs, **kw)
-            b.record()
-        sync_all()
-        return sum(a.elapsed_time(b) for a, b in pairs), o
-
-    # Pass 1, the reported step time: the call as a user makes it (its three kernels chained by programmatic dependent
-    # launch). Pass 2, the same K steps with the library's own event pair around the decode kernel (the roofline's
-    # duration): those events sit between the kernels and undo the chaining, so this pass is not the one reported.
-    total_ms, out = timed_pass()
-    _lib.check(lib.nvfp4_mla_profile_begin(args.steps))
-    timed_pass()
-    if sampler:
-        sampler.mark("timed_end")
-    kern_ms = (ctypes.c_float * args.steps)()
-    n_k = lib.nvfp4_mla_profile_end(kern_ms, args.steps)
-    if n_k < 0:
-        raise RuntimeError(lib.nvfp4_mla_last_error().decode())
-    ms_step = max_over_ranks(total_ms / args.steps)
-    kernel_ms = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
-    kv_bytes_all = kv_bytes
-    if world > 1:
-        t = torch.tensor([float(kv_bytes)], dtype=torch.float64, device=dev)
-        dist.all_reduce(t)
-        kv_bytes_all = float(t.item())
-    else:
-        kv_bytes_all = float(kv_bytes)
-    status = mla.workspace_status()
-    if status != 0 or bool(out.isnan().any()):
-        raise SystemExit(f"decode failed: status {status}")
-
-    # ---- end to end through the public API, per-step inputs from pinned host memory ---------------------------
-    host = [t.cpu().pin_memory() for t in (cache.q_nope, cache.q_pe, cache.page_table, cache.kv_lens)]
-    devbuf = [torch.empty_like(t, device=dev) for t in host]
-    out_host = torch.empty(B, H, 512, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host)
-    d2h = out_host.numel() * out_host.element_size()
-
-    def e2e_step():
-        for d, h in zip(devbuf, host):
-            d.copy_(h, non_blocking=True)
-        o = decode_fn(devbuf[0], devbuf[1], cache.ckv_cache, cache.ckv_sf_cache, cache.kpe_cache, devbuf[2], devbuf[3],
-                      SM_SCALE, cache.ckv_scale, cache.kpe_scale, **kw)
-        out_host.copy_(o, non_blocking=True)
-
-    for _ in range(args.warmup):
-        e2e_step()
-    sync_all()
-    if flush is None:
-        ev0.record()
-        for _ in range(args.steps):
-            e2e_step()
-        ev1.record()
-        sync_all()
-        total_ms = ev0.elapsed_time(ev1)
-    else:
-        for a, b in pairs:
-            flush.zero_()
-            a.record()
-            e2e_step()
-            b.record()
-        sync_all()
-        total_ms = sum(a.elapsed_time(b) for a, b in pairs)
-    e2e_ms = max_over_ranks(total_ms / args.steps)
+    m = measure(args, args.workload, precision, args.steps, args.warmup, rank, world, dev, sampler)
     clocks = sampler.stop() if sampler else None
+    # The default (headline) run also times the one path that has a collective: the long-context configuration with
+    # every request's pages cut over the ranks, local split-KV decode, all-gather of (o, lse) and merge.
+    seq_extra = None
+    if args.workload == "c2_h16_b64_64k" and not args.no_seq_sharded and args.precision is None:
+        sm = measure(args, "c4_h128_b2_1m_seq", "bf16", max(3, min(args.steps, 100)), args.warmup, rank, world, dev, None, want_e2e=False)
+        seq_extra = {"workload": "c4_h128_b2_1m_seq: B=2, H=128, kv_len=1048576 in total, bf16 mode, strong scaling",
+                     "n_gpus": world, "steps": sm["steps"], "ms_per_step": sm["ms_step"], "decode_ms": sm["kernel_ms"],
+                     "exchange_merge_us": (sm["ms_step"] - sm["local_decode_ms"]) * 1e3 if "local_decode_ms" in sm else 0.0,
+                     "kv_tbps": sm["kv_bytes_all"] / (sm["ms_step"] * 1e-3) / 1e12, "parity_check": sm["parity_check"]}
 
     if rank != 0:
         if world > 1:
@@ -536,9 +596,11 @@ def main():
         return
 
     peak, peak_kind = measured_peak()
+    kv_bytes, kernel_ms, ms_step = m["kv_bytes"], m["kernel_ms"], m["ms_step"]
     achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
     tokens = kv_bytes // TOKEN_BYTES
-    kernel_name = "mla_decode_hm_kernel" if (H % 128 == 0 and precision == "fp8") else "mla_decode_kernel"
+    kernel_name = ("mla_decode_hm_kernel" if (H % 128 == 0 and precision == "fp8") else
+                   "mla_decode_vt_kernel" if precision == "bf16" else "mla_decode_kernel")
     if H >= 128:  # 2176 flop per token and head: the tensor pipe is the bound, the HBM figure becomes secondary
         tpeak, tkind = measured_tensor_peak(precision)
         tflops = 2176.0 * H * tokens / (kernel_ms * 1e-3) / 1e12
@@ -546,11 +608,15 @@ def main():
                     "peak_kind": tkind, "kernel": kernel_name, "kernel_ms": kernel_ms,
                     "algorithmic_flops_per_launch": 2176.0 * H * tokens, "hbm_gbs": achieved, "traffic": None}
     else:
+        per_token = NCU_TRAFFIC_BYTES_PER_TOKEN.get(precision)
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "peak_kind": f"of {peak_kind}", "kernel": kernel_name, "kernel_ms": kernel_ms,
                     "algorithmic_bytes_per_launch": kv_bytes,
-                    "traffic": (NCU_TRAFFIC_BYTES_PER_TOKEN * tokens) if NCU_TRAFFIC_BYTES_PER_TOKEN else None}
-    value = kv_bytes_all / (ms_step * 1e-3) / 1e12
+                    "traffic": per_token * tokens if per_token else None,
+                    "traffic_kind": f"ncu capture of h16_b8_64k ({precision} mode, {per_token} B per token) scaled by tokens"
+                                    if per_token else None}
+    value = m["kv_bytes_all"] / (ms_step * 1e-3) / 1e12
+    config["l2"] = m["l2"]
     line = {
         "metric": "nvfp4_mla_decode_kv_bandwidth", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if seq else "weak",
@@ -558,14 +624,21 @@ def main():
         "dtype": "f16 operands, f32 accumulate" if precision == "bf16" else "e4m3 operands, f32 accumulate",
         "data": "synthetic", "config": config,
         "decode_us": ms_step * 1e3, "frac_of_8tbps": value / world / 8.0,
-        "e2e": {"value": kv_bytes_all / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": m["kv_bytes_all"] / (m["e2e_ms"] * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": m["e2e_ms"],
+                "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
         "gpu_launches": (KERNELS_PER_DECODE + (1 if seq and world > 1 else 0)) * args.steps,
         "roofline": roofline,
+        "parity_check": m["parity_check"],
         "clocks": clocks,
     }
+    if seq and "local_decode_ms" in m:
+        line["exchange_merge_us"] = (ms_step - m["local_decode_ms"]) * 1e3
+    if seq_extra:
+        line["seq_sharded"] = seq_extra
     if world == 1 and not args.no_cpu_baseline:
+        from nvfp4_mla_b200.testing import SyntheticCache
         n = args.cpu_sample_requests
+        cache = SyntheticCache(request_lengths(kv_len, B, 0)[:n], ps, H, None, None, seed=0, device="cpu")
         dt, nbytes, threads = cpu_reference_sample(cache, n)
         line["cpu_baseline"] = {"value": nbytes / dt / 1e12, "unit": "TB/s", "cores": threads, "kind": "port",
                                 "seconds": dt,
@@ -573,6 +646,9 @@ def main():
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    bad = [k for k, pc in (("headline", line["parity_check"]), ("seq_sharded", (seq_extra or {}).get("parity_check"))) if pc and not pc["ok"]]
+    if bad:
+        raise SystemExit(f"parity check failed: {bad}")
 
 
 if __name__ == "__main__":

@@ -79,18 +79,23 @@ NVFP4_MLA_API int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const u
  * (nvfp4_mla_decode_static_capacity() bytes, held by every GPU that loads the library until the process exits).
  * Arguments and results are those of nvfp4_mla_decode, without `workspace` / `workspace_bytes`.
  *
- *   - Limit: the call fails, launching nothing, when nvfp4_mla_decode_workspace_bytes(batch, heads, num_splits) exceeds
- *     the capacity. On a 148-SM B200 that allows batch * (heads / 16) * max(num_splits, 1) up to about 130, e.g.
- *     batch 64 with 16 heads, or batch 16 with 128 heads.
+ *   - Limit: the partial results take 2 KB per head, CTA and work item, so the call fails, launching nothing, when
+ *     (SMs + batch * (heads / 16) * max(num_splits, 1)) * 32.1 KB exceeds the capacity: on a 148-SM B200 that allows
+ *     batch * (heads / 16) * max(num_splits, 1) up to about 138 in either precision, e.g. batch 64 with 16 heads, or
+ *     batch 16 with 128 heads. The 8-bit mode normally groups 32 or 128 heads per CTA, which needs more scratch than
+ *     that; this entry point uses the widest grouping that fits and falls back to 16 heads per CTA (same results
+ *     within the mode's tolerance, slower at 128 heads).
  *   - Nothing is allocated or freed here, by CUDA or by any library, on any call.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and does the one-time
  *     kernel set-up; make that first call outside any stream capture.
  *   - All calls on a device share the one array. Calls that can overlap on the GPU (different streams, or graphs
  *     replayed concurrently) race on it and corrupt each other's results: serialise them, or give the concurrent
  *     ones their own workspace through nvfp4_mla_decode.
- *   - The array keeps what the previous call wrote. The one word that has to start from zero, the device-side status,
- *     is cleared on `stream` at the start of every call; nvfp4_mla_decode_static_status(stream) synchronises `stream`
- *     and returns the status of the calls made since (same codes as nvfp4_mla_workspace_status). */
+ *   - The array keeps what the previous call wrote. Nothing in it has to be cleared between calls: every record the
+ *     kernels read is rewritten by the call's own schedule kernel first. The device-side status word is zero when the
+ *     library is loaded and sticky afterwards: nvfp4_mla_decode_static_status(stream) synchronises `stream`, returns
+ *     the status of all static calls since it last reported a non-zero one (same codes as nvfp4_mla_workspace_status)
+ *     and, if it was non-zero, clears the word. */
 NVFP4_MLA_API int nvfp4_mla_decode_static(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache,
                                           const uint8_t* ckv_sf_cache, const uint8_t* kpe_cache, int64_t num_pages,
                                           int page_size, const int32_t* page_table, int64_t page_table_stride,
@@ -102,7 +107,9 @@ NVFP4_MLA_API int nvfp4_mla_decode_static_status(void* stream);
 
 /* Synchronises `stream` and returns the status word of a decode workspace: 0 = every kernel ran to completion,
  * 1 = a bounded wait inside the decode kernel gave up (results invalid), 2 = batch * num_splits too large for the
- * schedule kernel; negative = CUDA error (see nvfp4_mla_last_error). No counterpart in the reference, whose kernels
+ * schedule kernel, 3 = a page id inside a request's live range lies outside [0, num_pages) (it was not dereferenced:
+ * pages of 64 tokens or more read as zeros, smaller pages keep whatever the staging buffer held; results invalid);
+ * negative = CUDA error (see nvfp4_mla_last_error). No counterpart in the reference, whose kernels
  * have no bounded waits. */
 NVFP4_MLA_API int nvfp4_mla_workspace_status(const void* workspace, void* stream);
 
@@ -116,7 +123,9 @@ NVFP4_MLA_API int nvfp4_mla_profile_begin(int capacity);
 NVFP4_MLA_API int nvfp4_mla_profile_end(float* ms, int capacity);
 
 /* Whole-cache dequantisation: ckv = e2m1 * block_scale * ckv_scale, kpe = e4m3 * kpe_scale, in that multiply
- * order, to float (out_bf16 = 0) or bfloat16 (out_bf16 = 1). num_tokens = num_pages * page_size.
+ * order, to float (out_bf16 = 0) or bfloat16 (out_bf16 = 1). num_tokens = num_pages * page_size. ckv_cache must be
+ * 4-byte aligned, kpe_cache 2-byte, ckv_out 16-byte and kpe_out 8-byte aligned (checked; a misaligned pointer is an error
+ * return, never a device fault).
  * Replaces the pybind `dequantize` (nvfp4_mla/csrc/mla_decode.cu:1113-1132; nvfp4_mla/__init__.py:84-92). */
 NVFP4_MLA_API int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache, const uint8_t* kpe_cache,
                          int64_t num_tokens, float ckv_scale, float kpe_scale, int out_bf16, void* ckv_out,
@@ -144,6 +153,15 @@ NVFP4_MLA_API int nvfp4_mla_quantize_append(const void* ckv, const void* kpe, co
  * sequence-sharded decode across GPUs. */
 NVFP4_MLA_API int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32,
                       float* lse, void* stream);
+
+/* nvfp4_mla_combine over partials that are not densely stacked: part i has its o rows at o_part + i * o_part_stride
+ * floats and its lse values at lse_part + i * lse_part_stride floats. This is the shape of an all-gather of one packed
+ * [o | lse] record per GPU (sequence-sharded decode: o_part = buffer, lse_part = buffer + rows * 512, both strides
+ * rows * 513), merged without unpacking. o_part_stride must be a multiple of 4. Same reference counterpart as
+ * nvfp4_mla_combine (nvfp4_mla/csrc/mla_decode.cu:933-966, :1281-1294). */
+NVFP4_MLA_API int nvfp4_mla_combine_strided(const float* o_part, const float* lse_part, int parts, int64_t rows,
+                                            int64_t o_part_stride, int64_t lse_part_stride, void* out, float* out_f32,
+                                            float* lse, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,7 +8,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["decode", "dequantize", "decode_partial", "combine", "workspace_status", "quantize_append_paged_mla_kv_cache",
+__all__ = ["decode", "dequantize", "decode_partial", "combine", "combine_packed", "workspace_status", "quantize_append_paged_mla_kv_cache",
            "get_batch_indices_positions"]
 __version__ = "0.1.0"
 
@@ -53,7 +53,7 @@ def _workspace(device, stream, nbytes):
 
 
 def _decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens, sm_scale, ckv_scale, kpe_scale,
-            max_kv_len, num_splits, precision, want_out, want_partial):
+            max_kv_len, num_splits, precision, want_out, want_partial, partial_into=None):
     _check_cache(ckv_cache, ckv_sf_cache, kpe_cache)
     if q_nope.dim() != 3 or q_nope.shape[2] != CKV:
         raise RuntimeError("q_nope must be [batch, heads, 512]")
@@ -87,8 +87,14 @@ def _decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_len
             raise RuntimeError(lib.nvfp4_mla_last_error().decode())
         ws = _workspace(dev, stream, nbytes)
         out = torch.empty(B, H, CKV, dtype=torch.bfloat16, device=dev) if want_out else None
-        o32 = torch.empty(B, H, CKV, dtype=torch.float32, device=dev) if want_partial else None
-        lse = torch.empty(B, H, dtype=torch.float32, device=dev) if want_partial else None
+        if partial_into is not None:
+            o32, lse = partial_into
+            if not (o32.dtype == lse.dtype == torch.float32 and tuple(o32.shape) == (B, H, CKV) and tuple(lse.shape) == (B, H)
+                    and o32.is_contiguous() and lse.is_contiguous() and o32.device == dev and lse.device == dev):
+                raise RuntimeError("into must be contiguous float32 ([batch, heads, 512], [batch, heads]) tensors on the cache device")
+        else:
+            o32 = torch.empty(B, H, CKV, dtype=torch.float32, device=dev) if want_partial else None
+            lse = torch.empty(B, H, dtype=torch.float32, device=dev) if want_partial else None
         _lib.check(lib.nvfp4_mla_decode(
             _ptr(q_nope), _ptr(q_pe), _ptr(ckv_cache), _ptr(ckv_sf_cache), _ptr(kpe_cache), ckv_cache.shape[0], ps,
             _ptr(page_table), page_table.stride(0), _ptr(kv_lens), B, H, float(sm_scale), float(ckv_scale),
@@ -129,15 +135,38 @@ def decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens
 
 
 def decode_partial(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens, sm_scale,
-                   ckv_scale=1.0, kpe_scale=1.0, max_kv_len=None, num_splits=0, precision="bf16"):
+                   ckv_scale=1.0, kpe_scale=1.0, max_kv_len=None, num_splits=0, precision="bf16", into=None):
     """As ``decode`` but returns ``(o [batch, heads, 512] float32, lse [batch, heads] float32)`` with ``lse`` the
     log2-domain log-sum-exp of the scaled scores: the (o, lse) pair that ``combine`` merges, e.g. across GPUs that
-    each hold a slice of one long context. A request with ``kv_len == 0`` gives ``o = 0`` and ``lse = -inf``."""
+    each hold a slice of one long context. A request with ``kv_len == 0`` gives ``o = 0`` and ``lse = -inf``.
+    ``into=(o, lse)`` writes into caller-owned tensors (e.g. the send buffer of a collective) instead of new ones."""
     if precision not in _PRECISIONS:
         raise ValueError(f"precision must be one of {list(_PRECISIONS)}, got {precision!r}")
     _, o, lse = _decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens, sm_scale, ckv_scale,
-                        kpe_scale, max_kv_len, num_splits, _PRECISIONS[precision], False, True)
+                        kpe_scale, max_kv_len, num_splits, _PRECISIONS[precision], False, True, into)
     return o, lse
+
+
+def combine_packed(packed, rows, out_dtype=torch.bfloat16):
+    """Merge of ``packed [parts, rows * 513]`` float32, one record ``[o (rows x 512) | lse (rows)]`` per part: the
+    receive buffer of an all-gather of the ranks' partial results, merged in place of unpacking it. Returns
+    ``[rows, 512]`` in ``out_dtype``."""
+    if packed.dtype != torch.float32 or packed.dim() != 2 or packed.shape[1] != rows * (CKV + 1) or not packed.is_contiguous():
+        raise RuntimeError("packed must be a contiguous float32 [parts, rows * 513] tensor")
+    if not packed.is_cuda:
+        raise RuntimeError("packed must be a CUDA tensor")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"out_dtype must be bfloat16 or float32, got {out_dtype}")
+    dev = packed.device
+    out = torch.empty(rows, CKV, dtype=out_dtype, device=dev)
+    lib = _lib.load()
+    stride = rows * (CKV + 1)
+    with torch.cuda.device(dev):
+        _lib.check(lib.nvfp4_mla_combine_strided(
+            packed.data_ptr(), packed.data_ptr() + rows * CKV * 4, packed.shape[0], rows, stride, stride,
+            _ptr(out) if out_dtype == torch.bfloat16 else None, _ptr(out) if out_dtype == torch.float32 else None, None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
 
 
 def combine(o_part, lse_part, out_dtype=torch.bfloat16, return_lse=False):
@@ -231,9 +260,11 @@ def quantize_append_paged_mla_kv_cache(ckv, kpe, batch_indices, positions, ckv_c
         raise RuntimeError("quantize_append: a token named a request, position or page outside the tables")
 
 
-def workspace_status(device=None):
+def workspace_status(device=None, clear=False):
     """Synchronises and returns the worst device-side status of the decode workspaces of ``device`` (0 = fine,
-    1 = a bounded wait inside the decode kernel gave up, 2 = schedule capacity exceeded). For tests and debugging."""
+    1 = a bounded wait inside the decode kernel gave up, 2 = schedule capacity exceeded, 3 = a page id inside a request's
+    live range lies outside the cache; the id was not dereferenced). The status word is sticky; ``clear=True`` zeroes
+    it after reading. For tests and debugging."""
     lib = _lib.load()
     worst = 0
     for (idx, stream), ws in list(_workspaces.items()):
@@ -244,5 +275,8 @@ def workspace_status(device=None):
             st = lib.nvfp4_mla_workspace_status(_ptr(ws), None)
             if st < 0:
                 raise RuntimeError(lib.nvfp4_mla_last_error().decode())
+            if clear and st:
+                ws[:4].zero_()
+                torch.cuda.synchronize(idx)
             worst = max(worst, st)
     return worst

@@ -10,6 +10,7 @@
 #include "../../include/nvfp4_mla_b200.h"
 #include "mla_common.cuh"
 #include "mla_decode_sm100.cuh"
+#include "mla_decode_vt_sm100.cuh"
 #include "mla_decode_hm_sm100.cuh"
 #include "mla_dequant.cuh"
 #include "mla_quantize.cuh"
@@ -53,9 +54,11 @@ constexpr int kRawSlotsHm = 4;  // heads-as-M kernel: staging slots of 32 tokens
 // means less conversion work per head; 32 fit next to the tiles only in the 8-bit mode (tensor memory and shared memory).
 // With 128 heads per request the 8-bit mode runs the heads-as-M kernel: a pair of CTAs per 128 heads (each CTA
 // accumulates half of the output channels), scheduled as one unit, so the schedule sees half as many "CTAs".
-int heads_per_cta(int heads, int precision, const DeviceInfo& d) {
+// `limit` caps the grouping (a caller with little scratch asks for a narrower one: the partial results of a CTA take
+// 2 KB per head).
+int heads_per_cta(int heads, int precision, const DeviceInfo& d, int limit = 128) {
   if (precision != NVFP4_MLA_PRECISION_FP8) return 16;
-  return heads % 128 == 0 && d.hm_pairs > 0 ? 128 : heads % 32 == 0 ? 32 : 16;
+  return heads % 128 == 0 && d.hm_pairs > 0 && limit >= 128 ? 128 : heads % 32 == 0 && limit >= 32 ? 32 : 16;
 }
 int schedule_units(const DeviceInfo& d, int hpc) { return hpc == 128 ? d.hm_pairs : d.sm_count; }
 int ctas_per_unit(int hpc) { return hpc == 128 ? 2 : 1; }
@@ -64,18 +67,20 @@ DecodeKernel decode_kernel(int precision, int hpc) {
     return hpc == 128  ? mla::mla_decode_hm_kernel<kRawSlotsHm>
            : hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true>
                        : mla::mla_decode_kernel<16, kRawSlots8, true>;
-  return mla::mla_decode_kernel<16, kRawSlots16, false>;
+  if (getenv("NVFP4_MLA_OLD16")) return mla::mla_decode_kernel<16, kRawSlots16, false>;
+  return mla::mla_decode_vt_kernel;
 }
 size_t decode_smem(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
     return hpc == 128  ? mla::hm_smem_bytes<kRawSlotsHm>()
            : hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>()
                        : mla::decode_smem_bytes<16, kRawSlots8, true>();
-  return mla::decode_smem_bytes<16, kRawSlots16, false>();
+  if (getenv("NVFP4_MLA_OLD16")) return mla::decode_smem_bytes<16, kRawSlots16, false>();
+  return mla::vt_smem_bytes();
 }
 static_assert(mla::hm_smem_bytes<kRawSlotsHm>() <= 232448, "heads-as-M kernel exceeds the shared memory a CTA can opt in to");
 static_assert(mla::decode_smem_bytes<32, kRawSlots8, true>() <= 232448 && mla::decode_smem_bytes<16, kRawSlots8, true>() <= 232448 &&
-                  mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448,
+                  mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448 && mla::vt_smem_bytes() <= 232448,
               "decode kernel exceeds the 227 KB of shared memory a CTA can opt in to");
 
 // Per-device one-time setup (SM count, opt-in shared memory). Must first run outside stream capture.
@@ -219,11 +224,11 @@ int nvfp4_mla_version(void) { return 100; }
 const char* nvfp4_mla_last_error(void) { return g_error; }
 
 // workspace of one precision mode (the modes may group the heads differently); negative on error
-static int64_t workspace_bytes_of(int batch, int heads, int num_splits, int precision) {
+static int64_t workspace_bytes_of(int batch, int heads, int num_splits, int precision, int hpc_limit = 128) {
   DeviceInfo* d;
   if (device_info(&d)) return -1;
   mla::Problem pb;
-  const int hpc = heads_per_cta(heads, precision, *d);
+  const int hpc = heads_per_cta(heads, precision, *d, hpc_limit);
   if (problem_of(batch, heads, 1, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
   return int64_t(mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total);
 }
@@ -235,11 +240,12 @@ int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
   return a < 0 || b < 0 ? -1 : (a > b ? a : b);
 }
 
-int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
-                     const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
-                     int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale, float ckv_scale,
-                     float kpe_scale, int max_kv_len, int num_splits, int precision, void* out, float* out_f32, float* lse,
-                     void* workspace, int64_t workspace_bytes, void* stream) {
+// The decode call proper; `hpc_limit` caps the heads per CTA (see heads_per_cta).
+static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
+                       const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
+                       int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale, float ckv_scale,
+                       float kpe_scale, int max_kv_len, int num_splits, int precision, void* out, float* out_f32, float* lse,
+                       void* workspace, int64_t workspace_bytes, void* stream, int hpc_limit) {
   g_error[0] = 0;
   MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16 || precision == NVFP4_MLA_PRECISION_FP8,
             "precision must be 0 (bf16) or 1 (fp8), got %d", precision);
@@ -255,7 +261,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   DeviceInfo* d;
   if (device_info(&d)) return 1;
   mla::Problem pb;
-  const int hpc = heads_per_cta(heads, precision, *d);
+  const int hpc = heads_per_cta(heads, precision, *d, hpc_limit);
   if (problem_of(batch, heads, max_kv_len, num_splits, schedule_units(*d, hpc), hpc, &pb)) return 1;
   if (batch == 0) return 0;
   const mla::WsLayout L = mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta);
@@ -283,7 +289,7 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
   mla::DecodeParams P;
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
   P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
-  P.page_shift = __builtin_ctz(unsigned(page_size)), P.heads = heads, P.heads_per_cta = hpc;
+  P.page_shift = __builtin_ctz(unsigned(page_size)), P.num_pages = int(num_pages), P.heads = heads, P.heads_per_cta = hpc;
   P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
@@ -308,6 +314,16 @@ int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_ca
                               static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
                               static_cast<const float*>(o_part), out, out_f32, lse));
   return 0;
+}
+
+int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache,
+                     const uint8_t* kpe_cache, int64_t num_pages, int page_size, const int32_t* page_table,
+                     int64_t page_table_stride, const int32_t* kv_lens, int batch, int heads, float sm_scale, float ckv_scale,
+                     float kpe_scale, int max_kv_len, int num_splits, int precision, void* out, float* out_f32, float* lse,
+                     void* workspace, int64_t workspace_bytes, void* stream) {
+  return decode_impl(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, num_pages, page_size, page_table, page_table_stride, kv_lens,
+                     batch, heads, sm_scale, ckv_scale, kpe_scale, max_kv_len, num_splits, precision, out, out_f32, lse, workspace,
+                     workspace_bytes, stream, 128);
 }
 
 // ---- decode without caller-provided scratch -----------------------------------------------------------------------
@@ -346,26 +362,39 @@ int nvfp4_mla_decode_static(const void* q_nope, const void* q_pe, const uint8_t*
   g_error[0] = 0;
   MLA_CHECK(precision == NVFP4_MLA_PRECISION_BF16 || precision == NVFP4_MLA_PRECISION_FP8,
             "precision must be 0 (bf16) or 1 (fp8), got %d", precision);
-  const int64_t need = workspace_bytes_of(batch, heads, num_splits, precision);  // of the mode that will run
-  if (need < 0) return 1;  // message already set
-  MLA_CHECK(need <= int64_t(kStaticScratchBytes),
+  // The widest grouping of heads per CTA whose partial results fit the array: the 8-bit mode prefers 128 or 32 heads
+  // per CTA (2 KB of partial result per head and CTA), which needs more scratch than 16 heads per CTA do.
+  int limit = 128;
+  int64_t need = -1;
+  for (; limit >= 16; limit = limit == 128 ? 32 : limit == 32 ? 16 : 0) {
+    need = workspace_bytes_of(batch, heads, num_splits, precision, limit);
+    if (need < 0) return 1;  // message already set
+    if (need <= int64_t(kStaticScratchBytes)) break;
+  }
+  MLA_CHECK(limit >= 16,
             "problem too large for the built-in scratch: batch %d x heads %d x num_splits %d needs %lld bytes, the library holds "
             "%lld; use nvfp4_mla_decode with a caller-provided workspace",
             batch, heads, num_splits, (long long)need, (long long)kStaticScratchBytes);
   void* scratch = nullptr;
   if (static_scratch(&scratch)) return 1;
-  // the status word must start each call at zero: the array keeps whatever the previous call left in it
-  MLA_CUDA(cudaMemsetAsync(scratch, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
-  return nvfp4_mla_decode(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, num_pages, page_size, page_table, page_table_stride,
-                          kv_lens, batch, heads, sm_scale, ckv_scale, kpe_scale, max_kv_len, num_splits, precision, out, out_f32, lse,
-                          scratch, int64_t(kStaticScratchBytes), stream);
+  // Nothing of the array has to be cleared per call: the schedule kernel rewrites every record the other kernels read,
+  // and the status word (zero when the library is loaded) is sticky until nvfp4_mla_decode_static_status clears it.
+  return decode_impl(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, num_pages, page_size, page_table, page_table_stride, kv_lens,
+                     batch, heads, sm_scale, ckv_scale, kpe_scale, max_kv_len, num_splits, precision, out, out_f32, lse, scratch,
+                     int64_t(kStaticScratchBytes), stream, limit);
 }
 
 int nvfp4_mla_decode_static_status(void* stream) {
   g_error[0] = 0;
   void* scratch = nullptr;
   if (static_scratch(&scratch)) return -1;
-  return nvfp4_mla_workspace_status(scratch, stream);
+  const int status = nvfp4_mla_workspace_status(scratch, stream);
+  if (status > 0) {  // reported once: start the next run of calls from a clean word
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int), static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return -fail("clearing the status word failed: %s", cudaGetErrorString(e));
+  }
+  return status;
 }
 
 int nvfp4_mla_profile_begin(int capacity) {
@@ -414,8 +443,8 @@ int nvfp4_mla_dequantize(const uint8_t* ckv_cache, const uint8_t* ckv_sf_cache, 
   MLA_CHECK(num_tokens >= 0, "num_tokens must be non-negative");
   if (num_tokens == 0) return 0;
   MLA_CHECK(ckv_cache && ckv_sf_cache && kpe_cache && ckv_out && kpe_out, "null pointer argument");
-  MLA_CHECK(aligned(ckv_cache, 2) && aligned(kpe_cache, 2) && aligned(ckv_out, 16) && aligned(kpe_out, 8),
-            "caches must be 2-byte aligned, ckv_out 16-byte and kpe_out 8-byte aligned");
+  MLA_CHECK(aligned(ckv_cache, 4) && aligned(kpe_cache, 2) && aligned(ckv_out, 16) && aligned(kpe_out, 8),
+            "ckv_cache must be 4-byte and kpe_cache 2-byte aligned, ckv_out 16-byte and kpe_out 8-byte aligned");
   DeviceInfo* d;
   if (device_info(&d)) return 1;
   const long long warps_per_block = mla::kDequantThreads / 32;
@@ -463,8 +492,8 @@ int nvfp4_mla_quantize_append(const void* ckv, const void* kpe, const int32_t* b
   return 0;
 }
 
-int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32, float* lse,
-                      void* stream) {
+int nvfp4_mla_combine_strided(const float* o_part, const float* lse_part, int parts, int64_t rows, int64_t o_part_stride,
+                              int64_t lse_part_stride, void* out, float* out_f32, float* lse, void* stream) {
   g_error[0] = 0;
   MLA_CHECK(parts > 0 && rows >= 0, "parts must be positive and rows non-negative");
   MLA_CHECK(parts <= mla::kCombineMaxParts, "at most %d partials per row, got %d", mla::kCombineMaxParts, parts);
@@ -472,15 +501,22 @@ int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int
   MLA_CHECK(o_part && lse_part, "null pointer argument");
   MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
   MLA_CHECK(aligned(o_part, 16) && aligned(out, 8) && aligned(out_f32, 16), "o_part and out_f32 must be 16-byte, out 8-byte aligned");
+  MLA_CHECK(o_part_stride >= rows * mla::CKV && o_part_stride % 4 == 0 && lse_part_stride >= rows,
+            "o_part_stride must be a multiple of 4 floats and at least rows * 512, lse_part_stride at least rows");
   MLA_CHECK(rows < (int64_t(1) << 31), "rows must be below 2^31");
   if (rows <= 296)
-    mla::mla_combine_dense_kernel<4><<<unsigned(rows), 512, 0, static_cast<cudaStream_t>(stream)>>>(o_part, lse_part, parts, rows, out,
-                                                                                                   out_f32, lse);
+    mla::mla_combine_dense_kernel<4><<<unsigned(rows), 512, 0, static_cast<cudaStream_t>(stream)>>>(
+        o_part, lse_part, parts, rows, o_part_stride, lse_part_stride, out, out_f32, lse);
   else
-    mla::mla_combine_dense_kernel<1><<<unsigned(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(o_part, lse_part, parts, rows, out,
-                                                                                                   out_f32, lse);
+    mla::mla_combine_dense_kernel<1><<<unsigned(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        o_part, lse_part, parts, rows, o_part_stride, lse_part_stride, out, out_f32, lse);
   MLA_CUDA(cudaGetLastError());
   return 0;
+}
+
+int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32, float* lse,
+                      void* stream) {
+  return nvfp4_mla_combine_strided(o_part, lse_part, parts, rows, rows * mla::CKV, rows, out, out_f32, lse, stream);
 }
 
 }  // extern "C"

@@ -54,6 +54,7 @@ enum Status : int {
   kOk = 0,
   kWaitTimeout = 1,   // a bounded wait inside the decode kernel gave up
   kBadSchedule = 2,   // schedule kernel: batch * splits exceeds its scan capacity
+  kBadPage = 3,       // a page id of a request's live range lies outside [0, num_pages): its rows were not loaded
 };
 
 }  // namespace mla

@@ -125,14 +125,17 @@ __device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const Dec
         const int page = __shfl_sync(~0u, win_page, t - win0);
         const int page2 = __shfl_sync(~0u, win_page, t + kAhead - win0);
         if (lane == 0) {
-          const int row = (page << P.page_shift) + (tok & (ps - 1));
+          // a stale or corrupt id is never dereferenced: boxes beyond the last row of the cache read as zeros (see producer_role)
+          const bool bad = uint32_t(page) >= uint32_t(P.num_pages);
+          if (bad) atomicExch(P.header, int(kBadPage));
+          const int row = bad ? (P.num_pages << P.page_shift) : (page << P.page_shift) + (tok & (ps - 1));
           ptx::mbar_arrive_expect_tx(bar, kHmRows * TOKEN_BYTES);
           ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kHmRawCkvHi, ckv_map, 128, row, bar);
           ptx::tma_load_2d(dst + kHmRawSf, sf_map, 0, row, bar);
           ptx::tma_load_2d(dst + kHmRawKpe, kpe_map, 0, row, bar);
           const int tok_pf = tok + kAhead * kHmTile;  // L2 prefetch a few tiles ahead
-          if (tok_pf < seg.tok_end) {
+          if (tok_pf < seg.tok_end && uint32_t(page2) < uint32_t(P.num_pages)) {
             const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
             ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
             ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
@@ -141,13 +144,20 @@ __device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const Dec
           }
         }
       } else {
-        // small pages: one box per page that holds a valid token, lanes share the pages; scales and rope arrive unswizzled
+        // small pages: one box per page that holds a valid token (at most 32 per slot), one lane per page; scales and
+        // rope arrive unswizzled
         const int npages = (nvalid + ps - 1) >> P.page_shift;
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(npages) * ps * TOKEN_BYTES);
+        int page = lane < npages ? pt[(tok >> P.page_shift) + lane] : -1;
+        const bool ok_page = lane < npages && uint32_t(page) < uint32_t(P.num_pages);
+        if (lane < npages && !ok_page) atomicExch(P.header, int(kBadPage));
+        const uint32_t good = __popc(__ballot_sync(~0u, ok_page));
+        if (lane == 0) {
+          if (good) ptx::mbar_arrive_expect_tx(bar, good * ps * TOKEN_BYTES);
+          else ptx::mbar_arrive(bar);
+        }
         __syncwarp();
-        for (int pi = lane; pi < npages; pi += 32) {
-          const int page = pt[(tok >> P.page_shift) + pi];
-          const int row = page << P.page_shift, r0 = pi << P.page_shift;
+        if (ok_page) {
+          const int row = page << P.page_shift, r0 = lane << P.page_shift;
           ptx::tma_load_2d(dst + r0 * 128, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kHmRawCkvHi + r0 * 128, ckv_map, 128, row, bar);
           ptx::bulk_load(dst + kHmRawSf + r0 * 32, P.sf + (long long)row * 32, ps * 32, bar);

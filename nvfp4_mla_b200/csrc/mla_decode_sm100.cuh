@@ -84,6 +84,7 @@ struct DecodeParams {
   const int* page_table;
   long long pt_stride;
   int page_shift;  // log2(page_size)
+  int num_pages;   // page ids outside [0, num_pages) are never dereferenced: the rows stay unloaded and kBadPage is reported
   // Pages of at least a staging slot (64 tokens) arrive through swizzled tensor maps: the 32-byte scale rows with the
   // 32-byte swizzle (16-byte chunk ^= row / 4 % 2), the 64-byte rope rows with the 64-byte swizzle (chunk ^= row / 2 % 4),
   // so that 32 threads reading the same chunk of 32 consecutive rows touch every bank once. Smaller pages arrive
@@ -192,7 +193,11 @@ __device__ __forceinline__ void producer_role(Smem& s, const DecodeParams& P, co
       } else if (ps >= HALF) {
         if (lane == 0) {
           const int page = pt[tok >> P.page_shift];
-          const int row = (page << P.page_shift) + (tok & (ps - 1));
+          // A stale or corrupt id is never dereferenced: the boxes are taken beyond the last row of the cache instead,
+          // where TMA fills zeros (scale 0: the rows contribute score 0 and value 0), and the call is flagged.
+          const bool bad = uint32_t(page) >= uint32_t(P.num_pages);
+          if (bad) atomicExch(P.header, int(kBadPage));
+          const int row = bad ? (P.num_pages << P.page_shift) : (page << P.page_shift) + (tok & (ps - 1));
           ptx::mbar_arrive_expect_tx(bar, HALF * TOKEN_BYTES);
           ptx::tma_load_2d(dst, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kRawCkvHi, ckv_map, 128, row, bar);
@@ -202,21 +207,38 @@ __device__ __forceinline__ void producer_role(Smem& s, const DecodeParams& P, co
           const int tok_pf = tok + 6 * HALF;
           if (tok_pf < seg.tok_end) {
             const int page2 = pt[tok_pf >> P.page_shift];
-            const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
-            ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
-            ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
-            ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
-            ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+            if (uint32_t(page2) < uint32_t(P.num_pages)) {
+              const int row2 = (page2 << P.page_shift) + (tok_pf & (ps - 1));
+              ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
+              ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
+              ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
+              ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+            }
           }
         }
       } else {
-        // small pages: one box per page that holds a valid token, lanes share the pages
+        // small pages: one box per page that holds a valid token, lanes share the pages (at most 64 pages per slot)
         const int npages = (nvalid + ps - 1) >> P.page_shift;
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(npages) * ps * TOKEN_BYTES);
+        int page[2];
+        uint32_t good = 0;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int pi = lane + 32 * k;
+          page[k] = pi < npages ? pt[(tok >> P.page_shift) + pi] : -1;
+          const bool ok_page = pi < npages && uint32_t(page[k]) < uint32_t(P.num_pages);
+          if (pi < npages && !ok_page) atomicExch(P.header, int(kBadPage));
+          if (!ok_page) page[k] = -1;
+          good += __popc(__ballot_sync(~0u, ok_page));
+        }
+        if (lane == 0) {
+          if (good) ptx::mbar_arrive_expect_tx(bar, good * ps * TOKEN_BYTES);
+          else ptx::mbar_arrive(bar);
+        }
         __syncwarp();
-        for (int pi = lane; pi < npages; pi += 32) {
-          const int page = pt[(tok >> P.page_shift) + pi];
-          const int row = page << P.page_shift, r0 = pi << P.page_shift;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (page[k] < 0) continue;
+          const int row = page[k] << P.page_shift, r0 = (lane + 32 * k) << P.page_shift;
           ptx::tma_load_2d(dst + r0 * 128, ckv_map, 0, row, bar);
           ptx::tma_load_2d(dst + kRawCkvHi + r0 * 128, ckv_map, 128, row, bar);
           ptx::bulk_load(dst + kRawSf + r0 * 32, P.sf + (long long)row * 32, ps * 32, bar);

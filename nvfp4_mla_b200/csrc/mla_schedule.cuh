@@ -287,18 +287,19 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
   if (threadIdx.x == 0) MLA_STAMP(52, true);
 }
 
-// Dense partials [parts, rows, 512] / [parts, rows]: the merge a caller runs on (o, lse) pairs gathered from
-// several GPUs or produced by its own splits.
+// Dense partials: part i holds o rows at o_part + i * o_stride (floats) and lse values at lse_part + i * lse_stride. The
+// merge a caller runs on (o, lse) pairs gathered from several GPUs (one packed [o | lse] record per GPU) or produced by
+// its own splits ([parts, rows, 512] / [parts, rows]).
 template <int GROUPS>
 __global__ void __launch_bounds__(128 * GROUPS)
 mla_combine_dense_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, int parts, long long rows,
-                         void* out_bf16, float* out_f32, float* lse_out) {
+                         long long o_stride, long long lse_stride, void* out_bf16, float* out_f32, float* lse_out) {
   __shared__ float weights[kCombineMaxParts];
   __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
   const long long row = blockIdx.x;
   merge_row<GROUPS>(
-      parts, [&](int i) { return lse_part[(long long)i * rows + row]; },
-      [&](int i) { return o_part + ((long long)i * rows + row) * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
+      parts, [&](int i) { return lse_part[(long long)i * lse_stride + row]; },
+      [&](int i) { return o_part + (long long)i * o_stride + row * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
 }
 
 }  // namespace mla

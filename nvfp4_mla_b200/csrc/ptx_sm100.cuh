@@ -215,6 +215,28 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// 16x128b.x8: 16 lanes (taddr's lane, a multiple of 16 inside the warp's quadrant) x 32 columns. Thread (g = lane / 4,
+// q = lane % 4) writes register 2i to (lane g, column 4i + q) and register 2i + 1 to (lane g + 8, column 4i + q).
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// ldmatrix, 8-bit, transposing: two 16 x 16 byte matrices; lanes 0-15 give the row addresses (16 bytes each) of the
+// first, lanes 16-31 of the second. Thread (g = lane / 4, q = lane % 4) receives, per matrix, byte column g of rows
+// 4q .. 4q + 3 (first register) and byte column g + 8 of the same rows (second register).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t saddr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr)
+               : "memory");
+}
+
 // by array length
 __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
 __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }

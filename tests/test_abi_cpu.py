@@ -74,3 +74,24 @@ def test_python_host_rejects_bad_arguments_before_any_gpu_call():
         mla.combine(torch.zeros(2, 4, 512, dtype=torch.float16), torch.zeros(2, 4))
     with pytest.raises(RuntimeError, match="CUDA"):
         mla.combine(torch.zeros(2, 4, 512), torch.zeros(2, 4))
+
+
+def test_reference_style_imports_resolve():
+    """The import forms the reference's own tests and benchmarks use (tests/test_decode.py:8-10, benchmarks/bench.py:31)."""
+    import nvfp4_mla
+    from nvfp4_mla.testing import SM_SCALE, RandomCache, rel_l2
+    import nvfp4_mla_b200.testing as T
+    assert nvfp4_mla.decode is mla.decode and nvfp4_mla.dequantize is mla.dequantize
+    assert RandomCache is T.SyntheticCache and rel_l2 is T.rel_l2 and SM_SCALE == T.SM_SCALE
+    c = RandomCache([5, 40], 16, 16, seed=1)
+    assert c.ckv_cache.dtype == torch.uint8 and c.ckv_cache.shape[1:] == (16, 256)
+
+
+def test_dequantize_rejects_a_misaligned_cache_before_any_launch(lib):
+    """A ckv_cache pointer that is 2- but not 4-byte aligned must come back as an error code: the bf16 kernel loads
+    4-byte words from it, and a misaligned device address would fault the GPU."""
+    lib.nvfp4_mla_dequantize.restype = ctypes.c_int
+    lib.nvfp4_mla_dequantize.argtypes = _lib.SIGNATURES["nvfp4_mla_dequantize"][1]
+    lib.nvfp4_mla_last_error.restype = ctypes.c_char_p
+    rc = lib.nvfp4_mla_dequantize(0x10002, 0x20000, 0x30000, 64, 1.0, 1.0, 1, 0x40000, 0x50000, None)
+    assert rc != 0 and b"aligned" in lib.nvfp4_mla_last_error()

@@ -252,6 +252,33 @@ def test_rejects_bad_inputs():
         mla.decode(*a[:8], 0.0, 1.0)
 
 
+@pytest.mark.parametrize("precision,heads", [("bf16", 16), ("fp8", 16), ("fp8", 128)])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_page_ids_are_range_checked(page_size, precision, heads):
+    """A page id outside [0, num_pages) must never be dereferenced. Beyond a request's live pages the table may hold
+    anything (it is not read); inside the live range a bad id raises status 3 and the kernel loads nothing for it:
+    with pages of a staging slot or more the rows read as zeros (finite output), smaller pages are left unloaded.
+    The reference poisons everything out of range the same way (nvfp4_mla/testing.py:18-20, 47-50)."""
+    c = SyntheticCache([300, 200], page_size, heads, 0.5, 2.0, seed=8).to("cuda")
+    clean = mla.decode(*c.args(), max_kv_len=300, precision=precision)
+    check_status()
+    a = list(c.args())
+    pt = torch.cat([c.page_table, torch.full((2, 3), 1 << 30, dtype=torch.int32, device="cuda")], 1).contiguous()
+    n1 = math.ceil(200 / page_size)
+    pt[1, n1:] = -7                      # the shorter request's unused entries
+    a[5] = pt
+    out = mla.decode(*a, max_kv_len=300, precision=precision)
+    assert mla.workspace_status() == 0
+    assert torch.equal(out, clean)
+    pt[0, 1] = c.ckv_cache.shape[0]      # first id past the pool, inside request 0's live range
+    pt[1, 0] = -1
+    out = mla.decode(*a, max_kv_len=300, precision=precision)
+    assert mla.workspace_status(clear=True) == 3
+    if page_size >= 64:
+        assert not out.isnan().any()
+    assert mla.workspace_status() == 0
+
+
 def test_config1_shape_streamed_reference():
     """B=32, H=16, kv=8192 (DeepSeek-V3 TP8 shard): checked against the streamed torch reference on the GPU for a
     sample of requests, and through the split-invariance property for all of them."""
@@ -267,6 +294,49 @@ def test_config1_shape_streamed_reference():
     assert (lse2[reqs] * LN2 - want_lse).abs().max().item() <= 1e-3
     o_split = mla.decode_partial(*c.args(), max_kv_len=8192, num_splits=5)[0]
     assert (o_split - o32).abs().max().item() <= 1e-3   # property: the result does not depend on the split
+    check_status()
+
+
+def test_config2_shape_streamed_reference():
+    """B=64, H=16, kv=65536, bf16 mode: the configuration the headline metric is quoted on (1.48 GB of NVFP4 KV), at
+    its own size. A sample of requests (first, middle, last) against the streamed dequantise-then-attention reference on
+    the GPU, and the split-invariance property over all 64."""
+    c = SyntheticCache([65536] * 64, 64, 16, None, None, seed=0, device="cuda")
+    out = mla.decode(*c.args(), max_kv_len=65536)
+    o32, lse2 = mla.decode_partial(*c.args(), max_kv_len=65536)
+    check_status()
+    assert not out.isnan().any()
+    reqs = [0, 31, 63]
+    want, want_lse = attention_paged_nvfp4(*c.args(), requests=reqs)
+    err, rel = (out[reqs].float() - want).abs().max().item(), rel_l2(out[reqs], want)
+    lse_err = (lse2[reqs] * LN2 - want_lse).abs().max().item()
+    print(f"config 2: max-abs {err:.2e} rel-L2 {rel:.2e} lse {lse_err:.2e}")
+    assert err <= 2e-2 and rel < 4e-3 and lse_err <= 1e-3
+    o_split = mla.decode_partial(*c.args(), max_kv_len=65536, num_splits=3)[0]
+    assert (o_split - o32).abs().max().item() <= 1e-3   # property: the result does not depend on the split
+    check_status()
+
+
+def test_config4_shape_one_gpu():
+    """B=2, H=128, kv=1 048 576 each, bf16 mode (the long-context configuration on one GPU: page-table rows of 16 384
+    entries, 8 192 tiles per request, P summed over a million tokens): request 1 against the streamed reference on a
+    sample of 16 heads, plus split invariance over everything."""
+    c = SyntheticCache([1048576] * 2, 64, 128, 2.0 ** -9, 2.0 ** -6, seed=4, device="cuda")
+    out = mla.decode(*c.args(), max_kv_len=1048576)
+    o32, lse2 = mla.decode_partial(*c.args(), max_kv_len=1048576)
+    check_status()
+    assert not out.isnan().any()
+    heads = list(range(3, 128, 8))
+    a = list(c.args())
+    a[0], a[1] = c.q_nope[:, heads].contiguous(), c.q_pe[:, heads].contiguous()
+    want, want_lse = attention_paged_nvfp4(*a, requests=[1])
+    got = out[1:2, heads].float()
+    err, rel = (got - want).abs().max().item(), rel_l2(got, want)
+    lse_err = (lse2[1:2, heads] * LN2 - want_lse).abs().max().item()
+    print(f"config 4: max-abs {err:.2e} rel-L2 {rel:.2e} lse {lse_err:.2e}")
+    assert err <= 2e-2 and rel < 4e-3 and lse_err <= 1e-3
+    o_split = mla.decode_partial(*c.args(), max_kv_len=1048576, num_splits=5)[0]
+    assert (o_split - o32).abs().max().item() <= 1e-3
     check_status()
 
 

@@ -70,7 +70,15 @@ def _rank(rank, world, port, ret):
             o[b], lse[b] = ob[b], lb[b]
         out = mdist.merge_partials(torch.from_numpy(o), torch.from_numpy(lse), None, torch_combine, torch.float32)
         want = O.attention(*args)
-        ret[rank] = float(np.abs(out.numpy() - want).max())
+        err = float(np.abs(out.numpy() - want).max())
+        # the packed path: the partial is written into the merger's send record, one all-gather, merge from the records
+        mg = mdist.PartialMerger(len(lens), 16, "cpu")
+        mg.o.copy_(torch.from_numpy(o)), mg.lse.copy_(torch.from_numpy(lse))
+
+        def packed_combine(recv, rows, out_dtype):
+            return torch_combine(recv[:, :rows * 512].reshape(-1, rows, 512), recv[:, rows * 512:], out_dtype)
+        out2 = mg.merge(torch.float32, packed_combine)
+        ret[rank] = max(err, float(np.abs(out2.numpy() - want).max()))
     finally:
         dist.destroy_process_group()
 

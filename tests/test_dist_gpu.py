@@ -67,6 +67,13 @@ def _rank(rank, world, port, ret):
                                             c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32)
         torch.cuda.synchronize()
         err_seq = float(np.abs(out.cpu().numpy() - want).max())
+        # the same through preallocated buffers: the kernels write into the send record, one packed all-gather per step
+        mg = mdist.PartialMerger(len(c.kv_lens_list), 16, dev)
+        for _ in range(2):  # twice: the buffers are reused
+            out = mdist.decode_sequence_sharded(c.q_nope.to(dev), c.q_pe.to(dev), ckv, sf, kpe, pt, lens, SM_SCALE, c.ckv_scale,
+                                                c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32, merger=mg)
+            torch.cuda.synchronize()
+            err_seq = max(err_seq, float(np.abs(out.cpu().numpy() - want).max()))
         # ---- batch sharded: this rank's requests only
         mine = mdist.shard_batch(c.kv_lens_list, world)[rank]
         sub = SyntheticCache.__new__(SyntheticCache)
