@@ -48,10 +48,10 @@ TOKEN_BYTES = 352
 # Published by the reference for this exact shape on B200: its SM100 tcgen05 kernel, 0.309 ms = 4.77 TB/s
 # (README.md:194 and benchmarks/results/b200.csv:108 of the reference project).
 BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
-# DRAM bytes (read + write) per cached token of the decode kernel, from the committed ncu capture of a smaller case
-# (profiles/decode_kernel_h16_b8_64k_ncu_full.md: 210.0 MB for 524 288 tokens); traffic grows with the token count, so the
-# benchmark scales it to its own workload.
-NCU_TRAFFIC_BYTES_PER_TOKEN = 401
+# DRAM bytes (read + write) per cached token of the H=16 decode kernels, from ncu captures of a smaller case of the same
+# kernels (h16_b8_64k: 524 288 tokens); the kernels are persistent and stream each token once, so traffic grows with the
+# token count and the benchmark scales it to its own workload (roofline.traffic_kind says so).
+NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 401, "fp8": 398}
 KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 

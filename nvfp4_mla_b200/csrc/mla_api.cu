@@ -70,6 +70,10 @@ DecodeKernel decode_kernel(int precision, int hpc) {
   if (getenv("NVFP4_MLA_OLD16")) return mla::mla_decode_kernel<16, kRawSlots16, false>;
   return mla::mla_decode_vt_kernel;
 }
+unsigned decode_threads(int precision, int hpc) {
+  if (precision == NVFP4_MLA_PRECISION_FP8) return hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads;
+  return getenv("NVFP4_MLA_OLD16") ? mla::kDecodeThreads : mla::kVtThreads;
+}
 size_t decode_smem(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
     return hpc == 128  ? mla::hm_smem_bytes<kRawSlotsHm>()
@@ -209,11 +213,14 @@ int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, 
 
 }  // namespace
 
-#ifdef MLA_TRACE
-namespace { long long* g_trace = nullptr; }
+#ifdef MLA_VT_TRACE
 extern "C" NVFP4_MLA_API void nvfp4_mla_set_trace(long long* device_buffer) {
-  g_trace = device_buffer;
-  cudaMemcpyToSymbol(mla::d_trace_ptr, &device_buffer, sizeof(device_buffer));
+  cudaMemcpyToSymbol(mla::vt_trace_ptr, &device_buffer, sizeof(device_buffer));
+}
+#endif
+#ifdef MLA_VT_PROF
+extern "C" NVFP4_MLA_API void nvfp4_mla_set_prof(long long* device_buffer) {
+  cudaMemcpyToSymbol(mla::vt_prof_ptr, &device_buffer, sizeof(device_buffer));
 }
 #endif
 
@@ -293,13 +300,10 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
   P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
-#ifdef MLA_TRACE
-  P.trace = g_trace;
-#endif
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
   MLA_CUDA(launch_dependent_cluster(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)),
-                                    dim3(hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads), decode_smem(precision, hpc), st,
+                                    dim3(decode_threads(precision, hpc)), decode_smem(precision, hpc), st,
                                     unsigned(ctas_per_unit(hpc)), ckv_map, sf_map, kpe_map, P));
   if (prof) MLA_CUDA(cudaEventRecord(prof->stop[prof->used++], st));
 

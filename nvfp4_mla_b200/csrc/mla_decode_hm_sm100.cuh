@@ -111,7 +111,7 @@ __device__ __forceinline__ void hm_producer_role(HmSmem<RAW_SLOTS>& s, const Dec
         }
       const int slot = it % RAW_SLOTS;
       const uint32_t use = it / RAW_SLOTS;
-      bool ok = MLA_WAIT(P, 0, ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag));
+      bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
       const int tok = seg.tok0 + t * kHmTile + kHmRows * cg;
       int nvalid = seg.tok_end - tok;
@@ -187,9 +187,8 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
     const Seg seg = s.segs[si];
     for (int t = 0; t < 2 * seg.ntiles; ++t, ++it) {
       const int slot = it % RAW_SLOTS, kb = it % kHmKvBufs;
-      bool ok = MLA_WAIT(P, 1 | (256 << 8), ptx::mbar_wait(&s.raw_full[slot], (it / RAW_SLOTS) & 1, &s.abort_flag));
+      bool ok = ptx::mbar_wait(&s.raw_full[slot], (it / RAW_SLOTS) & 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
-      if (threadIdx.x == 256) MLA_TRACE_AT(P, 0, it);
       const uint8_t* raw = s.raw[slot];
       const bool valid = seg.tok0 + t * kHmTile + R < seg.tok_end;
       const bool full = seg.tok0 + (t + 1) * kHmTile <= seg.tok_end;  // warp-uniform: a live tile skips the masking
@@ -209,7 +208,7 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
       // the buffer's previous tile (it - kHmKvBufs) must have been consumed by the PV of both CTAs
-      ok = it < kHmKvBufs || MLA_WAIT(P, 2 | (256 << 8), ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag));
+      ok = it < kHmKvBufs || ptx::mbar_wait(&s.kv_free[kb], ((it / kHmKvBufs) - 1) & 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
       uint8_t* out_row = s.kv[kb][p] + R * 128;
       const uint32_t words[8] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w};
@@ -253,7 +252,6 @@ __device__ __forceinline__ void hm_convert_role(HmSmem<RAW_SLOTS>& s, const Deco
         if (cw == 0) ptx::mbar_arrive_expect_tx(&s.kv_full[kb], kHmPeerBytes);  // what the peer will send for this tile
         else ptx::mbar_arrive(&s.kv_full[kb]);
       }
-      if (threadIdx.x == 256) MLA_TRACE_AT(P, 7, it);
     }
   }
 }
@@ -295,10 +293,9 @@ __device__ __forceinline__ void hm_qk_role(HmSmem<RAW_SLOTS>& s, const DecodePar
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1, kb = it % kHmKvBufs;
       // the softmax warps have read the scores of tile it - 1
-      if (!__all_sync(~0u, it < 1 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.s_free, (it - 1) & 1, &s.abort_flag)))) return;
-      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.kv_full[kb], (it / kHmKvBufs) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, it < 1 || ptx::mbar_wait(&s.s_free, (it - 1) & 1, &s.abort_flag))) return;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.kv_full[kb], (it / kHmKvBufs) & 1, &s.abort_flag))) return;
       ptx::tc_fence_after_sync();
-      if (leader) MLA_TRACE_AT(P, 12, it);
       if (leader) {
         const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][0]), 16, 1024);
 #pragma unroll 1
@@ -312,7 +309,6 @@ __device__ __forceinline__ void hm_qk_role(HmSmem<RAW_SLOTS>& s, const DecodePar
         for (int ks = 0; ks < 2; ++ks)
           ptx::mma_f8_ss(tm + HmCols::S, qpe_desc + ((ks * 32) >> 4), k_desc + ((4 * kHmPanelBytes + ks * 32) >> 4), idesc, 1);
         ptx::mma_commit(&s.s_full);
-        MLA_TRACE_AT(P, 17, it);
       }
       __syncwarp();
     }
@@ -329,9 +325,8 @@ __device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodePar
     const int ntiles = 2 * s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1, kb = it % kHmKvBufs;
-      if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
       ptx::tc_fence_after_sync();
-      if (leader) MLA_TRACE_AT(P, 18, it);
       if (leader) {
         const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.kv[kb][2 * cg]), kHmPanelBytes, 1024);
 #pragma unroll
@@ -339,7 +334,6 @@ __device__ __forceinline__ void hm_pv_role(HmSmem<RAW_SLOTS>& s, const DecodePar
           ptx::mma_f8_ts(tm + HmCols::O, tm + HmCols::p(buf) + 8 * ks, v_desc + ((ks * 32 * 128) >> 4), idesc, (t | ks) != 0);
         ptx::mma_commit(&s.pv_done[buf]);
         ptx::mma_commit(&s.pv_local[kb]);
-        MLA_TRACE_AT(P, 19, it);
       }
       __syncwarp();
     }
@@ -366,7 +360,6 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     if (seg.ntiles <= 0) continue;
     // ---- query of (request seg.b, head group seg.hg), this head's row: channels [256 half, +256), rope with half 1.
     // Every MMA that read the previous segment's query has completed (both warps consumed the scores of its last tile).
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 24, si);
     const long long row = (long long)seg.b * P.heads + (long long)seg.hg * kHmHeads + h;
     const uint4* qn = reinterpret_cast<const uint4*>(P.q_nope + row * CKV) + 32 * half;
     const uint4* qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE);
@@ -450,16 +443,14 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.q_full);
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 25, si);
 
     float m = -INFINITY, l = 0.f;  // m is identical in the head's two threads; l is this thread's share of the sum
     const int ntiles = 2 * seg.ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      bool ok = MLA_WAIT(P, 8 | 32, ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag));
+      bool ok = ptx::mbar_wait(&s.s_full, it & 1, &s.abort_flag);
       // PV of tile it - 2 has read its P from the buffer this tile's P will overwrite (long done: it was issued two tiles ago)
       ok = ok && (it < 2 || ptx::mbar_wait(&s.pv_done[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
       ptx::tc_fence_after_sync();
       const int nvalid = seg.tok_end - (seg.tok0 + t * kHmTile) - 32 * half;  // this warp's columns at or beyond it are masked
       // raw scores of this head for this warp's 32 tokens; the score scale qa > 0 is applied inside the exponent
@@ -471,7 +462,6 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.s_free);  // QK^T of tile it + 1 may overwrite the scores
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       if (!ok || nvalid < 32) {  // tail tile: masked tokens get the score -inf
 #pragma unroll
         for (int j = 0; j < 32; ++j) sr[j] = (ok && j < nvalid) ? sr[j] : 0xFF800000u;
@@ -494,7 +484,7 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
         const float corr = need ? ((m == -INFINITY) ? 0.f : ptx::ex2(m - mn)) : 1.f;
         l *= corr, m = mn;
         if (t > 0) {  // O holds the segment's earlier tiles: wait for the PV of tile it - 1, then scale this head's half row
-          const bool okv = MLA_WAIT(P, 9 | 32, ptx::mbar_wait(&s.pv_done[buf ^ 1], ((it - 1) >> 1) & 1, &s.abort_flag));
+          const bool okv = ptx::mbar_wait(&s.pv_done[buf ^ 1], ((it - 1) >> 1) & 1, &s.abort_flag);
           if (ptx::bar_red_or(pair_bar, 64, !okv)) return;
           ptx::tc_fence_after_sync();
 #pragma unroll 1
@@ -509,7 +499,6 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
           ptx::tmem_wait_st();
         }
       }
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
       // P = 2^(s qa - m) as E4M3 into this warp's 8 of the tile's 16 P columns
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       uint32_t pk[8];
@@ -522,19 +511,15 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
         pk[c] = ptx::pack_e4m3x4(p0, p1, p2, p3);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
       ptx::tmem_st8(tm_lane + HmCols::p(buf) + 8 * half, pk);
       ptx::tmem_wait_st();
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
     // ---- segment epilogue: wait for the last PV, add the two halves of the sum, write this warp's 128 of the head's
     // 256 channels of the normalised partial
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, si);
     const bool ok = ptx::mbar_wait(&s.pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);
     s.xl[half][h] = l;
     if (ptx::bar_red_or(pair_bar, 64, !ok)) return;
@@ -556,7 +541,6 @@ __device__ __forceinline__ void hm_softmax_role(HmSmem<RAW_SLOTS>& s, const Deco
     if (cg == 0 && half == 0) P.lse_part[slot * kHmHeads + h] = lt > 0.f ? m + log2f(lt) : -INFINITY;
     ptx::tc_fence_before_sync();
     ptx::bar_sync(pair_bar, 64);  // s.xl and s.xch are reused by the next segment
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, si);
   }
 }
 

@@ -44,38 +44,6 @@ constexpr int kRawCkvHi = HALF * 128, kRawSf = 2 * HALF * 128, kRawKpe = kRawSf 
 constexpr int kVPanelBytes = TILE * 128;  // one 64-channel panel of the FP16 V tile
 constexpr int kTmemCols = 512;
 
-// Optional timeline tracing (compiled in with -DMLA_TRACE): CTA 0 records clock64() at pipeline events of its first
-// kTraceTiles tiles into trace[event][tile].
-#ifdef MLA_TRACE
-#ifndef MLA_TRACE_CTA
-#define MLA_TRACE_CTA 0  // the CTA whose pipeline events are recorded
-#endif
-constexpr int kTraceTiles = 64, kTraceEvents = 32;
-#define MLA_TRACE_AT(P, ev, tile)                                                             \
-  do {                                                                                        \
-    if ((P).trace && blockIdx.x == MLA_TRACE_CTA && (tile) < mla::kTraceTiles) (P).trace[(ev) * mla::kTraceTiles + (tile)] = clock64(); \
-  } while (0)
-// wait-time accounting: MLA_WAIT(P, slot, expr) evaluates the (waiting) expression and adds the cycles it took to
-// trace[31][slot] (CTA 0 only; meant to be used by one thread per role)
-#define MLA_WAIT(P, slot, expr)                                                                     \
-  ([&] {                                                                                            \
-    const long long t0_ = clock64();                                                                \
-    const bool r_ = (expr);                                                                         \
-    if ((P).trace && blockIdx.x == MLA_TRACE_CTA && (threadIdx.x & 31) == 0 && ((slot) < 32 || threadIdx.x == ((slot) >> 8)))                   \
-      atomicAdd(reinterpret_cast<unsigned long long*>((P).trace + 31 * mla::kTraceTiles + ((slot) & 31)), (unsigned long long)(clock64() - t0_)); \
-    return r_;                                                                                      \
-  }())
-#else
-#define MLA_TRACE_AT(P, ev, tile) do {} while (0)
-#define MLA_WAIT(P, slot, expr) (expr)
-#endif
-// Timing experiments (results become wrong): compile with -DMLA_EXPERIMENT=<bits>: 1 no V stores, 2 no K stores,
-// 4 no K loads, 8 no arithmetic, 16 no softmax exp / P stores, 32 no PV MMAs, 64 no latent QK MMAs
-#ifndef MLA_EXPERIMENT
-#define MLA_EXPERIMENT 0
-#endif
-#define MLA_EXP(P, bit) ((MLA_EXPERIMENT & (bit)) != 0)
-
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
   const __nv_bfloat16* q_pe;
@@ -97,9 +65,6 @@ struct DecodeParams {
   float* lse_part;
   float* o_part;
   int* header;
-#ifdef MLA_TRACE
-  long long* trace;
-#endif
 };
 
 template <int N, int RAW_SLOTS, bool P8>
@@ -179,10 +144,8 @@ __device__ __forceinline__ void producer_role(Smem& s, const DecodeParams& P, co
     for (int hk = 0; hk < 2 * seg.ntiles; ++hk, ++hcount) {
       const int slot = hcount % RAW_SLOTS;
       const uint32_t use = hcount / RAW_SLOTS;
-      if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 25, hcount >> 1);
-      bool ok = MLA_WAIT(P, 0, ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag));
+      bool ok = ptx::mbar_wait(&s.raw_empty[slot], (use & 1) ^ 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
-      if (lane == 0 && (hcount & 1) == 0) MLA_TRACE_AT(P, 24, hcount >> 1);
       const int tok = seg.tok0 + hk * HALF;
       int nvalid = seg.tok_end - tok;
       nvalid = nvalid < 0 ? 0 : (nvalid > HALF ? HALF : nvalid);
@@ -344,7 +307,6 @@ template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
 __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
                                              int lane, int quad, int hf) {
   static_assert(!P8, "the 8-bit mode uses convert_step");
-  const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
@@ -357,10 +319,8 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
   bool ok, valid = true;
   uint4 sf16 = make_uint4(0, 0, 0, 0);
   if (has_a) {
-    if (tr) MLA_TRACE_AT(P, 1, it);
-    ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag));
+    ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
-    if (tr) MLA_TRACE_AT(P, 0, it);
     valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
     sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((uint32_t(hf) ^ ((rr >> 2) & P.sf_swz_mask)) << 4));  // the 16 block scales of this half row
     // ---- rope chunk: 32 channels of this thread's half
@@ -378,19 +338,17 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
     }
     ptx::tmem_st16(tm_lane + Cols<N, P8>::krope(it & 1) + 16 * hf, h);
-    if (tr) MLA_TRACE_AT(P, 2, it);
   }
   uint32_t hb[W];  // a panel of tile it - 1 on its way from tensor memory to the V tile
   // stores panel g of tile it - 1 (in hb) to the V tile, once PV of tile it - 2 has finished with that 128-channel block
   auto store_v = [&](int g) -> bool {
     const uint32_t tb = it - 1;
-    const bool okv = tb < 1 || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag));
+    const bool okv = tb < 1 || ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag);
     if (!__all_sync(~0u, okv)) return false;
     uint8_t* vrow = s.v16[0][g + 4 * hf] + r * 128;
 #pragma unroll
-    for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c)
+    for (int c = 0; c < W / 4; ++c)
       *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
-    if (tr) MLA_TRACE_AT(P, 8 + g, it);
     return true;
   };
 #pragma unroll
@@ -410,15 +368,11 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
       }
     }
     if (has_b && g > 0 && !store_v(g - 1)) return false;
-    if (has_b && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p, (it - 1) & 1), hb);
+    if (has_b) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p, (it - 1) & 1), hb);
     auto convert_half = [&](int j0) {  // words j0 .. j0 + 3 of the panel -> h
 #pragma unroll
       for (int j = 0; j < 4; ++j) {  // word j0 + j = channels [8 (j0 + j), + 8) of the panel, scale block (j0 + j) / 2
         uint32_t e[4];
-        if (MLA_EXP(P, 8)) {
-          for (int i = 0; i < 4; ++i) h[4 * j + i] = (wds[j0 + j] + i + sc[0]) & 0x03FF03FFu;  // tiny finite values
-          continue;
-        }
         ptx::e2m1x8_to_f16x8(wds[j0 + j], e);
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[(j0 + j) >> 1]) : 0u;
@@ -449,14 +403,13 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
     if (has_a) {
       if (g == 1) {  // from here on the tile overwrites columns of the previous one: its QK^T must have finished
-        ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag));
+        ok = it == 0 || ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag);
         if (!__all_sync(~0u, ok)) return false;
         ptx::tc_fence_after_sync();
       }
-      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
+      ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
       convert_half(4);
-      if (!MLA_EXP(P, 2)) ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1) + W / 2, h);
-      if (tr) MLA_TRACE_AT(P, 3 + g, it);
+      ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1) + W / 2, h);
     }
   }
   if (has_b && !store_v(3)) return false;
@@ -465,7 +418,6 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][3]);
-    if (tr) MLA_TRACE_AT(P, 7, it);
   }
   if (has_b) {
     ptx::fence_proxy_async_smem();
@@ -487,7 +439,6 @@ __device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS
 template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
 __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
                                              int lane, int quad, int hf) {
-  const bool tr = (threadIdx.x == 128);  // first convert thread (tracing only)
   const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
   const int half = r >> 6, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
@@ -500,23 +451,22 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     const uint32_t tb = it - 1, vbuf = tb % VB;  // the tile being copied and its V buffer
     const uint32_t swz_v = uint32_t(r & 7) << 4;
     uint32_t hb[2][W];
-    if (!MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(4 * hf, tb & 1), hb[0]);
+    ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(4 * hf, tb & 1), hb[0]);
     // the PV that last read this V buffer (tile tb - VB) must have finished
-    ok = tb < VB || MLA_WAIT(P, 3 | (128 << 8), ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag));
+    ok = tb < VB || ptx::mbar_wait(&s.p_free[(tb - VB) & 1], ((tb - VB) >> 1) & 1, &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       const int p = g + 4 * hf;  // 64-channel panel; 16-bit mode: V panel p, 8-bit mode: half p % 2 of V panel p / 2
       ptx::tmem_wait_ld();
-      if (g < 3 && !MLA_EXP(P, 4)) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p + 1, tb & 1), hb[(g + 1) & 1]);
+      if (g < 3) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p + 1, tb & 1), hb[(g + 1) & 1]);
       const uint32_t* v = hb[g & 1];
       uint8_t* vrow = (P8 ? s.v16[vbuf][p >> 1] : s.v16[vbuf][p]) + r * 128;
 #pragma unroll
-      for (int c = 0; c < (MLA_EXP(P, 1) ? 0 : W / 4); ++c) {
+      for (int c = 0; c < W / 4; ++c) {
         const uint32_t chunk = P8 ? uint32_t(4 * (p & 1) + c) : uint32_t(c);
         *reinterpret_cast<uint4*>(vrow + ((chunk << 4) ^ swz_v)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
       }
-      if (tr) MLA_TRACE_AT(P, 8 + g, it);
     }
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
@@ -531,10 +481,8 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   const uint8_t* raw = s.raw[slot];
   const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
   const uint32_t swz = uint32_t(rr & 7) << 4;
-  if (tr) MLA_TRACE_AT(P, 1, it);
-  ok = MLA_WAIT(P, 1 | (128 << 8), ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag));
+  ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
   if (!__all_sync(~0u, ok)) return false;
-  if (tr) MLA_TRACE_AT(P, 0, it);
   const bool valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
   const uint4 sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((uint32_t(hf) ^ ((rr >> 2) & P.sf_swz_mask)) << 4));  // the 16 block scales of this half row
   {  // ---- rope chunk: 32 channels of this thread's half
@@ -542,7 +490,7 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
     const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
     // K of the previous tile may be overwritten once its QK^T has finished (the copy above has already read it)
-    ok = it == 0 || MLA_WAIT(P, 2 | (128 << 8), ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag));
+    ok = it == 0 || ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag);
     if (!__all_sync(~0u, ok)) return false;
     ptx::tc_fence_after_sync();
     const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
@@ -560,7 +508,6 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       for (int j = 0; j < 8; ++j) h[j] = valid ? rw[j] : 0u;
       ptx::tmem_st8(tm_lane + Cols<N, P8>::krope(it & 1) + 8 * hf, h);
     }
-    if (tr) MLA_TRACE_AT(P, 2, it);
   }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -585,10 +532,6 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 #pragma unroll
     for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block j / 2
       uint32_t e[4];
-      if (MLA_EXP(P, 8)) {
-        for (int i = 0; i < (P8 ? 2 : 4); ++i) h[(P8 ? 2 : 4) * j + i] = (wds[j] + i + sc[0]) & 0x07070707u;  // tiny finite values
-        continue;
-      }
       ptx::e2m1x8_to_f16x8(wds[j], e);
       if constexpr (!P8) {
 #pragma unroll
@@ -605,14 +548,12 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     ptx::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][g == 0 ? 4 : g - 1]);
-    if (!MLA_EXP(P, 2)) ptx::tmem_stn(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
-    if (tr) MLA_TRACE_AT(P, 3 + g, it);
+    ptx::tmem_stn(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
   }
   ptx::tmem_wait_st();
   ptx::tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][3]);
-  if (tr) MLA_TRACE_AT(P, 7, it);
   return true;
 }
 
@@ -685,10 +626,9 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t par = it & 1, buf = it & 1;
       // softmax of tile it - 2 must have read this S^T buffer
-      if (!__all_sync(~0u, it < 2 || MLA_WAIT(P, 4, ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, it < 2 || ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag))) return;
       // ---- S^T = K . Q^T : rope chunk into SP, latent chunks into SN
-      if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[par][4], (it >> 1) & 1, &s.abort_flag)))) return;
-      if (leader) MLA_TRACE_AT(P, 12, it);
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[par][4], (it >> 1) & 1, &s.abort_flag))) return;
       ptx::tc_fence_after_sync();
       if (leader) {
 #pragma unroll
@@ -699,12 +639,11 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       // group that has given most of its registers away
 #pragma unroll 1
       for (int g = 0; g < 4; ++g) {
-        if (!__all_sync(~0u, MLA_WAIT(P, 5, ptx::mbar_wait(&s.k_full[par][g], (it >> 1) & 1, &s.abort_flag)))) return;
-        if (leader) MLA_TRACE_AT(P, 13 + g, it);
+        if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[par][g], (it >> 1) & 1, &s.abort_flag))) return;
         ptx::tc_fence_after_sync();
         if (leader) {
 #pragma unroll 1
-          for (int half = 0; half < (MLA_EXP(P, 64) ? 0 : 2); ++half) {
+          for (int half = 0; half < 2; ++half) {
             const int p = g + 4 * half;
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
@@ -713,7 +652,6 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
           if (g == 3) ptx::mma_commit(s.kdone_bar(it)), ptx::mma_commit(&s.s_full[buf]);
         }
       }
-      if (leader) MLA_TRACE_AT(P, 17, it);
     }
   }
 }
@@ -736,20 +674,19 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][0]), 16, 1024);
       const uint64_t v_desc = v_desc0 + (((it % VB) * sizeof(s.v16[0])) >> 4);
       // ---- O^T += V^T . P^T
-      if (!__all_sync(~0u, MLA_WAIT(P, 6, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
       constexpr bool kVBlock = !P8;  // 16-bit mode: the single V tile is handed over per 128-channel block
-      if (!kVBlock && !__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag)))) return;
-      if (leader) MLA_TRACE_AT(P, 18, it);
+      if (!kVBlock && !__all_sync(~0u, ptx::mbar_wait(&s.v_full[it % VB], (it / VB) & 1, &s.abort_flag))) return;
       ptx::tc_fence_after_sync();
 #pragma unroll 1
       for (int mb = 0; mb < 4; ++mb) {
         if (kVBlock) {
-          if (!__all_sync(~0u, MLA_WAIT(P, 7, ptx::mbar_wait(&s.vb_full[mb], par, &s.abort_flag)))) return;
+          if (!__all_sync(~0u, ptx::mbar_wait(&s.vb_full[mb], par, &s.abort_flag))) return;
           ptx::tc_fence_after_sync();
         }
         if (leader) {
 #pragma unroll 1
-          for (int kh = 0; kh < (MLA_EXP(P, 32) ? 0 : (P8 ? 1 : 2)); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
+          for (int kh = 0; kh < (P8 ? 1 : 2); ++kh) {  // one P^T panel (128 bytes of tokens) per trip
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               const int row = (4 * kh + ks) * KROWS;  // first token of this K step
@@ -765,7 +702,6 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
           if (mb == 3) ptx::mma_commit(&s.p_free[buf]);
         }
       }
-      if (leader) MLA_TRACE_AT(P, 19, it);
     }
   }
 }
@@ -799,8 +735,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      bool ok = MLA_WAIT(P, 8 | (0 << 8) | 32, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 20, it);
+      bool ok = ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag);
       ptx::tc_fence_after_sync();
       float x[N];
       if (kScalesInRegs && !scales_loaded) {  // written by the convert warps before the segment's first K chunk was published
@@ -831,7 +766,6 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.s_free[buf]);  // QK^T of tile it + 2 may overwrite this S^T buffer
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 23, it);
       bool need = !ok;
 #pragma unroll
       for (int h = 0; h < N; ++h) need |= x[h] > m[h] + kGrow;
@@ -881,15 +815,13 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
           ptx::tmem_wait_st();
         }
       }
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 21, it);
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
-      if (it >= 2) MLA_WAIT(P, 9 | (0 << 8) | 32, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 28, it);
+      if (it >= 2) ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
       // P^T[head][token] = 2^(x - m) as FP16, and the row's share of the softmax denominators
       uint8_t* const p_base = s.p[buf][0] + p_off;
 #pragma unroll
-      for (int h = 0; h < (MLA_EXP(P, 16) ? 0 : N); ++h) {
+      for (int h = 0; h < N; ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
         if constexpr (P8)
@@ -897,17 +829,13 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
         else
           *reinterpret_cast<__half*>(p_base + h * 128 + (p_chunk ^ (uint32_t(h & 7) << 4))) = __float2half_rn(pv);
       }
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 29, it);
       ptx::fence_proxy_async_smem();
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 30, it);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
-      if (threadIdx.x == 0) MLA_TRACE_AT(P, 22, it);
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, 2 * si);
     bool ok = ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of the last tile
     if (ptx::bar_red_or(1, 128, !ok)) return;
     ptx::tc_fence_after_sync();
@@ -954,7 +882,6 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     }
     ptx::tc_fence_before_sync();
     ptx::bar_sync(1, 128);  // s.red is reused by the next segment
-    if (threadIdx.x == 0) MLA_TRACE_AT(P, 27, 2 * si + 1);
   }
 }
 
@@ -1020,19 +947,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
-  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 0);
-#ifdef MLA_TRACE
-  if (threadIdx.x == 0 && P.trace && blockIdx.x < 256) {  // rows 32..: per-CTA start / end / segment slots, global timer
-    long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    P.trace[32 * kTraceTiles + 4 * blockIdx.x] = gt;
-  }
-#endif
   ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
   // The combine kernel may be scheduled from here on: it reads the schedule at once (settled, as this grid has just
   // seen) and waits for this grid before it reads partials.
   ptx::grid_launch_dependents();
-  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 1);
 
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
@@ -1056,16 +974,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) MLA_TRACE_AT(P, 26, 2);
-#ifdef MLA_TRACE
-  if (threadIdx.x == 0 && P.trace && blockIdx.x < 256) {
-    long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    P.trace[32 * kTraceTiles + 4 * blockIdx.x + 1] = gt;
-    const int2 rg = P.cta_range[blockIdx.x];
-    P.trace[32 * kTraceTiles + 4 * blockIdx.x + 2] = rg.y - rg.x;
-  }
-#endif
   if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }

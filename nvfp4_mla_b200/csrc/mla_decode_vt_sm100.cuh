@@ -1,14 +1,24 @@
-// Weight-absorbed MLA decode, 16-bit mode, 16 heads per CTA: both MMAs take their A operand from TENSOR MEMORY.
+// Weight-absorbed MLA decode, 16-bit mode, 16 heads per CTA: QK^T runs on the cache's own bytes, PV on V^T in TENSOR
+// MEMORY; no 16-bit copy of a tile ever touches shared memory and K is never dequantised by a thread.
 //
-//   HBM --TMA--> raw ring (smem) --K warps--> K  as FP16 in tensor memory, lanes = tokens        --QK^T--> S^T (TMEM)
-//                               \--V warps--> V^T as FP16 in tensor memory, lanes = channel pairs --PV----> O^T (TMEM)
+//   HBM --TMA--> raw ring (smem) --------------------------------> A operand of QK^T (packed E2M1, as stored)
+//                               \--K warps--> cache block scales -> tensor memory (the MMA's scale factors of A)
+//                               \--V warps--> V^T as FP16 in tensor memory, lanes = channel pairs --PV--> O^T (TMEM)
 //
-// No 16-bit copy of the tile ever touches shared memory: the packed bytes are dequantised twice, once per layout.
-//   QK^T : S^T[token, head] = K[token, 576] . Q^T        A = K (lane = token, column j = channels 2j, 2j + 1),
-//          B = Q^T from smem, rope rows of Q pre-multiplied by kpe_scale / ckv_scale so one accumulator holds the score
+//   QK^T : S^T[token, head] = K[token, 512] . Q^T with tcgen05.mma kind::mxf4nvf4 (block-scaled FP4 x FP4, fp32
+//          accumulation): A = the packed ckv bytes exactly as TMA delivered them (K-major, 128-byte swizzle), its scale
+//          factors = the cache's E4M3 block scales, so K enters the product EXACTLY (e2m1 x e4m3, no rounding). The
+//          BF16 query cannot be an FP4 operand as it is; it is written once per request as a sum of four E2M1 terms,
+//          q * 2^k = sum_t s_t . c_t with one E4M3 scale s_t per row and term (a quarter of the residual's maximum, so
+//          the codes stay in [-4, 4] where E2M1 is spaced by at most 1) and c_t the nearest E2M1 codes of the residual:
+//          the residual shrinks by 8 per term, five terms reproduce q to 2^-15 of the row maximum (finer than the
+//          rounding of an FP16 operand), and the terms are five MMA chains into one accumulator.
+//          The rope part (64 E4M3 channels) is converted to FP16 and multiplied with kind::f16 into the same
+//          accumulator, with the rope rows of Q pre-multiplied by kpe_scale / ckv_scale.
 //   PV   : a byte of the cache holds one token's channels 2c and 2c + 1, and the conversion instruction turns it
-//          into the FP16 pair (V[t, 2c], V[t, 2c + 1]). That pair is stored as ONE 32-bit column entry of lane c, i.e.
-//          the contraction index is k = 2 t + parity, and the parity is sorted out on the B side:
+//          into the FP16 pair (V[t, 2c], V[t, 2c + 1]) (times the block scale: exact in FP16). That pair is stored as
+//          ONE 32-bit column entry of lane c, i.e. the contraction index is k = 2 t + parity, and the parity is sorted
+//          out on the B side:
 //              O^T[c, 2h + e] = sum_{t, par} A[c, 2t + par] . B[2t + par, 2h + e],   B[2t + par, 2h + e] = P[t, h] (par == e)
 //          so N = 32 (head, channel parity), M = 128 channel pairs per block (two blocks), and no value is ever
 //          shuffled between registers: thread data from a transposing 8-bit ldmatrix goes straight through
@@ -17,160 +27,346 @@
 //   (column 16 tg + 4 (t % 4) + (t % 16) / 4 for token 16 tg + t % 16); P^T uses the same order, and a contraction
 //   does not care about the order of its index.
 //
-// Tensor memory (512 columns): K 288 | V^T ring 4 x 32 | S^T 2 x 16 | O^T 2 x 32.
-//   K is single-buffered and released per chunk (rope, then four pairs of 64-channel panels), so the conversion of
-//   the next tile follows QK^T of this one chunk by chunk. V^T is a ring of four slots of 32 tokens x 128 channel
-//   pairs; a tile is eight slots. PV of tile j needs P(j), which exists about a tile after K(j) was converted, so the V
-//   warps run about one tile behind the K warps; the raw ring (six slots of 64 tokens) holds the bytes meanwhile.
-// The block scales as FP16 pairs (s, s) are computed once per tile by the K warps, which also park them in shared
-// memory ([block][token], two tiles) for the V warps; rows beyond the request's end get scale 0 there, so V is 0 and
-// finite wherever P is 0.
+// Tensor memory (512 columns): V^T ring 8 x 32 | rope K 2 x 32 | scale factors of A 2 x 32 | of B 16 | S^T 2 x 16 | O^T 2 x 32.
+//   V^T is a ring of eight slots of 32 tokens x 128 channel pairs = one tile: V^T(j) can be complete before P(j)
+//   exists, and the V warps of tile j + 1 follow PV of tile j slot by slot. Scale factors: the word of the four blocks
+//   of one K = 64 step of operand row r sits in lane r % 32 of every lane quadrant, column 4 step + r / 32.
+// Shared memory: raw ring of three 128-token tiles (packed low / high halves, block scales, rope), the query terms,
+//   P^T (two tiles), and the block scales as FP16 pairs (s, s) for the V warps: a ring of ten quarter tiles
+//   ([block][32 tokens] each), written by the K warps; rows beyond the request's end get scale 0 there, so V is 0 and
+//   finite wherever P is 0.
 //
-// Warp roles (512 threads): 0-3 softmax + epilogue, 4-7 K conversion (thread = token), 8-11 V^T conversion
-// (warp % 4 = lane quadrant = 32 channel pairs of each block), 12 QK^T issue, 13 TMA producer, 14 PV issue.
+// Warp roles (512 threads): 0-3 softmax + epilogue, 4-7 K side (thread = token: scale factors and rope into tensor
+// memory, scale table for the V warps; the query terms at the start of a request), 8-11 V^T conversion (warp % 4 = lane
+// quadrant = 32 channel pairs of each block), 12 QK^T issue, 13 TMA producer, 14 PV issue.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel reports kWaitTimeout.
 #pragma once
 #include "mla_decode_sm100.cuh"
 
 namespace mla {
 
-constexpr int kVtRawSlots = 6;
-constexpr int kVtRing = 4;
+#ifndef VT_DBG
+#define VT_DBG 0
+#endif
+constexpr int kVtRawSlots = 3;   // raw tiles in flight
+constexpr int kVtRing = 8;       // V^T slots (32 tokens x 128 channel pairs, 32 columns): one tile
+constexpr int kVtScRing = 12;    // quarter-tile scale tables (2 KB each)
+#ifndef VT_TERMS
+#define VT_TERMS 4
+#endif
+constexpr int kVtTerms = VT_TERMS;      // E2M1 terms of the query (even: two terms share an MMA)
+constexpr int kVtPasses = kVtTerms / 2;
+static_assert(kVtTerms % 2 == 0, "terms are stacked in pairs along N");
+constexpr int kVtThreads = 512;  // 16 warps: 4 softmax, 4 K side, 4 V^T conversion, QK^T / producer / PV issue, one spare
+// raw tile of 128 tokens: packed low halves | packed high halves | block scales | rope
+constexpr int kVtRawHi = TILE * 128, kVtRawSf = 2 * TILE * 128, kVtRawKpe = kVtRawSf + TILE * 32;
+constexpr int kVtRawTileBytes = TILE * TOKEN_BYTES;
+static_assert(kVtRawTileBytes % 1024 == 0, "raw tile alignment");
+
+#ifdef MLA_VT_PROF  // development builds: cycles spent in each kind of wait, per warp of one CTA
+__device__ long long* vt_prof_ptr;
+#define VT_WAIT(slot, expr)                                                                        \
+  ([&] {                                                                                           \
+    const long long t0_ = clock64();                                                               \
+    const bool r_ = (expr);                                                                        \
+    if ((threadIdx.x & 31) == 0) s.prof[threadIdx.x >> 5][slot] += clock64() - t0_;                \
+    return r_;                                                                                     \
+  }())
+#else
+#define VT_WAIT(slot, expr) (expr)
+#endif
+#ifdef MLA_VT_TRACE  // development builds: clock stamps of pipeline events of CTA 1's tiles 8..71
+__device__ long long* vt_trace_ptr;
+#define VT_EV(ev, tile)                                                                                              \
+  do {                                                                                                               \
+    if (vt_trace_ptr && blockIdx.x == 1 && (threadIdx.x & 31) == 0 && (tile) >= 8u && (tile) < 72u)                  \
+      vt_trace_ptr[(ev) * 64 + ((tile) - 8u)] = clock64();                                                           \
+  } while (0)
+#else
+#define VT_EV(ev, tile) do {} while (0)
+#endif
+#define VT_EVG(ev, g) VT_EV(ev, (g) - 100u)
 
 struct VtCols {
-  static constexpr uint32_t K = 0, KROPE = 256, VT = 288, S = 416, O = 448;
-  __host__ __device__ static constexpr uint32_t s(uint32_t buf) { return S + 16 * buf; }
+  // V^T ring | rope K | scale factors of A (two tiles) | scale factors of B (four columns per pass) | S^T (two tiles) | O^T
+  static constexpr uint32_t VT = 0, KROPE = 32 * kVtRing, SFA = KROPE + 32, SFB = SFA + 64, S = SFB + 4 * kVtPasses, O = S + 64;
   __host__ __device__ static constexpr uint32_t vt(uint32_t ring) { return VT + 32 * ring; }
+  __host__ __device__ static constexpr uint32_t sfa(uint32_t buf) { return SFA + 32 * buf; }
+  __host__ __device__ static constexpr uint32_t s(uint32_t buf) { return S + 32 * buf; }
   __host__ __device__ static constexpr uint32_t o(uint32_t mb) { return O + 32 * mb; }
   static_assert(O + 64 <= kTmemCols, "tensor memory overflow");
+  static_assert(SFA % 4 == 0 && SFB % 4 == 0 && kVtPasses <= 2, "scale-factor columns must be multiples of four (the B side is stored as eight)");
 };
 
 struct VtSmem {
-  alignas(1024) uint8_t q[9][16 * 128];         // Q^T: 8 latent panels + rope, K-major, 128-byte swizzle
-  alignas(1024) uint8_t p[2][4][32 * 128];      // P^T: [buffer][32-token group][row 2h + parity], 128-byte swizzle
-  alignas(1024) uint8_t raw[kVtRawSlots][kRawSlotBytes];
-  alignas(16) uint32_t sc[2][32][TILE];         // block scales as FP16 pairs (s, s): [tile parity][block][token]
+  alignas(1024) uint8_t q4[kVtPasses][2][32 * 128]; // query terms: packed E2M1, row 16 (term % 2) + head of pass term / 2, two 256-channel
+                                                    // panels, K-major, 128-byte swizzle
+  alignas(1024) uint8_t qrope[16 * 128];            // rope part of Q^T as FP16
+  alignas(1024) uint8_t p[2][4][32 * 128];          // P^T: [buffer][32-token group][row 2h + parity], 128-byte swizzle
+  alignas(1024) uint8_t raw[kVtRawSlots][kVtRawTileBytes];
+  alignas(16) uint16_t sc[kVtScRing][32][32];       // block scales as E4M3 byte pairs (b, b): [quarter tile][block][token slot], the
+                                                    // slot of token 16 h + 4 q + i of the quarter being 8 q + 4 h + i
   Seg segs[kSegBatch];
-  float qa[4][16];                              // per-head score scale, ring indexed by segment count
+  float qa[4][16];                                  // per-head score scale, ring indexed by segment count
   float red[4][16];
   float corr[16];
+  uint32_t sfb[kVtTerms][16];                       // scale word of (term, head) on its way to tensor memory
   alignas(8) uint64_t raw_full[kVtRawSlots];
   uint64_t raw_empty[kVtRawSlots];
-  uint64_t k_full[5], k_free[5];                // K chunk written / read by QK^T: rope, panels {0,1}, {2,3}, {4,5}, {6,7}
+  uint64_t k_full[2], k_free[2];                    // K side of the tile in tensor memory / QK^T of the tile complete
+  uint64_t rope_free;                               // QK^T's rope MMAs of the tile complete (rope K is single-buffered)
   uint64_t s_full[2], s_free[2];
   uint64_t p_full[2], p_free[2];
   uint64_t vt_full[kVtRing], vt_free[kVtRing];
-  uint64_t sc_full[2], sc_free[2];
+  uint64_t sc_full[kVtScRing], sc_free[kVtScRing];
   uint32_t tmem_base;
   int abort_flag;
+#ifdef MLA_VT_PROF
+  long long prof[20][8];
+#endif
 };
 constexpr size_t vt_smem_bytes() { return sizeof(VtSmem) + 1024; }
 
 // ---------------------------------------------------------------------------------------------------------------
-// role: K conversion (4 warps; thread = token row of the tile = tensor-memory lane)
+// role: TMA producer (one warp; lane 0 issues, all lanes help with the page ids of small pages)
 // ---------------------------------------------------------------------------------------------------------------
-// The query of a segment: 16 rows x (512 + 64) BF16, rope part times kpe_scale / ckv_scale, each row scaled by a power
-// of two so that its largest magnitude lies in [2^14, 2^15), converted to FP16 and stored K-major with the 128-byte
-// swizzle. Eight consecutive threads share a row, so the row maximum is three shuffles away.
-__device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, const Seg& seg, int kt, int par) {
+__device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& P, const CUtensorMap* ckv_map, const CUtensorMap* sf_map,
+                                                 const CUtensorMap* kpe_map, int n_segs, uint32_t& it) {
+  const int lane = ptx::lane_id();
+  const int ps = 1 << P.page_shift;
+  for (int si = 0; si < n_segs; ++si) {
+    const Seg seg = s.segs[si];
+    if (seg.ntiles <= 0) continue;
+    const int* pt = P.page_table + (long long)seg.b * P.pt_stride;
+    for (int t = 0; t < seg.ntiles; ++t, ++it) {
+      const int slot = it % kVtRawSlots;
+      const int tok = seg.tok0 + t * TILE;
+      int nvalid = seg.tok_end - tok;
+      nvalid = nvalid < 0 ? 0 : (nvalid > TILE ? TILE : nvalid);
+      // page ids of the two half tiles and of the two that are prefetched into L2 (three tiles ahead: the ring itself is
+      // too shallow to cover HBM latency), read before the wait for the slot so that their latency hides behind it
+      int page[2] = {0, 0}, page_pf[2] = {-1, -1};
+      if (ps >= HALF && lane == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int tk = tok + h * HALF;
+          if (tk < seg.tok_end) page[h] = pt[tk >> P.page_shift];
+          if (tk + 3 * TILE < seg.tok_end) page_pf[h] = pt[(tk + 3 * TILE) >> P.page_shift];
+        }
+      }
+      const bool ok = ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag);
+      if (!__all_sync(~0u, ok)) return;
+      VT_EV(0, it);
+      uint8_t* dst = s.raw[slot];
+      uint64_t* bar = &s.raw_full[slot];
+      if (nvalid == 0) {
+        if (lane == 0) ptx::mbar_arrive(bar);
+      } else if (ps >= HALF) {
+        if (lane == 0) {
+          const int nh = nvalid > HALF ? 2 : 1;  // half tiles that hold a live token
+          ptx::mbar_arrive_expect_tx(bar, uint32_t(nh) * HALF * TOKEN_BYTES);
+          for (int h = 0; h < nh; ++h) {
+            const int tk = tok + h * HALF;
+            // A stale or corrupt id is never dereferenced: the boxes are taken beyond the last row of the cache instead,
+            // where TMA fills zeros (scale 0: the rows contribute score 0 and value 0), and the call is flagged.
+            const bool bad = uint32_t(page[h]) >= uint32_t(P.num_pages);
+            if (bad) atomicExch(P.header, int(kBadPage));
+            const int row = bad ? (P.num_pages << P.page_shift) : (page[h] << P.page_shift) + (tk & (ps - 1));
+            ptx::tma_load_2d(dst + h * HALF * 128, ckv_map, 0, row, bar);
+            ptx::tma_load_2d(dst + kVtRawHi + h * HALF * 128, ckv_map, 128, row, bar);
+            ptx::tma_load_2d(dst + kVtRawSf + h * HALF * 32, sf_map, 0, row, bar);
+            ptx::tma_load_2d(dst + kVtRawKpe + h * HALF * 64, kpe_map, 0, row, bar);
+          }
+          for (int h = 0; h < 2; ++h) {
+            if (uint32_t(page_pf[h]) < uint32_t(P.num_pages)) {
+              const int row2 = (page_pf[h] << P.page_shift) + ((tok + h * HALF) & (ps - 1));
+              ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
+              ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
+              ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
+              ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+            }
+          }
+        }
+      } else {
+        // small pages: one box per page that holds a live token (at most 128 per tile), lanes share the pages;
+        // scales and rope arrive through linear bulk copies (unswizzled)
+        const int npages = (nvalid + ps - 1) >> P.page_shift;
+        int page[4];
+        uint32_t good = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int pi = lane + 32 * k;
+          page[k] = pi < npages ? pt[(tok >> P.page_shift) + pi] : -1;
+          const bool ok_page = pi < npages && uint32_t(page[k]) < uint32_t(P.num_pages);
+          if (pi < npages && !ok_page) atomicExch(P.header, int(kBadPage));
+          if (!ok_page) page[k] = -1;
+          good += __popc(__ballot_sync(~0u, ok_page));
+        }
+        if (lane == 0) {
+          if (good) ptx::mbar_arrive_expect_tx(bar, good * ps * TOKEN_BYTES);
+          else ptx::mbar_arrive(bar);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (page[k] < 0) continue;
+          const int row = page[k] << P.page_shift, r0 = (lane + 32 * k) << P.page_shift;
+          ptx::tma_load_2d(dst + r0 * 128, ckv_map, 0, row, bar);
+          ptx::tma_load_2d(dst + kVtRawHi + r0 * 128, ckv_map, 128, row, bar);
+          ptx::bulk_load(dst + kVtRawSf + r0 * 32, P.sf + (long long)row * 32, ps * 32, bar);
+          ptx::bulk_load(dst + kVtRawKpe + r0 * 64, P.kpe + (long long)row * 64, ps * 64, bar);
+        }
+      }
+      __syncwarp();
+      VT_EV(1, it);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// role: K side (4 warps; thread = token row of the tile)
+// ---------------------------------------------------------------------------------------------------------------
+// The query of a segment, by the 128 K threads: row n = thread / 8, channels [64 sub, 64 sub + 64) with sub = thread % 8.
+// The row (latent part, and rope part times kpe_scale / ckv_scale) is scaled by 2^(6 - e), e = floor(log2(row maximum)).
+// Latent part: E2M1 terms; term t has ONE E4M3 scale per row, amax(residual) / 4 rounded, the codes are the nearest
+// E2M1 of residual / scale (saturating), and the residual is updated with what the codes decode to, so every term
+// corrects the rounding of the ones before it. Rope part: FP16, K-major with the 128-byte swizzle.
+__device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, const Seg& seg, int kt, int par, int lane, int quad) {
   const int n = kt >> 3, sub = kt & 7;
   const long long row = (long long)seg.b * P.heads + (long long)seg.hg * 16 + n;
-  uint4 qn[8];
+  float r[64];
+  {
+    uint4 qn[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) qn[k] = reinterpret_cast<const uint4*>(P.q_nope + row * CKV)[sub + 8 * k];
+    for (int k = 0; k < 8; ++k) qn[k] = reinterpret_cast<const uint4*>(P.q_nope + row * CKV)[8 * sub + k];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t w[4] = {qn[k].x, qn[k].y, qn[k].z, qn[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[8 * k + 2 * j] = __uint_as_float(w[j] << 16), r[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+  }
   const uint4 qp = reinterpret_cast<const uint4*>(P.q_pe + row * KPE)[sub];
   const float ratio = P.kpe_scale / P.ckv_scale;
-  auto finite = [](uint32_t bits) { return bits < 0x7F800000u ? bits : 0u; };  // inf / nan do not set the scale
-  uint32_t m = 0;
+  auto finite = [](float v) { const uint32_t b = __float_as_uint(v) & 0x7FFFFFFFu; return b < 0x7F800000u ? b : 0u; };  // inf / nan do not set the scale
+  auto row_max = [&](uint32_t m) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint32_t w[4] = {qn[k].x, qn[k].y, qn[k].z, qn[k].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) m = max(m, max(finite((w[j] << 16) & 0x7FFFFFFFu), finite(w[j] & 0x7FFF0000u)));
-  }
+    for (int o = 1; o < 8; o <<= 1) m = max(m, __shfl_xor_sync(~0u, m, o));
+    return m;
+  };
   float pe[8];
+  uint32_t m_pe = 0, m = 0;
   {
     const uint32_t w[4] = {qp.x, qp.y, qp.z, qp.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       pe[2 * j] = __uint_as_float(w[j] << 16) * ratio, pe[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u) * ratio;
-      m = max(m, max(finite(__float_as_uint(pe[2 * j]) & 0x7FFFFFFFu), finite(__float_as_uint(pe[2 * j + 1]) & 0x7FFFFFFFu)));
+      m_pe = max(m_pe, max(finite(pe[2 * j]), finite(pe[2 * j + 1])));
     }
   }
 #pragma unroll
-  for (int o = 1; o < 8; o <<= 1) m = max(m, __shfl_xor_sync(~0u, m, o));
-  int e = int(m >> 23) - 127;  // floor(log2(amax)); -127 for 0 / subnormal rows
+  for (int i = 0; i < 64; ++i) m = max(m, finite(r[i]));
+  m = row_max(m), m_pe = row_max(m_pe);
+  // e = floor(log2(latent maximum)), so that the four E4M3 term scales stay in the format's normal range; raised if the rope
+  // part (FP16, at most 2^15 after scaling) is more than 2^8 times larger
+  int e = int(m >> 23) - 127, e_pe = int(m_pe >> 23) - 127;
+  e = e > e_pe - 8 ? e : e_pe - 8;
   e = e < -100 ? -100 : e;
-  const float up = __uint_as_float(uint32_t(14 - e + 127) << 23);  // 2^(14 - e), exact
-  const uint32_t swz = uint32_t(sub ^ (n & 7)) << 4;
+  const float up = __uint_as_float(uint32_t(6 - e + 127) << 23);  // 2^(6 - e), exact: the row maximum lands in [64, 128)
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint32_t w[4] = {qn[k].x, qn[k].y, qn[k].z, qn[k].w};
-    uint32_t h[4];
+  for (int i = 0; i < 64; ++i) {
+    r[i] *= up;
+    if (!(fabsf(r[i]) < INFINITY)) r[i] = 0.f;  // a non-finite query element has no meaningful result anyway; keep the rest of the row intact
+  }
+  const uint32_t panel = uint32_t(sub) >> 2, c0 = 2 * (uint32_t(sub) & 3);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) h[j] = ptx::f32x2_to_f16x2(__uint_as_float(w[j] << 16) * up, __uint_as_float(w[j] & 0xFFFF0000u) * up);
-    *reinterpret_cast<uint4*>(s.q[k] + n * 128 + swz) = make_uint4(h[0], h[1], h[2], h[3]);
+  for (int t = 0; t < kVtTerms; ++t) {
+    uint32_t mt = 0;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) mt = max(mt, __float_as_uint(r[i]) & 0x7FFFFFFFu);
+    mt = row_max(mt);
+    const uint32_t sc8 = ptx::f32x2_to_e4m3x2(__uint_as_float(mt) * 0.25f, 0.f) & 0xFFu;  // E4M3 (positive), round to nearest
+    const float scf = __half2float(__ushort_as_half(uint16_t(ptx::e4m3x2_to_f16x2(uint16_t(sc8)) & 0xFFFFu)));
+    const float inv = scf > 0.f ? 1.f / scf : 0.f;
+    uint32_t cw[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = r[8 * w + i] * inv;
+      uint32_t h[4];
+      cw[w] = ptx::f32x8_to_e2m1x8(y, h);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+        r[8 * w + 2 * i] = fmaf(-d.x, scf, r[8 * w + 2 * i]);
+        r[8 * w + 2 * i + 1] = fmaf(-d.y, scf, r[8 * w + 2 * i + 1]);
+      }
+    }
+    uint8_t* dst = s.q4[t >> 1][panel] + (16 * (t & 1) + n) * 128;  // (the swizzle term of row 16 + n is that of row n)
+    *reinterpret_cast<uint4*>(dst + (((c0) ^ uint32_t(n & 7)) << 4)) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ uint32_t(n & 7)) << 4)) = make_uint4(cw[4], cw[5], cw[6], cw[7]);
+    if (sub == 0) s.sfb[t][n] = sc8 * 0x01010101u;
   }
   {
     uint32_t h[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) h[j] = ptx::f32x2_to_f16x2(pe[2 * j] * up, pe[2 * j + 1] * up);
-    *reinterpret_cast<uint4*>(s.q[8] + n * 128 + swz) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(s.qrope + n * 128 + (uint32_t(sub ^ (n & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
   }
-  if (sub == 0) s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * __uint_as_float(uint32_t(e - 14 + 127) << 23);
+  if (sub == 0) s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * __uint_as_float(uint32_t(e - 6 + 127) << 23);
   ptx::fence_proxy_async_smem();
+  ptx::bar_sync(2, 128);
+  // scale factors of B: pass p multiplies K with B rows [terms 2p | 2p + 1] x 16 heads; the scale word of row i goes to
+  // lane i of every lane quadrant, column 4 p
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = 0u;
+#pragma unroll
+  for (int pp = 0; pp < kVtPasses; ++pp) w[4 * pp] = s.sfb[2 * pp + (lane >> 4)][lane & 15];
+  ptx::tmem_st8(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, w);
+  ptx::tmem_wait_st();
 }
 
 // One tile of a K thread. Returns false if a wait gave up.
 __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it, int lane, int quad) {
   const int r = quad * 32 + lane;
-  const int half = quad >> 1, rr = r & 63;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
-  const uint32_t hidx = 2 * it + half;
-  const int slot = hidx % kVtRawSlots;
+  const int slot = it % kVtRawSlots;
   const uint8_t* raw = s.raw[slot];
-  const uint32_t kpar = it & 1;        // phase of the per-tile barriers completed by tile `it`
-  const uint32_t buf = it & 1;         // scale table of this tile
-  if (!__all_sync(~0u, ptx::mbar_wait(&s.raw_full[slot], (hidx / kVtRawSlots) & 1, &s.abort_flag))) return false;
+  const uint32_t buf = it & 1;
+  if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return false;
   const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
+  if (quad == 0) VT_EV(2, it);
 
-  // ---- block scales: 32 E4M3 bytes -> 32 FP16 pairs (s, s); 0 for rows beyond the end of the request
-  uint32_t sc[32];
+  // ---- block scales of this token for the V warps: each E4M3 byte doubled (the conversion of the pair gives (s, s)); 0
+  // beyond the request's end
   {
-    const uint32_t x = (rr >> 2) & P.sf_swz_mask;
-    const uint4 a = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((0u ^ x) << 4));
-    const uint4 b = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((1u ^ x) << 4));
+    const uint32_t x = (uint32_t(r) >> 2) & P.sf_swz_mask;
+    const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((0u ^ x) << 4));
+    const uint4 b = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t qi = 4 * it + quad, qs = qi % kVtScRing;  // this warp's quarter of the tile has a table of its own in the ring
+    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((qi / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
+    // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
+    uint16_t* dst = &s.sc[qs][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(w[j] & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(w[j] >> 16));
-      sc[4 * j] = __byte_perm(s01, s01, 0x1010), sc[4 * j + 1] = __byte_perm(s01, s01, 0x3232);
-      sc[4 * j + 2] = __byte_perm(s23, s23, 0x1010), sc[4 * j + 3] = __byte_perm(s23, s23, 0x3232);
+      const uint32_t wj = valid ? w[j] : 0u;
+      const uint32_t lo = __byte_perm(wj, 0, 0x1100), hi = __byte_perm(wj, 0, 0x3322);  // (b0, b0, b1, b1), (b2, b2, b3, b3)
+      dst[(4 * j + 0) * 32] = uint16_t(lo & 0xFFFF), dst[(4 * j + 1) * 32] = uint16_t(lo >> 16);
+      dst[(4 * j + 2) * 32] = uint16_t(hi & 0xFFFF), dst[(4 * j + 3) * 32] = uint16_t(hi >> 16);
     }
-    if (!valid) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) sc[j] = 0u;
-    }
-  }
-  auto publish = [&](int chunk) {
-    ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[chunk]);
-  };
-  // QK^T of the previous tile must have finished with the chunk's columns
-  auto acquire = [&](int chunk) -> bool {
-    const bool ok = ptx::mbar_wait(&s.k_free[chunk], kpar ^ 1, &s.abort_flag);
-    ptx::tc_fence_after_sync();
-    return __all_sync(~0u, ok);
-  };
-
-  // ---- rope chunk: 64 E4M3 bytes -> 32 columns
+    if (lane == 0) ptx::mbar_arrive(&s.sc_full[qs]);
+  }
+  // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs
+  uint32_t h[32];
   {
-    const uint32_t x = (rr >> 1) & P.kpe_swz_mask;
-    uint32_t h[32];
+    const uint32_t x = (uint32_t(r) >> 1) & P.kpe_swz_mask;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const uint4 v = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(c) ^ x) << 4));
+      const uint4 v = *reinterpret_cast<const uint4*>(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -178,46 +374,31 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
         h[8 * c + 2 * j + 1] = ptx::e4m3x2_to_f16x2(uint16_t(w[j] >> 16));
       }
     }
-    if (!acquire(0)) return false;
-    ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
   }
-  // ---- latent panels: 64 channels = 32 packed bytes -> 32 columns each. The publish of a chunk is deferred until the
-  // next panel's values have been computed, so the latency of the tensor-memory store hides behind arithmetic.
+  // ---- scale factors of A: lane l of this quadrant holds, for K step a, columns 4a + j = the scale word a of token 32 j + l
+  uint32_t f[32];
 #pragma unroll
-  for (int p = 0; p < 8; ++p) {
-    const uint8_t* base = raw + (p >> 2) * kRawCkvHi + rr * 128;
-    const uint32_t c0 = uint32_t(2 * (p & 3)), x = uint32_t(rr & 7);
-    const uint4 n0 = *reinterpret_cast<const uint4*>(base + ((c0 ^ x) << 4));
-    const uint4 n1 = *reinterpret_cast<const uint4*>(base + (((c0 + 1) ^ x) << 4));
-    if (p == 7) {  // last read of the raw slot by this thread
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
-    }
-    const uint32_t wds[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
-    uint32_t h[32];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {  // word j = channels [8j, 8j + 8) of the panel, scale block 4p + j / 2
-      uint32_t e[4];
-      ptx::e2m1x8_to_f16x8(wds[j], e);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h[4 * j + i] = ptx::hmul2(e[i], sc[4 * p + (j >> 1)]);
-    }
-    if ((p & 1) == 0 && !acquire(1 + (p >> 1))) return false;
-    ptx::tmem_wait_st();
-    if (p == 0) publish(0);
-    else if ((p & 1) == 0) publish(p >> 1);
-    ptx::tmem_st32(tm_lane + VtCols::K + 32 * p, h);
-    if (p == 1) {
-      // park the scales for the V warps, once they have finished with the tile that used this table before
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.sc_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag))) return false;
-#pragma unroll
-      for (int b = 0; b < 32; ++b) s.sc[buf][b][r] = sc[b];
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.sc_full[buf]);
-    }
+  for (int j = 0; j < 4; ++j) {
+    const int tk = 32 * j + lane;
+    const uint32_t x = (uint32_t(tk) >> 2) & P.sf_swz_mask;
+    const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
+    const uint4 b = *reinterpret_cast<const uint4*>(raw + kVtRawSf + tk * 32 + ((1u ^ x) << 4));
+    f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
   }
-  ptx::tmem_wait_st();
-  publish(4);
+  // QK^T of tile it - 2 must have finished with this scale-factor buffer, the rope MMAs of tile it - 1 with rope K
+  bool ok = VT_WAIT(1, ptx::mbar_wait(&s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag));
+  ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.rope_free, (it & 1) ^ 1, &s.abort_flag));
+  ptx::tc_fence_after_sync();
+  if (!__all_sync(~0u, ok)) return false;
+  ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
+  ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);  // every byte this warp read from the raw tile is in a register or stored
+  VT_WAIT(3, (ptx::tmem_wait_st(), true));
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(&s.k_full[buf]);
+  if (quad == 0) VT_EV(3, it);
   return true;
 }
 
@@ -231,10 +412,25 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
-    // the previous tile's QK^T must be done reading Q^T before the new query overwrites it
-    const bool ok = !dead && ptx::mbar_wait(&s.k_free[4], (it & 1) ^ 1, &s.abort_flag);
+    // the previous tile's QK^T must be done reading the query before the new one overwrites it
+    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag));
     if (ptx::bar_red_or(2, 128, !ok)) return;
-    vt_load_query(s, P, seg, quad * 32 + lane, seg_count & 3);
+    ptx::tc_fence_after_sync();
+    vt_load_query(s, P, seg, quad * 32 + lane, seg_count & 3, lane, quad);
+#if defined(MLA_VT_PROF) && (VT_DBG & 8)
+    if (vt_prof_ptr && seg.b == 0 && seg.hg == 0 && seg.tok0 == 0) {  // dump the query terms, their scales and the score scales
+      ptx::bar_sync(2, 128);
+      uint32_t* out = reinterpret_cast<uint32_t*>(vt_prof_ptr) + 1024;
+      const int kt = quad * 32 + lane;
+      for (int i = kt; i < kVtTerms * 2 * 16 * 128 / 4; i += 128) out[i] = reinterpret_cast<const uint32_t*>(s.q4)[i];
+      for (int i = kt; i < kVtTerms * 16; i += 128) out[4096 + i] = (&s.sfb[0][0])[i];
+      for (int i = kt; i < 16; i += 128) out[4096 + 64 + i] = __float_as_uint(s.qa[seg_count & 3][i]);
+      uint32_t sf[16];
+      ptx::tmem_ld16(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, sf);
+      ptx::tmem_wait_ld();
+      for (int i = 0; i < 16; ++i) out[4096 + 128 + kt * 16 + i] = sf[i];
+    }
+#endif
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       if (!vt_k_step(s, P, seg, t, it, lane, quad)) {
@@ -248,70 +444,121 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
 // ---------------------------------------------------------------------------------------------------------------
 // role: V^T conversion (4 warps; warp % 4 = lane quadrant = channel pairs [32 quad, +32) of each 128-pair block)
 // ---------------------------------------------------------------------------------------------------------------
+// A unit of work is one transposing ldmatrix: 32 tokens x 16 channel pairs (two scale blocks), i.e. half of this
+// warp's share of a V^T slot. A 32-token group is four units (2 blocks x 2 halves), a tile four groups. The scales come
+// from the table as E4M3 byte pairs (b, b), which the conversion instruction turns into the FP16 pair (s, s) it is
+// multiplied with. The loop over groups is software pipelined: the loads of a unit are issued before the arithmetic of
+// the unit before it, and a finished slot is published only after the arithmetic of the following unit, when its
+// tensor-memory stores have landed.
+struct VtUnitRegs {
+  uint32_t rw[4];
+  uint4 sa, sb;  // scale byte pairs of the unit's two blocks: 8 tokens each (4q .. 4q + 3 of both 16-token halves)
+};
 __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const int lane = ptx::lane_id();
   const int quad = (threadIdx.x >> 5) & 3;
   const int q = lane & 3;
   const int mrow = lane & 15, mat = lane >> 4;  // this lane addresses row `mrow` of ldmatrix matrix `mat`
-  const uint32_t tm = s.tmem_base;
-  for (int si = 0; si < n_segs; ++si) {
-    const int ntiles = s.segs[si].ntiles;
-    for (int t = 0; t < ntiles; ++t, ++it) {
-      const uint32_t buf = it & 1;
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.sc_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
-#pragma unroll 1
-      for (int qt = 0; qt < 4; ++qt) {   // 32-token group of the tile
-        const uint32_t hidx = 2 * it + (qt >> 1);
-        const int slot = hidx % kVtRawSlots;
-        if (!__all_sync(~0u, ptx::mbar_wait(&s.raw_full[slot], (hidx / kVtRawSlots) & 1, &s.abort_flag))) return;
-        const int rr = 32 * (qt & 1) + 16 * mat + mrow;  // token row inside the 64-token raw slot
-        const uint32_t row_addr = ptx::smem_u32(s.raw[slot]) + rr * 128;
-#pragma unroll
-        for (int mb = 0; mb < 2; ++mb) {  // block of 128 channel pairs = 128-byte half of the packed row
-          const uint32_t vs = 8 * it + 2 * qt + mb, ring = vs % kVtRing;
-          const bool ok = ptx::mbar_wait(&s.vt_free[ring], ((vs / kVtRing) & 1) ^ 1, &s.abort_flag);
-          ptx::tc_fence_after_sync();
-          if (!__all_sync(~0u, ok)) return;
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {  // 16 channel pairs = two scale blocks
-            const uint32_t chunk = 2 * quad + ch;
-            uint32_t rw[4];
-            ptx::ldmatrix_x2_trans_b8(row_addr + mb * kRawCkvHi + ((chunk ^ uint32_t(rr & 7)) << 4), rw);
-            const uint32_t b0 = 16 * mb + 2 * chunk;
-            const uint4 sa0 = *reinterpret_cast<const uint4*>(&s.sc[buf][b0][32 * qt + 4 * q]);
-            const uint4 sb0 = *reinterpret_cast<const uint4*>(&s.sc[buf][b0 + 1][32 * qt + 4 * q]);
-            const uint4 sa1 = *reinterpret_cast<const uint4*>(&s.sc[buf][b0][32 * qt + 16 + 4 * q]);
-            const uint4 sb1 = *reinterpret_cast<const uint4*>(&s.sc[buf][b0 + 1][32 * qt + 16 + 4 * q]);
-            const uint32_t sa[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
-            const uint32_t sb[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
-            uint32_t v[16];
-#pragma unroll
-            for (int tg = 0; tg < 2; ++tg) {
-              uint32_t ea[4], eb[4];
-              ptx::e2m1x8_to_f16x8(rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
-              ptx::e2m1x8_to_f16x8(rw[2 * tg + 1], eb);  // channel pair g + 8
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa[4 * tg + i]);
-                v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb[4 * tg + i]);
-              }
-            }
-            ptx::tmem_st_16x128b_x8(tm + (uint32_t(32 * quad + 16 * ch) << 16) + VtCols::vt(ring), v);
-          }
-          ptx::tmem_wait_st();
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&s.vt_full[ring]);
-        }
-        if (qt & 1) {  // both 32-token groups of the raw slot have been read
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
-        }
-      }
+  const uint32_t tm_q = s.tmem_base + (uint32_t(32 * quad) << 16);
+  int total = 0;
+  for (int si = 0; si < n_segs; ++si) total += s.segs[si].ntiles > 0 ? s.segs[si].ntiles : 0;
+  if (total == 0) return;
+  const uint32_t n_groups = 4u * uint32_t(total);
+  // per-lane constants: byte offset of this lane's ldmatrix row inside a 32-token group, swizzle term
+  const uint32_t row_off = uint32_t(16 * mat + mrow) * 128, swz = uint32_t(mrow & 7);
+  bool ok_all = true;
+  uint32_t raw_base = 0, sc_base = 0;  // of the group whose loads are being issued
+  // group g of this batch: tile it + g / 4, token group g % 4. Waits for its scale table and raw bytes.
+  auto open_group = [&](uint32_t g) {
+    const uint32_t tile = it + (g >> 2), qt = g & 3;
+    const uint32_t slot = tile % kVtRawSlots, qi = 4 * tile + qt, qs = qi % kVtScRing;
+    bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[qs], (qi / kVtScRing) & 1, &s.abort_flag));
+    ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
+    ok_all = ok_all && ok;
+    raw_base = ptx::smem_u32(s.raw[slot]) + qt * 32 * 128 + row_off;
+    sc_base = ptx::smem_u32(&s.sc[qs][0][0]) + 16 * q;
+    if (quad == 0 && qt == 0) VT_EV(11, tile);
+  };
+  // unit (mb, ch) of the open group: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
+  auto load_unit = [&](int mb, int ch, VtUnitRegs& R) {
+    const uint32_t chunk = 2 * quad + ch;
+    ptx::ldmatrix_x2_trans_b8(raw_base + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
+    const uint32_t a = sc_base + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sa.x), "=r"(R.sa.y), "=r"(R.sa.z), "=r"(R.sa.w) : "r"(a));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sb.x), "=r"(R.sb.y), "=r"(R.sb.z), "=r"(R.sb.w) : "r"(a + 64));
+  };
+  uint32_t pending = ~0u;  // V^T ring slot stored but not yet published
+  auto publish_pending = [&]() {
+    if (pending != ~0u) {
+      VT_WAIT(3, (ptx::tmem_wait_st(), true));
+      ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.sc_free[buf]);
+      if (lane == 0) ptx::mbar_arrive(&s.vt_full[pending]);
     }
+  };
+  // arithmetic and store of unit (mb, ch) of group g, whose loads are in R; false if a wait gave up
+  auto finish_unit = [&](uint32_t g, int mb, int ch, const VtUnitRegs& R) -> bool {
+    // word k of sa / sb: the byte pairs of tokens 16 (k / 2) + 4 q + 2 (k % 2) + {0, 1}
+    const uint32_t pa[4] = {R.sa.x, R.sa.y, R.sa.z, R.sa.w}, pb[4] = {R.sb.x, R.sb.y, R.sb.z, R.sb.w};
+    uint32_t v[16];
+#pragma unroll
+    for (int tg = 0; tg < 2; ++tg) {
+      uint32_t ea[4], eb[4];
+      ptx::e2m1x8_to_f16x8(R.rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
+      ptx::e2m1x8_to_f16x8(R.rw[2 * tg + 1], eb);  // channel pair g + 8
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t wa = pa[2 * tg + (i >> 1)], wb = pb[2 * tg + (i >> 1)];
+        const uint32_t sa2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wa >> 16 : wa & 0xFFFF));  // (s, s) of token i, first block
+        const uint32_t sb2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wb >> 16 : wb & 0xFFFF));
+        v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa2);
+        v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb2);
+      }
+    }
+    const uint32_t tile = it + (g >> 2), qt = g & 3, sl = 2 * qt + mb;
+    if (ch == 0) {
+      // a new slot begins: publish the previous one, then make sure PV has released this ring slot's previous tile
+      publish_pending();
+      const bool ok = VT_WAIT(2, ptx::mbar_wait(&s.vt_free[sl], (tile & 1) ^ 1, &s.abort_flag));
+      ptx::tc_fence_after_sync();
+      if (!__all_sync(~0u, ok)) return false;
+      pending = sl;
+      if (quad == 0 && sl == 0) VT_EV(12, tile);
+      if (quad == 0 && sl == 7) VT_EV(13, tile);
+    }
+    ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(sl), v);
+    return true;
+  };
+  // the inputs of group g have been read (their values are in registers or stored): release them
+  auto close_group = [&](uint32_t g) {
+    const uint32_t tile = it + (g >> 2), qt = g & 3;
+    __syncwarp();
+    if (lane == 0) {
+      ptx::mbar_arrive(&s.sc_free[(4 * tile + qt) % kVtScRing]);
+      if (qt == 3) ptx::mbar_arrive(&s.raw_empty[tile % kVtRawSlots]);
+    }
+    if (quad == 0 && qt == 3) VT_EV(14, tile);
+  };
+  VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
+  open_group(0);
+  load_unit(0, 0, ra);
+#pragma unroll 1
+  for (uint32_t g = 0; g < n_groups; ++g) {
+    load_unit(0, 1, rb);
+    if (!__all_sync(~0u, ok_all) || !finish_unit(g, 0, 0, ra)) return;
+    load_unit(1, 0, ra);
+    if (!finish_unit(g, 0, 1, rb)) return;
+    load_unit(1, 1, rb);
+    if (!finish_unit(g, 1, 0, ra)) return;
+    if (g + 1 < n_groups) {
+      open_group(g + 1);
+      load_unit(0, 0, ra);
+    }
+    if (!finish_unit(g, 1, 1, rb)) return;
+    close_group(g);
   }
+  publish_pending();
+  it += uint32_t(total);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -320,35 +567,47 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
 __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const bool leader = ptx::elect_one();
   const uint32_t tm = s.tmem_base;
-  const uint32_t idesc = ptx::instr_desc(128, 16, ptx::FMT_F16, ptx::FMT_F16, false, false);
-  const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q[0]), 16, 1024);
+  const uint32_t idesc16 = ptx::instr_desc(128, 16, ptx::FMT_F16, ptx::FMT_F16, false, false);
+  const uint32_t idesc4 = ptx::instr_desc_mxf4nvf4(128, 32);
+  const uint64_t qrope_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.qrope), 16, 1024);
+  const uint64_t q4_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q4[0][0]), 16, 1024);
   for (int si = 0; si < n_segs; ++si) {
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
-      const uint32_t buf = it & 1;
+      const uint32_t buf = it & 1, slot = it % kVtRawSlots;
       // softmax of tile it - 2 must have read this S^T buffer
-      if (!__all_sync(~0u, it < 2 || ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag))) return;
-#pragma unroll 1
-      for (int c = 0; c < 5; ++c) {
-        if (!__all_sync(~0u, ptx::mbar_wait(&s.k_full[c], it & 1, &s.abort_flag))) return;
-        ptx::tc_fence_after_sync();
-        if (leader) {
-          if (c == 0) {
+      if (!__all_sync(~0u, it < 2 || VT_WAIT(0, ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
+      // the packed bytes (this thread's MMAs read them through the async proxy) and the K side in tensor memory
+      if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return;
+      if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.k_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      ptx::tc_fence_after_sync();
+      VT_EV(4, it);
+      if (leader) {
+        const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.raw[slot]), 16, 1024);
+        // K step a = channels [64 a, +64): panel a / 4, 32 bytes per step. B of pass pp = rows [term 2 pp | term 2 pp + 1].
+        auto fp4 = [&](int pp, int a, uint32_t accum) {
+          const uint32_t off = uint32_t(a >> 2) * kVtRawHi + uint32_t(a & 3) * 32;
+          const uint32_t qoff = uint32_t(pp * 2 + (a >> 2)) * (32 * 128) + uint32_t(a & 3) * 32;
+          ptx::mma_mxf4nvf4_ss(tm + VtCols::s(buf), k_desc + (off >> 4), q4_desc + (qoff >> 4), idesc4, tm + VtCols::sfa(buf) + 4 * a,
+                               tm + VtCols::SFB + 4 * pp, accum);
+        };
+        fp4(0, 0, 0);  // the first MMA of the tile overwrites all 32 columns of the accumulator
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::KROPE + 8 * ks, q_desc + ((8 * 16 * 128 + ks * 32) >> 4), idesc, ks > 0);
-          } else {
-#pragma unroll 1
-            for (int p = 2 * (c - 1); p < 2 * c; ++p) {
+        for (int ks = 0; ks < 4; ++ks)  // rope: 64 channels as FP16 from tensor memory, into the columns of the even terms
+          ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::KROPE + 8 * ks, qrope_desc + ((ks * 32) >> 4), idesc16, 1);
+        ptx::mma_commit(&s.rope_free);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::K + 32 * p + 8 * ks, q_desc + ((p * 16 * 128 + ks * 32) >> 4), idesc, 1);
-            }
-          }
-          ptx::mma_commit(&s.k_free[c]);
-          if (c == 4) ptx::mma_commit(&s.s_full[buf]);
+        for (int a = 1; a < 8; ++a) fp4(0, a, 1);
+#pragma unroll 1
+        for (int pp = 1; pp < kVtPasses; ++pp) {
+#pragma unroll
+          for (int a = 0; a < 8; ++a) fp4(pp, a, 1);
         }
+        ptx::mma_commit(&s.k_free[buf]);
+        ptx::mma_commit(&s.s_full[buf]);
+        ptx::mma_commit(&s.raw_empty[slot]);
       }
+      VT_EV(5, it);
     }
   }
 }
@@ -361,11 +620,12 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
+      if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      VT_EV(8, it);
 #pragma unroll 1
       for (int sl = 0; sl < 8; ++sl) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
-        const uint32_t vs = 8 * it + sl, ring = vs % kVtRing;
-        if (!__all_sync(~0u, ptx::mbar_wait(&s.vt_full[ring], (vs / kVtRing) & 1, &s.abort_flag))) return;
+        const uint32_t ring = sl;  // the ring holds exactly one tile
+        if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[ring], it & 1, &s.abort_flag)))) return;
         ptx::tc_fence_after_sync();
         if (leader) {
           const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
@@ -376,10 +636,13 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
           ptx::mma_commit(&s.vt_free[ring]);
           if (sl == 7) ptx::mma_commit(&s.p_free[buf]);
         }
+        if (sl == 0) VT_EV(9, it);
+        if (sl == 7) VT_EV(10, it);
       }
     }
   }
 }
+
 
 // ---------------------------------------------------------------------------------------------------------------
 // role: softmax + epilogue (4 warps; thread r = token row of S^T and channel-pair row of O^T)
@@ -407,8 +670,9 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      const bool ok = ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag);
+      const bool ok = VT_WAIT(0, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
       ptx::tc_fence_after_sync();
+      if (warp == 0) VT_EV(6, it);
       float x[N];
       if (!scales_loaded) {  // written by the K warps before the segment's first K chunk was published
 #pragma unroll
@@ -417,11 +681,11 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       }
       if (ok) {
         const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
-        uint32_t sv[16];
-        ptx::tmem_ld16(tm_lane + VtCols::s(buf), sv);
+        uint32_t sv[32];  // columns [0, 16): even terms + rope, [16, 32): odd terms
+        ptx::tmem_ld32(tm_lane + VtCols::s(buf), sv);
         ptx::tmem_wait_ld();
 #pragma unroll
-        for (int h = 0; h < N; ++h) x[h] = valid ? __uint_as_float(sv[h]) * qa_r[h] : -INFINITY;
+        for (int h = 0; h < N; ++h) x[h] = valid ? (__uint_as_float(sv[h]) + __uint_as_float(sv[16 + h])) * qa_r[h] : -INFINITY;
       } else {
 #pragma unroll
         for (int h = 0; h < N; ++h) x[h] = -INFINITY;
@@ -432,7 +696,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       bool need = !ok;
 #pragma unroll
       for (int h = 0; h < N; ++h) need |= x[h] > m[h] + kGrow;
-      if (ptx::bar_red_or(1, 128, need)) {
+      if (VT_WAIT(2, ptx::bar_red_or(1, 128, need))) {
         if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
 #pragma unroll
         for (int h = 0; h < N; ++h) {
@@ -473,7 +737,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       }
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
-      if (it >= 2) ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
+      if (it >= 2) VT_WAIT(1, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
       uint8_t* const p_base = s.p[buf][r >> 5] + p_off;
 #pragma unroll
       for (int h = 0; h < N; ++h) {
@@ -487,6 +751,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
+      if (warp == 0) VT_EV(7, it);
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
@@ -541,13 +806,18 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
 // The CTA's segments are staged through shared memory in batches; every thread takes part in the two CTA-wide
 // barriers around a batch, whatever its role.
 // ---------------------------------------------------------------------------------------------------------------
+
+// ---------------------------------------------------------------------------------------------------------------
+// The CTA's segments are staged through shared memory in batches; every thread takes part in the two CTA-wide
+// barriers around a batch, whatever its role.
+// ---------------------------------------------------------------------------------------------------------------
 enum VtRole { kVtSoftmax, kVtK, kVtV, kVtQk, kVtProducer, kVtPv, kVtIdle };
 
 template <int ROLE>
 __device__ __forceinline__ void vt_run_role(VtSmem& s, const DecodeParams& P, const CUtensorMap* ckv_map, const CUtensorMap* sf_map,
                                             const CUtensorMap* kpe_map) {
   const int2 range = P.cta_range[blockIdx.x];
-  uint32_t it = 0, seg_count = 0, hcount = 0;  // every role advances its own copies identically
+  uint32_t it = 0, seg_count = 0;  // every role advances its own copies identically
   for (int w0 = range.x; w0 < range.y; w0 += kSegBatch) {
     const int n_segs = range.y - w0 < kSegBatch ? range.y - w0 : kSegBatch;
     if (ROLE == kVtSoftmax && int(threadIdx.x) < n_segs) {
@@ -560,14 +830,14 @@ __device__ __forceinline__ void vt_run_role(VtSmem& s, const DecodeParams& P, co
     if (ROLE == kVtK) vt_k_role(s, P, n_segs, it, seg_count);
     if (ROLE == kVtV) vt_v_role(s, P, n_segs, it);
     if (ROLE == kVtQk) vt_qk_role(s, P, n_segs, it);
-    if (ROLE == kVtProducer) producer_role<kVtRawSlots>(s, P, ckv_map, sf_map, kpe_map, n_segs, hcount);
+    if (ROLE == kVtProducer) vt_producer_role(s, P, ckv_map, sf_map, kpe_map, n_segs, it);
     if (ROLE == kVtPv) vt_pv_role(s, P, n_segs, it);
     __syncthreads();
     if (s.abort_flag) break;
   }
 }
 
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+__global__ void __launch_bounds__(kVtThreads, 1)
 mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_constant__ CUtensorMap sf_map,
                      const __grid_constant__ CUtensorMap kpe_map, const DecodeParams P) {
   extern __shared__ uint8_t smem_raw[];
@@ -575,13 +845,14 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   const int warp = threadIdx.x >> 5;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kVtRawSlots; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 6);  // 2 K + 4 V warps
-    for (int i = 0; i < 5; ++i) ptx::mbar_init(&s.k_full[i], 4), ptx::mbar_init(&s.k_free[i], 1);
+    for (int i = 0; i < kVtRawSlots; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 9);  // 4 K + 4 V warps + QK^T
     for (int i = 0; i < kVtRing; ++i) ptx::mbar_init(&s.vt_full[i], 4), ptx::mbar_init(&s.vt_free[i], 1);
+    for (int i = 0; i < kVtScRing; ++i) ptx::mbar_init(&s.sc_full[i], 1), ptx::mbar_init(&s.sc_free[i], 4);
+    ptx::mbar_init(&s.rope_free, 1);
     for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&s.k_full[i], 4), ptx::mbar_init(&s.k_free[i], 1);
       ptx::mbar_init(&s.s_full[i], 1), ptx::mbar_init(&s.s_free[i], 4);
       ptx::mbar_init(&s.p_full[i], 4), ptx::mbar_init(&s.p_free[i], 1);
-      ptx::mbar_init(&s.sc_full[i], 4), ptx::mbar_init(&s.sc_free[i], 4);
     }
     s.abort_flag = 0;
     ptx::fence_mbar_init();
@@ -597,6 +868,11 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
   ptx::grid_launch_dependents();
 
+#ifdef MLA_VT_PROF
+  if (threadIdx.x < 160) reinterpret_cast<long long*>(s.prof)[threadIdx.x] = 0;
+  __syncthreads();
+  const long long prof_t0 = clock64();
+#endif
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 16 warps x 128.
   constexpr int kSoftmaxRegs = 168, kKRegs = 152, kVRegs = 128;
   static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 4 * kVRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
@@ -616,8 +892,14 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
     else vt_run_role<kVtIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
   }
 
+#ifdef MLA_VT_PROF
+  if ((threadIdx.x & 31) == 0) s.prof[warp][7] = clock64() - prof_t0;
+#endif
   ptx::tc_fence_before_sync();
   __syncthreads();
+#ifdef MLA_VT_PROF
+  if (blockIdx.x == 1 && threadIdx.x < 160 && vt_prof_ptr) vt_prof_ptr[threadIdx.x] = reinterpret_cast<long long*>(s.prof)[threadIdx.x];
+#endif
   if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }

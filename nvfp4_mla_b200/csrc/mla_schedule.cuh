@@ -11,19 +11,6 @@
 
 namespace mla {
 
-#ifdef MLA_TRACE
-__device__ long long* d_trace_ptr;  // timeline tracing: slots 48.. of row 31 hold global-timer stamps of the helper kernels
-__device__ __forceinline__ void trace_stamp(int slot, bool max_of_all) {
-  if (!d_trace_ptr) return;
-  long long gt;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-  if (max_of_all) atomicMax(reinterpret_cast<unsigned long long*>(d_trace_ptr + 31 * 64 + slot), (unsigned long long)gt);
-  else d_trace_ptr[31 * 64 + slot] = gt;
-}
-#define MLA_STAMP(slot, all) trace_stamp(slot, all)
-#else
-#define MLA_STAMP(slot, all) do {} while (0)
-#endif
 constexpr int kSchedThreads = 1024;
 constexpr int kSchedMaxBZ = 8192;  // batch * splits the single-block scan holds in shared memory
 
@@ -34,7 +21,6 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
   __shared__ int total_bz;
   ptx::grid_launch_dependents();  // the decode kernel may start its prologue; it waits for this grid before reading
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) MLA_STAMP(48, false);
   const int BZ = pb.batch * pb.splits;
   if (BZ > kSchedMaxBZ) {
     if (tid == 0) header[0] = kBadSchedule;
@@ -141,7 +127,6 @@ mla_schedule_kernel(const int* __restrict__ kv_lens, Problem pb, int* header, in
     }
   }
   __syncthreads();
-  if (tid == 0) MLA_STAMP(49, false);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -246,7 +231,6 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
   __shared__ int n_parts_s;
   __shared__ float weights[kCombineMaxParts];
   __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
-  if (blockIdx.x == 0 && threadIdx.x == 0) MLA_STAMP(50, false);
   // Launched as a programmatic dependent of the decode kernel, which lets its dependents start only after it has seen
   // the schedule kernel complete: the schedule's output (item_range) may be read at once, the partials only after the wait.
   const long long row = blockIdx.x;
@@ -280,11 +264,9 @@ mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const 
   __syncthreads();
   const int n_parts = n_parts_s;
   ptx::grid_dependency_wait();
-  if (blockIdx.x == 0 && threadIdx.x == 0) MLA_STAMP(51, false);
   merge_row<GROUPS>(
       n_parts, [&](int i) { return lse_part[(long long)slots[i] * N + n]; },
       [&](int i) { return o_part + ((long long)slots[i] * N + n) * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
-  if (threadIdx.x == 0) MLA_STAMP(52, true);
 }
 
 // Dense partials: part i holds o rows at o_part + i * o_stride (floats) and lse values at lse_part + i * lse_stride. The

@@ -300,6 +300,23 @@ __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accum)
       : "memory");
 }
+// Instruction descriptor of kind::mxf4nvf4 (packed E2M1 operands, both K-major, one UE4M3 scale per 16 elements along K,
+// fp32 accumulator): formats at bits 7 and 10 (E2M1 = 1), N / 8 at bit 17, scale format at bit 23 (UE4M3 = 0), M / 16 at
+// bit 24; the scale-factor ids (bits 4-5 and 29-30) stay 0 because a K = 64 step uses all four bytes of a scale word.
+__host__ __device__ constexpr uint32_t instr_desc_mxf4nvf4(uint32_t m, uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// D[tmem] (+)= (A[smem] x SFA[tmem]) * (B[smem] x SFB[tmem]), K = 64 packed E2M1 per operand row. Scale factors: the
+// word (4 UE4M3 bytes = the 4 blocks of this K step) of operand row r lives in lane r % 32 of EVERY lane quadrant,
+// column sf + r / 32; `sfa` / `sfb` must be multiples of four columns (an unaligned address faults).
+__device__ __forceinline__ void mma_mxf4nvf4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                                uint32_t sfb_tmem, uint32_t accum) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accum), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
 // mbarrier arrives once every tcgen05 operation this thread issued so far has completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -316,6 +333,20 @@ __device__ __forceinline__ void e2m1x8_to_f16x8(uint32_t w, uint32_t (&h)[4]) {
       "cvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}"
       : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
       : "r"(w));
+}
+// eight floats -> eight E2M1 codes (round to nearest even, saturating at 6), element 0 in the lowest nibble, and what
+// the codes decode to as four f16x2 (element pairs in order): one block, so the bytes never leave their registers
+__device__ __forceinline__ uint32_t f32x8_to_e2m1x8(const float (&v)[8], uint32_t (&h)[4]) {
+  uint32_t d;
+  asm("{\n.reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %6, %5;\ncvt.rn.satfinite.e2m1x2.f32 b1, %8, %7;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %10, %9;\ncvt.rn.satfinite.e2m1x2.f32 b3, %12, %11;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b0;\ncvt.rn.f16x2.e2m1x2 %2, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b2;\ncvt.rn.f16x2.e2m1x2 %4, b3;\n}"
+      : "=&r"(d), "=&r"(h[0]), "=&r"(h[1]), "=&r"(h[2]), "=&r"(h[3])
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return d;
 }
 // two E4M3 bytes -> f16x2 (exact)
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t x) {
