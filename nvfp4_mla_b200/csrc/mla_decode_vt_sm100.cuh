@@ -48,6 +48,9 @@ namespace mla {
 #ifndef VT_DBG
 #define VT_DBG 0
 #endif
+#ifndef VT_EXP
+#define VT_EXP 0
+#endif
 constexpr int kVtRawSlots = 3;   // raw tiles in flight
 constexpr int kVtRing = 8;       // V^T slots (32 tokens x 128 channel pairs, 32 columns): one tile
 constexpr int kVtScRing = 12;    // quarter-tile scale tables (2 KB each)
@@ -72,8 +75,12 @@ __device__ long long* vt_prof_ptr;
     if ((threadIdx.x & 31) == 0) s.prof[threadIdx.x >> 5][slot] += clock64() - t0_;                \
     return r_;                                                                                     \
   }())
+#define VT_T(var) const long long var = clock64()
+#define VT_ACC(slot, a, b) do { if ((threadIdx.x & 31) == 0) s.prof[threadIdx.x >> 5][slot] += (b) - (a); } while (0)
 #else
 #define VT_WAIT(slot, expr) (expr)
+#define VT_T(var) do {} while (0)
+#define VT_ACC(slot, a, b) do {} while (0)
 #endif
 #ifdef MLA_VT_TRACE  // development builds: clock stamps of pipeline events of CTA 1's tiles 8..71
 __device__ long long* vt_trace_ptr;
@@ -82,8 +89,15 @@ __device__ long long* vt_trace_ptr;
     if (vt_trace_ptr && blockIdx.x == 1 && (threadIdx.x & 31) == 0 && (tile) >= 8u && (tile) < 72u)                  \
       vt_trace_ptr[(ev) * 64 + ((tile) - 8u)] = clock64();                                                           \
   } while (0)
+// fine-grained: point p of unit u of tile 40, V warp of quadrant 0
+#define VT_EVU(p, tile, u)                                                                                          \
+  do {                                                                                                               \
+    if (vt_trace_ptr && blockIdx.x == 1 && threadIdx.x == 256 && (tile) == 40u)                                      \
+      vt_trace_ptr[24 * 64 + (u) * 8 + (p)] = clock64();                                                             \
+  } while (0)
 #else
 #define VT_EV(ev, tile) do {} while (0)
+#define VT_EVU(p, tile, u) do {} while (0)
 #endif
 #define VT_EVG(ev, g) VT_EV(ev, (g) - 100u)
 
@@ -351,7 +365,7 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
     // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
     uint16_t* dst = &s.sc[qs][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < ((VT_EXP & 256) ? 0 : 8); ++j) {
       const uint32_t wj = valid ? w[j] : 0u;
       const uint32_t lo = __byte_perm(wj, 0, 0x1100), hi = __byte_perm(wj, 0, 0x3322);  // (b0, b0, b1, b1), (b2, b2, b3, b3)
       dst[(4 * j + 0) * 32] = uint16_t(lo & 0xFFFF), dst[(4 * j + 1) * 32] = uint16_t(lo >> 16);
@@ -364,8 +378,11 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   uint32_t h[32];
   {
     const uint32_t x = (uint32_t(r) >> 1) & P.kpe_swz_mask;
+#if VT_EXP & 256
+    for (int c = 0; c < 32; ++c) h[c] = c + r;
+#endif
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < ((VT_EXP & 256) ? 0 : 4); ++c) {
       const uint4 v = *reinterpret_cast<const uint4*>(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -377,8 +394,11 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   }
   // ---- scale factors of A: lane l of this quadrant holds, for K step a, columns 4a + j = the scale word a of token 32 j + l
   uint32_t f[32];
+#if VT_EXP & 256
+  for (int c = 0; c < 32; ++c) f[c] = 0x38383838u;
+#endif
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < ((VT_EXP & 256) ? 0 : 4); ++j) {
     const int tk = 32 * j + lane;
     const uint32_t x = (uint32_t(tk) >> 2) & P.sf_swz_mask;
     const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
@@ -472,20 +492,29 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   auto open_group = [&](uint32_t g) {
     const uint32_t tile = it + (g >> 2), qt = g & 3;
     const uint32_t slot = tile % kVtRawSlots, qi = 4 * tile + qt, qs = qi % kVtScRing;
+#if VT_EXP & 32
+    bool ok = true;
+#else
     bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[qs], (qi / kVtScRing) & 1, &s.abort_flag));
     ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
+#endif
     ok_all = ok_all && ok;
     raw_base = ptx::smem_u32(s.raw[slot]) + qt * 32 * 128 + row_off;
     sc_base = ptx::smem_u32(&s.sc[qs][0][0]) + 16 * q;
     if (quad == 0 && qt == 0) VT_EV(11, tile);
   };
   // unit (mb, ch) of the open group: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
-  auto load_unit = [&](int mb, int ch, VtUnitRegs& R) {
+  auto load_unit = [&](uint32_t g, int mb, int ch, VtUnitRegs& R) {
+    VT_T(t0_);
+    VT_EVU(4, it + (g >> 2), 4 * (g & 3) + 2 * mb + ch);
     const uint32_t chunk = 2 * quad + ch;
     ptx::ldmatrix_x2_trans_b8(raw_base + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
     const uint32_t a = sc_base + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sa.x), "=r"(R.sa.y), "=r"(R.sa.z), "=r"(R.sa.w) : "r"(a));
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sb.x), "=r"(R.sb.y), "=r"(R.sb.z), "=r"(R.sb.w) : "r"(a + 64));
+    VT_EVU(5, it + (g >> 2), 4 * (g & 3) + 2 * mb + ch);
+    VT_T(t1_);
+    VT_ACC(6, t0_, t1_);
   };
   uint32_t pending = ~0u;  // V^T ring slot stored but not yet published
   auto publish_pending = [&]() {
@@ -499,34 +528,74 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   // arithmetic and store of unit (mb, ch) of group g, whose loads are in R; false if a wait gave up
   auto finish_unit = [&](uint32_t g, int mb, int ch, const VtUnitRegs& R) -> bool {
     // word k of sa / sb: the byte pairs of tokens 16 (k / 2) + 4 q + 2 (k % 2) + {0, 1}
+    VT_T(t0_);
+    const uint32_t tile_ = it + (g >> 2), u_ = 4 * (g & 3) + 2 * mb + ch;
+    VT_EVU(0, tile_, u_);
     const uint32_t pa[4] = {R.sa.x, R.sa.y, R.sa.z, R.sa.w}, pb[4] = {R.sb.x, R.sb.y, R.sb.z, R.sb.w};
     uint32_t v[16];
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
+#if VT_EXP & 8
+      for (int i = 0; i < 4; ++i) ea[i] = R.rw[2 * tg] + i, eb[i] = R.rw[2 * tg + 1] + i;
+#else
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg + 1], eb);  // channel pair g + 8
+#endif
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t wa = pa[2 * tg + (i >> 1)], wb = pb[2 * tg + (i >> 1)];
+#if VT_EXP & 4
+        const uint32_t sa2 = wa, sb2 = wb;
+#else
         const uint32_t sa2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wa >> 16 : wa & 0xFFFF));  // (s, s) of token i, first block
         const uint32_t sb2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wb >> 16 : wb & 0xFFFF));
+#endif
+#if VT_EXP & 2
+        v[8 * tg + 2 * i] = ea[i] ^ sa2;
+        v[8 * tg + 2 * i + 1] = eb[i] ^ sb2;
+#else
         v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa2);
         v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb2);
+#endif
       }
     }
+#if defined(MLA_VT_PROF) || defined(MLA_VT_TRACE)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) asm volatile("" : "+r"(v[i]));
+#endif
+    VT_EVU(1, tile_, u_);
+    VT_T(t1_);
+    VT_ACC(4, t0_, t1_);
     const uint32_t tile = it + (g >> 2), qt = g & 3, sl = 2 * qt + mb;
     if (ch == 0) {
       // a new slot begins: publish the previous one, then make sure PV has released this ring slot's previous tile
+#if VT_EXP & 16
+      const bool ok = true;
+#else
       publish_pending();
       const bool ok = VT_WAIT(2, ptx::mbar_wait(&s.vt_free[sl], (tile & 1) ^ 1, &s.abort_flag));
+#endif
       ptx::tc_fence_after_sync();
       if (!__all_sync(~0u, ok)) return false;
       pending = sl;
       if (quad == 0 && sl == 0) VT_EV(12, tile);
       if (quad == 0 && sl == 7) VT_EV(13, tile);
     }
+    VT_EVU(2, tile_, u_);
+    VT_T(t2_);
+#if VT_EXP & 1
+    {
+      uint32_t x = 0;
+      for (int i = 0; i < 16; ++i) x ^= v[i];
+      if (x == 0x12345678u) s.abort_flag = 2;  // keeps the arithmetic alive
+    }
+#else
     ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(sl), v);
+#endif
+    VT_EVU(3, tile_, u_);
+    VT_T(t3_);
+    VT_ACC(5, t2_, t3_);
     return true;
   };
   // the inputs of group g have been read (their values are in registers or stored): release them
@@ -541,23 +610,25 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   };
   VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
   open_group(0);
-  load_unit(0, 0, ra);
+  load_unit(0, 0, 0, ra);
 #pragma unroll 1
   for (uint32_t g = 0; g < n_groups; ++g) {
-    load_unit(0, 1, rb);
+    load_unit(g, 0, 1, rb);
     if (!__all_sync(~0u, ok_all) || !finish_unit(g, 0, 0, ra)) return;
-    load_unit(1, 0, ra);
+    load_unit(g, 1, 0, ra);
     if (!finish_unit(g, 0, 1, rb)) return;
-    load_unit(1, 1, rb);
+    load_unit(g, 1, 1, rb);
     if (!finish_unit(g, 1, 0, ra)) return;
     if (g + 1 < n_groups) {
       open_group(g + 1);
-      load_unit(0, 0, ra);
+      load_unit(g + 1, 0, 0, ra);
     }
     if (!finish_unit(g, 1, 1, rb)) return;
     close_group(g);
   }
+#if !(VT_EXP & 16)
   publish_pending();
+#endif
   it += uint32_t(total);
 }
 
@@ -599,7 +670,7 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
 #pragma unroll
         for (int a = 1; a < 8; ++a) fp4(0, a, 1);
 #pragma unroll 1
-        for (int pp = 1; pp < kVtPasses; ++pp) {
+        for (int pp = 1; pp < ((VT_EXP & 128) ? 1 : kVtPasses); ++pp) {
 #pragma unroll
           for (int a = 0; a < 8; ++a) fp4(pp, a, 1);
         }
@@ -625,14 +696,18 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
 #pragma unroll 1
       for (int sl = 0; sl < 8; ++sl) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
         const uint32_t ring = sl;  // the ring holds exactly one tile
+#if !(VT_EXP & 16)
         if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[ring], it & 1, &s.abort_flag)))) return;
+#endif
         ptx::tc_fence_after_sync();
         if (leader) {
           const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
+#if !(VT_EXP & 64)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             ptx::mma_f16_ts(tm + VtCols::o(sl & 1), tm + VtCols::vt(ring) + 8 * ks, p_desc + ((ks * 32) >> 4), idesc,
                             (t | (sl >> 1) | ks) != 0);
+#endif
           ptx::mma_commit(&s.vt_free[ring]);
           if (sl == 7) ptx::mma_commit(&s.p_free[buf]);
         }
@@ -740,7 +815,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       if (it >= 2) VT_WAIT(1, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
       uint8_t* const p_base = s.p[buf][r >> 5] + p_off;
 #pragma unroll
-      for (int h = 0; h < N; ++h) {
+      for (int h = 0; h < ((VT_EXP & 512) ? 1 : N); ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
         const uint32_t w = ptx::f32x2_to_f16x2(pv, 0.f);  // (p, 0): the even channel of the pair
