@@ -53,7 +53,7 @@ namespace mla {
 #endif
 constexpr int kVtRawSlots = 3;   // raw tiles in flight
 constexpr int kVtRing = 8;       // V^T slots (32 tokens x 128 channel pairs, 32 columns): one tile
-constexpr int kVtScRing = 12;    // quarter-tile scale tables (2 KB each)
+constexpr int kVtScRing = 3;     // scale tables of whole tiles (8 KB each)
 #ifndef VT_TERMS
 #define VT_TERMS 4
 #endif
@@ -118,7 +118,7 @@ struct VtSmem {
   alignas(1024) uint8_t qrope[16 * 128];            // rope part of Q^T as FP16
   alignas(1024) uint8_t p[2][4][32 * 128];          // P^T: [buffer][32-token group][row 2h + parity], 128-byte swizzle
   alignas(1024) uint8_t raw[kVtRawSlots][kVtRawTileBytes];
-  alignas(16) uint16_t sc[kVtScRing][32][32];       // block scales as E4M3 byte pairs (b, b): [quarter tile][block][token slot], the
+  alignas(16) uint16_t sc[kVtScRing][4][32][32];    // block scales as E4M3 byte pairs (b, b): [tile][quarter][block][token slot], the
                                                     // slot of token 16 h + 4 q + i of the quarter being 8 q + 4 h + i
   Seg segs[kSegBatch];
   float qa[4][16];                                  // per-head score scale, ring indexed by segment count
@@ -131,7 +131,7 @@ struct VtSmem {
   uint64_t rope_free;                               // QK^T's rope MMAs of the tile complete (rope K is single-buffered)
   uint64_t s_full[2], s_free[2];
   uint64_t p_full[2], p_free[2];
-  uint64_t vt_full[kVtRing], vt_free[kVtRing];
+  uint64_t vt_full[2], vt_free[2];                  // halves of the V^T ring (64 tokens each)
   uint64_t sc_full[kVtScRing], sc_free[kVtScRing];
   uint32_t tmem_base;
   int abort_flag;
@@ -152,20 +152,38 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
     const int* pt = P.page_table + (long long)seg.b * P.pt_stride;
+    // page ids of a tile's two half tiles and of the two that are prefetched into L2 (three tiles ahead: the ring itself
+    // is too shallow to cover HBM latency); read one tile ahead of their use so that nothing ever waits for them
+    auto fetch_ids = [&](int tk0, int (&pg)[2], int (&pf)[2]) {
+      pg[0] = pg[1] = 0, pf[0] = pf[1] = -1;
+      if (ps >= HALF && lane == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int tk = tk0 + h * HALF;
+          if (tk < seg.tok_end) pg[h] = pt[tk >> P.page_shift];
+          if (tk + 3 * TILE < seg.tok_end) pf[h] = pt[(tk + 3 * TILE) >> P.page_shift];
+        }
+      }
+    };
+    int page_nx[2], pf_nx[2];
+    fetch_ids(seg.tok0, page_nx, pf_nx);
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const int slot = it % kVtRawSlots;
       const int tok = seg.tok0 + t * TILE;
       int nvalid = seg.tok_end - tok;
       nvalid = nvalid < 0 ? 0 : (nvalid > TILE ? TILE : nvalid);
-      // page ids of the two half tiles and of the two that are prefetched into L2 (three tiles ahead: the ring itself is
-      // too shallow to cover HBM latency), read before the wait for the slot so that their latency hides behind it
-      int page[2] = {0, 0}, page_pf[2] = {-1, -1};
-      if (ps >= HALF && lane == 0) {
+      const int page[2] = {page_nx[0], page_nx[1]}, page_pf[2] = {pf_nx[0], pf_nx[1]};
+      if (t + 1 < seg.ntiles) fetch_ids(tok + TILE, page_nx, pf_nx);
+      if (ps >= HALF && lane == 0) {  // the prefetches do not need the slot: issued before the wait for it
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int tk = tok + h * HALF;
-          if (tk < seg.tok_end) page[h] = pt[tk >> P.page_shift];
-          if (tk + 3 * TILE < seg.tok_end) page_pf[h] = pt[(tk + 3 * TILE) >> P.page_shift];
+          if (uint32_t(page_pf[h]) < uint32_t(P.num_pages)) {
+            const int row2 = (page_pf[h] << P.page_shift) + ((tok + h * HALF + 3 * TILE) & (ps - 1));
+            ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
+            ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
+            ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+          }
         }
       }
       const bool ok = ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag);
@@ -190,15 +208,6 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
             ptx::tma_load_2d(dst + kVtRawHi + h * HALF * 128, ckv_map, 128, row, bar);
             ptx::tma_load_2d(dst + kVtRawSf + h * HALF * 32, sf_map, 0, row, bar);
             ptx::tma_load_2d(dst + kVtRawKpe + h * HALF * 64, kpe_map, 0, row, bar);
-          }
-          for (int h = 0; h < 2; ++h) {
-            if (uint32_t(page_pf[h]) < uint32_t(P.num_pages)) {
-              const int row2 = (page_pf[h] << P.page_shift) + ((tok + h * HALF) & (ps - 1));
-              ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
-              ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
-              ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
-              ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
-            }
           }
         }
       } else {
@@ -360,10 +369,10 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
     const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((0u ^ x) << 4));
     const uint4 b = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    const uint32_t qi = 4 * it + quad, qs = qi % kVtScRing;  // this warp's quarter of the tile has a table of its own in the ring
-    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((qi / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
+    const uint32_t qs = it % kVtScRing;  // the tile's table; this warp writes its quarter
+    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((it / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
     // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
-    uint16_t* dst = &s.sc[qs][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)];
+    uint16_t* dst = &s.sc[qs][quad][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)];
 #pragma unroll
     for (int j = 0; j < ((VT_EXP & 256) ? 0 : 8); ++j) {
       const uint32_t wj = valid ? w[j] : 0u;
@@ -467,9 +476,11 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
 // A unit of work is one transposing ldmatrix: 32 tokens x 16 channel pairs (two scale blocks), i.e. half of this
 // warp's share of a V^T slot. A 32-token group is four units (2 blocks x 2 halves), a tile four groups. The scales come
 // from the table as E4M3 byte pairs (b, b), which the conversion instruction turns into the FP16 pair (s, s) it is
-// multiplied with. The loop over groups is software pipelined: the loads of a unit are issued before the arithmetic of
-// the unit before it, and a finished slot is published only after the arithmetic of the following unit, when its
-// tensor-memory stores have landed.
+// multiplied with. Every synchronisation costs this warp a shared-memory round trip during which it has nothing else
+// to do, so there are few of them: the inputs are waited for once per tile, and V^T is handed to the PV warp in halves of
+// 64 tokens (four ring slots). The loop over groups is software pipelined: the loads of a unit are issued before the
+// arithmetic of the unit before it, barrier tests are issued ahead of the point that needs their answer, and a finished
+// half is published only after the arithmetic of the following unit, when its tensor-memory stores have landed.
 struct VtUnitRegs {
   uint32_t rw[4];
   uint4 sa, sb;  // scale byte pairs of the unit's two blocks: 8 tokens each (4q .. 4q + 3 of both 16-token halves)
@@ -486,149 +497,104 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   const uint32_t n_groups = 4u * uint32_t(total);
   // per-lane constants: byte offset of this lane's ldmatrix row inside a 32-token group, swizzle term
   const uint32_t row_off = uint32_t(16 * mat + mrow) * 128, swz = uint32_t(mrow & 7);
-  bool ok_all = true;
-  uint32_t raw_base = 0, sc_base = 0;  // of the group whose loads are being issued
-  // group g of this batch: tile it + g / 4, token group g % 4. Waits for its scale table and raw bytes.
-  auto open_group = [&](uint32_t g) {
-    const uint32_t tile = it + (g >> 2), qt = g & 3;
-    const uint32_t slot = tile % kVtRawSlots, qi = 4 * tile + qt, qs = qi % kVtScRing;
-#if VT_EXP & 32
-    bool ok = true;
-#else
-    bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[qs], (qi / kVtScRing) & 1, &s.abort_flag));
+  uint32_t raw_base = 0, sc_base = 0;  // of the tile whose loads are being issued
+  // tile `tile`: waits for its scale table and raw bytes; false if a wait gave up
+  auto open_tile = [&](uint32_t tile) -> bool {
+    const uint32_t slot = tile % kVtRawSlots, ts = tile % kVtScRing;
+    bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag));
     ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
-#endif
-    ok_all = ok_all && ok;
-    raw_base = ptx::smem_u32(s.raw[slot]) + qt * 32 * 128 + row_off;
-    sc_base = ptx::smem_u32(&s.sc[qs][0][0]) + 16 * q;
-    if (quad == 0 && qt == 0) VT_EV(11, tile);
+    raw_base = ptx::smem_u32(s.raw[slot]) + row_off;
+    sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 16 * q;
+    if (quad == 0) VT_EV(11, tile);
+    return __all_sync(~0u, ok);
   };
-  // unit (mb, ch) of the open group: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
-  auto load_unit = [&](uint32_t g, int mb, int ch, VtUnitRegs& R) {
-    VT_T(t0_);
-    VT_EVU(4, it + (g >> 2), 4 * (g & 3) + 2 * mb + ch);
+  // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
+  auto load_unit = [&](uint32_t qt, int mb, int ch, VtUnitRegs& R) {
     const uint32_t chunk = 2 * quad + ch;
-    ptx::ldmatrix_x2_trans_b8(raw_base + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
-    const uint32_t a = sc_base + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
+    ptx::ldmatrix_x2_trans_b8(raw_base + qt * (32 * 128) + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
+    const uint32_t a = sc_base + qt * 2048 + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sa.x), "=r"(R.sa.y), "=r"(R.sa.z), "=r"(R.sa.w) : "r"(a));
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sb.x), "=r"(R.sb.y), "=r"(R.sb.z), "=r"(R.sb.w) : "r"(a + 64));
-    VT_EVU(5, it + (g >> 2), 4 * (g & 3) + 2 * mb + ch);
-    VT_T(t1_);
-    VT_ACC(6, t0_, t1_);
   };
-  uint32_t pending = ~0u;  // V^T ring slot stored but not yet published
+  uint32_t pending = ~0u;  // half of the V^T ring stored but not yet published
   auto publish_pending = [&]() {
     if (pending != ~0u) {
       VT_WAIT(3, (ptx::tmem_wait_st(), true));
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&s.vt_full[pending]);
+      pending = ~0u;
     }
   };
   // arithmetic and store of unit (mb, ch) of group g, whose loads are in R; false if a wait gave up
   auto finish_unit = [&](uint32_t g, int mb, int ch, const VtUnitRegs& R) -> bool {
+    const uint32_t tile = it + (g >> 2), qt = g & 3, sl = 2 * qt + mb;
+    const bool new_half = mb == 0 && ch == 0 && (qt & 1) == 0;
+    // PV must have released this half of the ring (the previous tile's): the test is issued now, its answer used after the arithmetic
+    uint32_t probed = 0;
+    if (new_half) probed = ptx::mbar_probe(&s.vt_free[qt >> 1], (tile & 1) ^ 1);
     // word k of sa / sb: the byte pairs of tokens 16 (k / 2) + 4 q + 2 (k % 2) + {0, 1}
-    VT_T(t0_);
-    const uint32_t tile_ = it + (g >> 2), u_ = 4 * (g & 3) + 2 * mb + ch;
-    VT_EVU(0, tile_, u_);
     const uint32_t pa[4] = {R.sa.x, R.sa.y, R.sa.z, R.sa.w}, pb[4] = {R.sb.x, R.sb.y, R.sb.z, R.sb.w};
     uint32_t v[16];
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
-#if VT_EXP & 8
-      for (int i = 0; i < 4; ++i) ea[i] = R.rw[2 * tg] + i, eb[i] = R.rw[2 * tg + 1] + i;
-#else
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg + 1], eb);  // channel pair g + 8
-#endif
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t wa = pa[2 * tg + (i >> 1)], wb = pb[2 * tg + (i >> 1)];
-#if VT_EXP & 4
-        const uint32_t sa2 = wa, sb2 = wb;
-#else
         const uint32_t sa2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wa >> 16 : wa & 0xFFFF));  // (s, s) of token i, first block
         const uint32_t sb2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wb >> 16 : wb & 0xFFFF));
-#endif
-#if VT_EXP & 2
-        v[8 * tg + 2 * i] = ea[i] ^ sa2;
-        v[8 * tg + 2 * i + 1] = eb[i] ^ sb2;
-#else
         v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa2);
         v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb2);
-#endif
       }
     }
-#if defined(MLA_VT_PROF) || defined(MLA_VT_TRACE)
-#pragma unroll
-    for (int i = 0; i < 16; ++i) asm volatile("" : "+r"(v[i]));
-#endif
-    VT_EVU(1, tile_, u_);
-    VT_T(t1_);
-    VT_ACC(4, t0_, t1_);
-    const uint32_t tile = it + (g >> 2), qt = g & 3, sl = 2 * qt + mb;
-    if (ch == 0) {
-      // a new slot begins: publish the previous one, then make sure PV has released this ring slot's previous tile
-#if VT_EXP & 16
-      const bool ok = true;
-#else
-      publish_pending();
-      const bool ok = VT_WAIT(2, ptx::mbar_wait(&s.vt_free[sl], (tile & 1) ^ 1, &s.abort_flag));
-#endif
+    if (mb == 0 && ch == 0) publish_pending();  // the previous half, if this group is the first after it
+    if (new_half) {
+      const bool ok = VT_WAIT(2, ptx::mbar_wait_probed(probed, &s.vt_free[qt >> 1], (tile & 1) ^ 1, &s.abort_flag));
       ptx::tc_fence_after_sync();
       if (!__all_sync(~0u, ok)) return false;
-      pending = sl;
-      if (quad == 0 && sl == 0) VT_EV(12, tile);
-      if (quad == 0 && sl == 7) VT_EV(13, tile);
+      if (quad == 0 && qt == 0) VT_EV(12, tile);
+      if (quad == 0 && qt == 2) VT_EV(13, tile);
     }
-    VT_EVU(2, tile_, u_);
-    VT_T(t2_);
-#if VT_EXP & 1
-    {
-      uint32_t x = 0;
-      for (int i = 0; i < 16; ++i) x ^= v[i];
-      if (x == 0x12345678u) s.abort_flag = 2;  // keeps the arithmetic alive
-    }
-#else
     ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(sl), v);
-#endif
-    VT_EVU(3, tile_, u_);
-    VT_T(t3_);
-    VT_ACC(5, t2_, t3_);
     return true;
   };
-  // the inputs of group g have been read (their values are in registers or stored): release them
-  auto close_group = [&](uint32_t g) {
-    const uint32_t tile = it + (g >> 2), qt = g & 3;
-    __syncwarp();
-    if (lane == 0) {
-      ptx::mbar_arrive(&s.sc_free[(4 * tile + qt) % kVtScRing]);
-      if (qt == 3) ptx::mbar_arrive(&s.raw_empty[tile % kVtRawSlots]);
-    }
-    if (quad == 0 && qt == 3) VT_EV(14, tile);
-  };
   VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
-  open_group(0);
+  if (!open_tile(it)) return;
   load_unit(0, 0, 0, ra);
 #pragma unroll 1
   for (uint32_t g = 0; g < n_groups; ++g) {
-    load_unit(g, 0, 1, rb);
-    if (!__all_sync(~0u, ok_all) || !finish_unit(g, 0, 0, ra)) return;
-    load_unit(g, 1, 0, ra);
+    const uint32_t qt = g & 3, tile = it + (g >> 2);
+    load_unit(qt, 0, 1, rb);
+    if (!finish_unit(g, 0, 0, ra)) return;
+    load_unit(qt, 1, 0, ra);
     if (!finish_unit(g, 0, 1, rb)) return;
-    load_unit(g, 1, 1, rb);
+    load_unit(qt, 1, 1, rb);
     if (!finish_unit(g, 1, 0, ra)) return;
-    if (g + 1 < n_groups) {
-      open_group(g + 1);
-      load_unit(g + 1, 0, 0, ra);
+    if (qt == 3) {
+      // the last loads of the tile have been issued: the next tile's inputs, then its first loads
+      if (g + 1 < n_groups) {
+        if (!open_tile(tile + 1)) return;
+        load_unit(0, 0, 0, ra);
+      }
+    } else {
+      load_unit(qt + 1, 0, 0, ra);
     }
     if (!finish_unit(g, 1, 1, rb)) return;
-    close_group(g);
+    if (qt & 1) pending = qt >> 1;
+    if (qt == 3) {
+      // every input of the tile is in a register or stored: release the table and this warp's share of the raw slot
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(&s.sc_free[tile % kVtScRing]);
+        ptx::mbar_arrive(&s.raw_empty[tile % kVtRawSlots]);
+      }
+      if (quad == 0) VT_EV(14, tile);
+    }
   }
-#if !(VT_EXP & 16)
   publish_pending();
-#endif
   it += uint32_t(total);
 }
 
@@ -694,25 +660,24 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
       if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
       VT_EV(8, it);
 #pragma unroll 1
-      for (int sl = 0; sl < 8; ++sl) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
-        const uint32_t ring = sl;  // the ring holds exactly one tile
-#if !(VT_EXP & 16)
-        if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[ring], it & 1, &s.abort_flag)))) return;
-#endif
+      for (int hf = 0; hf < 2; ++hf) {  // half of the ring = 64 tokens = slots 4 hf .. 4 hf + 3
+        if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[hf], it & 1, &s.abort_flag)))) return;
         ptx::tc_fence_after_sync();
         if (leader) {
-          const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
-#if !(VT_EXP & 64)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            ptx::mma_f16_ts(tm + VtCols::o(sl & 1), tm + VtCols::vt(ring) + 8 * ks, p_desc + ((ks * 32) >> 4), idesc,
-                            (t | (sl >> 1) | ks) != 0);
-#endif
-          ptx::mma_commit(&s.vt_free[ring]);
-          if (sl == 7) ptx::mma_commit(&s.p_free[buf]);
+          for (int k = 0; k < 4; ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
+            const int sl = 4 * hf + k;
+            const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              ptx::mma_f16_ts(tm + VtCols::o(sl & 1), tm + VtCols::vt(sl) + 8 * ks, p_desc + ((ks * 32) >> 4), idesc,
+                              (t | (sl >> 1) | ks) != 0);
+          }
+          ptx::mma_commit(&s.vt_free[hf]);
+          if (hf == 1) ptx::mma_commit(&s.p_free[buf]);
         }
-        if (sl == 0) VT_EV(9, it);
-        if (sl == 7) VT_EV(10, it);
+        if (hf == 0) VT_EV(9, it);
+        if (hf == 1) VT_EV(10, it);
       }
     }
   }
@@ -921,8 +886,8 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kVtRawSlots; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 9);  // 4 K + 4 V warps + QK^T
-    for (int i = 0; i < kVtRing; ++i) ptx::mbar_init(&s.vt_full[i], 4), ptx::mbar_init(&s.vt_free[i], 1);
-    for (int i = 0; i < kVtScRing; ++i) ptx::mbar_init(&s.sc_full[i], 1), ptx::mbar_init(&s.sc_free[i], 4);
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.vt_full[i], 4), ptx::mbar_init(&s.vt_free[i], 1);
+    for (int i = 0; i < kVtScRing; ++i) ptx::mbar_init(&s.sc_full[i], 4), ptx::mbar_init(&s.sc_free[i], 4);
     ptx::mbar_init(&s.rope_free, 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.k_full[i], 4), ptx::mbar_init(&s.k_free[i], 1);

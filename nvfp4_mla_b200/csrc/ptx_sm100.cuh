@@ -72,6 +72,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// Split form of the bounded wait, for a barrier that has usually completed by the time it is needed: mbar_probe()
+// issues the test early (its answer takes as long as any shared-memory round trip, during which the thread carries on
+// with independent work), mbar_wait_probed() consumes the answer and only polls if the test failed.
+__device__ __forceinline__ uint32_t mbar_probe(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_probed(uint32_t probed, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return probed != 0 || mbar_wait(bar, parity, abort_flag);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // fences between proxies / tcgen05 ordering
 // ---------------------------------------------------------------------------------------------------------------
