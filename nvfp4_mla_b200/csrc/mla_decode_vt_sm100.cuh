@@ -511,10 +511,27 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
   auto load_unit = [&](uint32_t qt, int mb, int ch, VtUnitRegs& R) {
     const uint32_t chunk = 2 * quad + ch;
+#if VT_EXP & 1024
+    R.rw[0] = R.rw[1] = R.rw[2] = R.rw[3] = chunk + qt, R.sa = make_uint4(qt, mb, ch, 1), R.sb = R.sa;
+    return;
+#endif
+#if VT_DBG & 32
+    VT_T(tl0_);
+#endif
     ptx::ldmatrix_x2_trans_b8(raw_base + qt * (32 * 128) + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
+#if VT_DBG & 32
+    asm volatile("mov.b32 %0, %0;" : "+r"(R.rw[0]));
+    VT_T(tl1_);
+    VT_ACC(4, tl0_, tl1_);
+#endif
     const uint32_t a = sc_base + qt * 2048 + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sa.x), "=r"(R.sa.y), "=r"(R.sa.z), "=r"(R.sa.w) : "r"(a));
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sb.x), "=r"(R.sb.y), "=r"(R.sb.z), "=r"(R.sb.w) : "r"(a + 64));
+#if VT_DBG & 32
+    asm volatile("mov.b32 %0, %0;" : "+r"(R.sb.x));
+    VT_T(tl2_);
+    VT_ACC(5, tl1_, tl2_);
+#endif
   };
   uint32_t pending = ~0u;  // half of the V^T ring stored but not yet published
   auto publish_pending = [&]() {
@@ -539,15 +556,28 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
+#if VT_EXP & 8
+      for (int i = 0; i < 4; ++i) ea[i] = R.rw[2 * tg] + i, eb[i] = R.rw[2 * tg + 1] + i;
+#else
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg + 1], eb);  // channel pair g + 8
+#endif
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t wa = pa[2 * tg + (i >> 1)], wb = pb[2 * tg + (i >> 1)];
+#if VT_EXP & 4
+        const uint32_t sa2 = wa, sb2 = wb;
+#else
         const uint32_t sa2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wa >> 16 : wa & 0xFFFF));  // (s, s) of token i, first block
         const uint32_t sb2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wb >> 16 : wb & 0xFFFF));
+#endif
+#if VT_EXP & 2
+        v[8 * tg + 2 * i] = ea[i] ^ sa2;
+        v[8 * tg + 2 * i + 1] = eb[i] ^ sb2;
+#else
         v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa2);
         v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb2);
+#endif
       }
     }
     if (mb == 0 && ch == 0) publish_pending();  // the previous half, if this group is the first after it
@@ -558,7 +588,15 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
       if (quad == 0 && qt == 0) VT_EV(12, tile);
       if (quad == 0 && qt == 2) VT_EV(13, tile);
     }
+#if VT_EXP & 1
+    {
+      uint32_t x = 0;
+      for (int i = 0; i < 16; ++i) x ^= v[i];
+      if (x == 0x12345678u) s.abort_flag = 2;  // keeps the arithmetic alive
+    }
+#else
     ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(sl), v);
+#endif
     return true;
   };
   VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
@@ -619,6 +657,7 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
       if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.k_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
       ptx::tc_fence_after_sync();
       VT_EV(4, it);
+      VT_T(tq0_);
       if (leader) {
         const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.raw[slot]), 16, 1024);
         // K step a = channels [64 a, +64): panel a / 4, 32 bytes per step. B of pass pp = rows [term 2 pp | term 2 pp + 1].
@@ -640,9 +679,13 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
 #pragma unroll
           for (int a = 0; a < 8; ++a) fp4(pp, a, 1);
         }
+        VT_T(tq1_);
+        VT_ACC(4, tq0_, tq1_);
         ptx::mma_commit(&s.k_free[buf]);
         ptx::mma_commit(&s.s_full[buf]);
         ptx::mma_commit(&s.raw_empty[slot]);
+        VT_T(tq2_);
+        VT_ACC(5, tq1_, tq2_);
       }
       VT_EV(5, it);
     }
@@ -663,9 +706,10 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
       for (int hf = 0; hf < 2; ++hf) {  // half of the ring = 64 tokens = slots 4 hf .. 4 hf + 3
         if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[hf], it & 1, &s.abort_flag)))) return;
         ptx::tc_fence_after_sync();
+        VT_T(tp0_);
         if (leader) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
+          for (int k = 0; k < ((VT_EXP & 64) ? 0 : 4); ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
             const int sl = 4 * hf + k;
             const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
 #pragma unroll
@@ -673,8 +717,12 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
               ptx::mma_f16_ts(tm + VtCols::o(sl & 1), tm + VtCols::vt(sl) + 8 * ks, p_desc + ((ks * 32) >> 4), idesc,
                               (t | (sl >> 1) | ks) != 0);
           }
+          VT_T(tp1_);
+          VT_ACC(4, tp0_, tp1_);
           ptx::mma_commit(&s.vt_free[hf]);
           if (hf == 1) ptx::mma_commit(&s.p_free[buf]);
+          VT_T(tp2_);
+          VT_ACC(5, tp1_, tp2_);
         }
         if (hf == 0) VT_EV(9, it);
         if (hf == 1) VT_EV(10, it);
