@@ -53,7 +53,7 @@ namespace mla {
 #endif
 constexpr int kVtRawSlots = 3;   // raw tiles in flight
 constexpr int kVtRing = 8;       // V^T slots (32 tokens x 128 channel pairs, 32 columns): one tile
-constexpr int kVtScRing = 3;     // scale tables of whole tiles (8 KB each)
+constexpr int kVtScRing = 2;     // scale tables of whole tiles (16 KB each)
 #ifndef VT_TERMS
 #define VT_TERMS 4
 #endif
@@ -118,8 +118,8 @@ struct VtSmem {
   alignas(1024) uint8_t qrope[16 * 128];            // rope part of Q^T as FP16
   alignas(1024) uint8_t p[2][4][32 * 128];          // P^T: [buffer][32-token group][row 2h + parity], 128-byte swizzle
   alignas(1024) uint8_t raw[kVtRawSlots][kVtRawTileBytes];
-  alignas(16) uint16_t sc[kVtScRing][4][32][32];    // block scales as E4M3 byte pairs (b, b): [tile][quarter][block][token slot], the
-                                                    // slot of token 16 h + 4 q + i of the quarter being 8 q + 4 h + i
+  alignas(16) uint32_t sc[kVtScRing][4][32][32];    // block scales as FP16 pairs (s, s): [tile][quarter][block][token slot], the slot
+                                                    // of token 16 h + 4 q + i of the quarter being 8 q + 4 h + i
   Seg segs[kSegBatch];
   float qa[4][16];                                  // per-head score scale, ring indexed by segment count
   float red[4][16];
@@ -356,33 +356,12 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   const int r = quad * 32 + lane;
   const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
   const int slot = it % kVtRawSlots;
-  const uint8_t* raw = s.raw[slot];
+  const uint32_t raw = ptx::smem_u32(s.raw[slot]);
   const uint32_t buf = it & 1;
   if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return false;
   const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
   if (quad == 0) VT_EV(2, it);
 
-  // ---- block scales of this token for the V warps: each E4M3 byte doubled (the conversion of the pair gives (s, s)); 0
-  // beyond the request's end
-  {
-    const uint32_t x = (uint32_t(r) >> 2) & P.sf_swz_mask;
-    const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((0u ^ x) << 4));
-    const uint4 b = *reinterpret_cast<const uint4*>(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    const uint32_t qs = it % kVtScRing;  // the tile's table; this warp writes its quarter
-    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((it / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
-    // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
-    uint16_t* dst = &s.sc[qs][quad][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)];
-#pragma unroll
-    for (int j = 0; j < ((VT_EXP & 256) ? 0 : 8); ++j) {
-      const uint32_t wj = valid ? w[j] : 0u;
-      const uint32_t lo = __byte_perm(wj, 0, 0x1100), hi = __byte_perm(wj, 0, 0x3322);  // (b0, b0, b1, b1), (b2, b2, b3, b3)
-      dst[(4 * j + 0) * 32] = uint16_t(lo & 0xFFFF), dst[(4 * j + 1) * 32] = uint16_t(lo >> 16);
-      dst[(4 * j + 2) * 32] = uint16_t(hi & 0xFFFF), dst[(4 * j + 3) * 32] = uint16_t(hi >> 16);
-    }
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.sc_full[qs]);
-  }
   // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs
   uint32_t h[32];
   {
@@ -392,7 +371,7 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
 #endif
 #pragma unroll
     for (int c = 0; c < ((VT_EXP & 256) ? 0 : 4); ++c) {
-      const uint4 v = *reinterpret_cast<const uint4*>(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
+      const uint4 v = ptx::lds128(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -410,8 +389,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   for (int j = 0; j < ((VT_EXP & 256) ? 0 : 4); ++j) {
     const int tk = 32 * j + lane;
     const uint32_t x = (uint32_t(tk) >> 2) & P.sf_swz_mask;
-    const uint4 a = *reinterpret_cast<const uint4*>(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
-    const uint4 b = *reinterpret_cast<const uint4*>(raw + kVtRawSf + tk * 32 + ((1u ^ x) << 4));
+    const uint4 a = ptx::lds128(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
+    const uint4 b = ptx::lds128(raw + kVtRawSf + tk * 32 + ((1u ^ x) << 4));
     f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
   }
   // QK^T of tile it - 2 must have finished with this scale-factor buffer, the rope MMAs of tile it - 1 with rope K
@@ -421,13 +400,36 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   if (!__all_sync(~0u, ok)) return false;
   ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
   ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
-  __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);  // every byte this warp read from the raw tile is in a register or stored
   VT_WAIT(3, (ptx::tmem_wait_st(), true));
   ptx::tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) ptx::mbar_arrive(&s.k_full[buf]);
   if (quad == 0) VT_EV(3, it);
+  // ---- block scales of this token for the V warps, as FP16 pairs (s, s) ready to be multiplied with a converted byte; 0
+  // beyond the request's end. Written last: the V warps are the furthest behind of all readers of the tile, and the wait
+  // for a free table must not hold up QK^T.
+  {
+    const uint32_t x = (uint32_t(r) >> 2) & P.sf_swz_mask;
+    const uint4 a = ptx::lds128(raw + kVtRawSf + r * 32 + ((0u ^ x) << 4));
+    const uint4 b = ptx::lds128(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t qs = it % kVtScRing;  // the tile's table; this warp writes its quarter
+    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((it / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
+    // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
+    const uint32_t dst = ptx::smem_u32(&s.sc[qs][quad][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)]);
+#pragma unroll
+    for (int j = 0; j < ((VT_EXP & 256) ? 0 : 8); ++j) {
+      const uint32_t wj = valid ? w[j] : 0u;
+      const uint32_t lo = ptx::e4m3x2_to_f16x2(uint16_t(wj & 0xFFFF)), hi = ptx::e4m3x2_to_f16x2(uint16_t(wj >> 16));
+      ptx::sts32(dst + (4 * j + 0) * 128, __byte_perm(lo, 0, 0x1010)), ptx::sts32(dst + (4 * j + 1) * 128, __byte_perm(lo, 0, 0x3232));
+      ptx::sts32(dst + (4 * j + 2) * 128, __byte_perm(hi, 0, 0x1010)), ptx::sts32(dst + (4 * j + 3) * 128, __byte_perm(hi, 0, 0x3232));
+    }
+    __syncwarp();
+    if (lane == 0) {
+      ptx::mbar_arrive(&s.sc_full[qs]);
+      ptx::mbar_arrive(&s.raw_empty[slot]);  // every byte this warp needs from the raw tile is in a register or stored
+    }
+  }
   return true;
 }
 
@@ -483,7 +485,7 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
 // half is published only after the arithmetic of the following unit, when its tensor-memory stores have landed.
 struct VtUnitRegs {
   uint32_t rw[4];
-  uint4 sa, sb;  // scale byte pairs of the unit's two blocks: 8 tokens each (4q .. 4q + 3 of both 16-token halves)
+  uint4 sa[2], sb[2];  // (s, s) of the unit's two blocks: 8 tokens each (4q .. 4q + 3 of both 16-token halves)
 };
 __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int n_segs, uint32_t& it) {
   const int lane = ptx::lane_id();
@@ -504,17 +506,13 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag));
     ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
     raw_base = ptx::smem_u32(s.raw[slot]) + row_off;
-    sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 16 * q;
+    sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 32 * q;
     if (quad == 0) VT_EV(11, tile);
     return __all_sync(~0u, ok);
   };
   // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
   auto load_unit = [&](uint32_t qt, int mb, int ch, VtUnitRegs& R) {
     const uint32_t chunk = 2 * quad + ch;
-#if VT_EXP & 1024
-    R.rw[0] = R.rw[1] = R.rw[2] = R.rw[3] = chunk + qt, R.sa = make_uint4(qt, mb, ch, 1), R.sb = R.sa;
-    return;
-#endif
 #if VT_DBG & 32
     VT_T(tl0_);
 #endif
@@ -524,14 +522,11 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     VT_T(tl1_);
     VT_ACC(4, tl0_, tl1_);
 #endif
-    const uint32_t a = sc_base + qt * 2048 + (16 * mb + 2 * chunk) * 64;  // block row of the table: [4 q][2 halves][4 tokens] byte pairs
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sa.x), "=r"(R.sa.y), "=r"(R.sa.z), "=r"(R.sa.w) : "r"(a));
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(R.sb.x), "=r"(R.sb.y), "=r"(R.sb.z), "=r"(R.sb.w) : "r"(a + 64));
-#if VT_DBG & 32
-    asm volatile("mov.b32 %0, %0;" : "+r"(R.sb.x));
-    VT_T(tl2_);
-    VT_ACC(5, tl1_, tl2_);
-#endif
+    const uint32_t a = sc_base + qt * 4096 + (16 * mb + 2 * chunk) * 128;  // block row of the table: [4 q][2 halves][4 tokens] words
+    auto lds = [](uint4& d, uint32_t addr) {
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "r"(addr));
+    };
+    lds(R.sa[0], a), lds(R.sa[1], a + 16), lds(R.sb[0], a + 128), lds(R.sb[1], a + 144);
   };
   uint32_t pending = ~0u;  // half of the V^T ring stored but not yet published
   auto publish_pending = [&]() {
@@ -550,34 +545,17 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     // PV must have released this half of the ring (the previous tile's): the test is issued now, its answer used after the arithmetic
     uint32_t probed = 0;
     if (new_half) probed = ptx::mbar_probe(&s.vt_free[qt >> 1], (tile & 1) ^ 1);
-    // word k of sa / sb: the byte pairs of tokens 16 (k / 2) + 4 q + 2 (k % 2) + {0, 1}
-    const uint32_t pa[4] = {R.sa.x, R.sa.y, R.sa.z, R.sa.w}, pb[4] = {R.sb.x, R.sb.y, R.sb.z, R.sb.w};
     uint32_t v[16];
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
-#if VT_EXP & 8
-      for (int i = 0; i < 4; ++i) ea[i] = R.rw[2 * tg] + i, eb[i] = R.rw[2 * tg + 1] + i;
-#else
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg], ea);      // channel pair g, tokens 16 tg + 4q + i
       ptx::e2m1x8_to_f16x8(R.rw[2 * tg + 1], eb);  // channel pair g + 8
-#endif
+      const uint32_t pa[4] = {R.sa[tg].x, R.sa[tg].y, R.sa[tg].z, R.sa[tg].w}, pb[4] = {R.sb[tg].x, R.sb[tg].y, R.sb[tg].z, R.sb[tg].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint32_t wa = pa[2 * tg + (i >> 1)], wb = pb[2 * tg + (i >> 1)];
-#if VT_EXP & 4
-        const uint32_t sa2 = wa, sb2 = wb;
-#else
-        const uint32_t sa2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wa >> 16 : wa & 0xFFFF));  // (s, s) of token i, first block
-        const uint32_t sb2 = ptx::e4m3x2_to_f16x2(uint16_t(i & 1 ? wb >> 16 : wb & 0xFFFF));
-#endif
-#if VT_EXP & 2
-        v[8 * tg + 2 * i] = ea[i] ^ sa2;
-        v[8 * tg + 2 * i + 1] = eb[i] ^ sb2;
-#else
-        v[8 * tg + 2 * i] = ptx::hmul2(ea[i], sa2);
-        v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], sb2);
-#endif
+        v[8 * tg + 2 * i] = ptx::hmul2(ea[i], pa[i]);
+        v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], pb[i]);
       }
     }
     if (mb == 0 && ch == 0) publish_pending();  // the previous half, if this group is the first after it
@@ -826,14 +804,14 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
       if (it >= 2) VT_WAIT(1, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
-      uint8_t* const p_base = s.p[buf][r >> 5] + p_off;
+      const uint32_t p_base = ptx::smem_u32(s.p[buf][r >> 5]) + p_off;
 #pragma unroll
       for (int h = 0; h < ((VT_EXP & 512) ? 1 : N); ++h) {
         const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
         lsum[h] += pv;
         const uint32_t w = ptx::f32x2_to_f16x2(pv, 0.f);  // (p, 0): the even channel of the pair
-        *reinterpret_cast<uint32_t*>(p_base + (2 * h) * 128 + ((p_chunk ^ uint32_t((2 * h) & 7)) << 4)) = w;
-        *reinterpret_cast<uint32_t*>(p_base + (2 * h + 1) * 128 + ((p_chunk ^ uint32_t((2 * h + 1) & 7)) << 4)) = w << 16;
+        ptx::sts32(p_base + (2 * h) * 128 + ((p_chunk ^ uint32_t((2 * h) & 7)) << 4), w);
+        ptx::sts32(p_base + (2 * h + 1) * 128 + ((p_chunk ^ uint32_t((2 * h + 1) & 7)) << 4), w << 16);
       }
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();

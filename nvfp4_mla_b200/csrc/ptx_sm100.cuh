@@ -72,6 +72,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// shared-memory accesses by 32-bit shared address (a generic pointer would cost an address translation per access)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 d;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "r"(addr));
+  return d;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+
 // Split form of the bounded wait, for a barrier that has usually completed by the time it is needed: mbar_probe()
 // issues the test early (its answer takes as long as any shared-memory round trip, during which the thread carries on
 // with independent work), mbar_wait_probed() consumes the answer and only polls if the test failed.
