@@ -60,7 +60,7 @@ constexpr int kVtScRing = 2;     // scale tables of whole tiles (16 KB each)
 constexpr int kVtTerms = VT_TERMS;      // E2M1 terms of the query (even: two terms share an MMA)
 constexpr int kVtPasses = kVtTerms / 2;
 static_assert(kVtTerms % 2 == 0, "terms are stacked in pairs along N");
-constexpr int kVtThreads = 512;  // 16 warps: 4 softmax, 4 K side, 4 V^T conversion, QK^T / producer / PV issue, one spare
+constexpr int kVtThreads = 640;  // 20 warps: 4 softmax, 4 K side, 8 V^T conversion, QK^T / producer / PV issue, one spare
 // raw tile of 128 tokens: packed low halves | packed high halves | block scales | rope
 constexpr int kVtRawHi = TILE * 128, kVtRawSf = 2 * TILE * 128, kVtRawKpe = kVtRawSf + TILE * 32;
 constexpr int kVtRawTileBytes = TILE * TOKEN_BYTES;
@@ -487,7 +487,7 @@ struct VtUnitRegs {
   uint32_t rw[4];
   uint4 sa[2], sb[2];  // (s, s) of the unit's two blocks: 8 tokens each (4q .. 4q + 3 of both 16-token halves)
 };
-__device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int n_segs, uint32_t& it) {
+__device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int n_segs, uint32_t& it, const uint32_t vw) {
   const int lane = ptx::lane_id();
   const int quad = (threadIdx.x >> 5) & 3;
   const int q = lane & 3;
@@ -495,57 +495,27 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   const uint32_t tm_q = s.tmem_base + (uint32_t(32 * quad) << 16);
   int total = 0;
   for (int si = 0; si < n_segs; ++si) total += s.segs[si].ntiles > 0 ? s.segs[si].ntiles : 0;
-  if (total == 0) return;
-  const uint32_t n_groups = 4u * uint32_t(total);
   // per-lane constants: byte offset of this lane's ldmatrix row inside a 32-token group, swizzle term
   const uint32_t row_off = uint32_t(16 * mat + mrow) * 128, swz = uint32_t(mrow & 7);
   uint32_t raw_base = 0, sc_base = 0;  // of the tile whose loads are being issued
-  // tile `tile`: waits for its scale table and raw bytes; false if a wait gave up
-  auto open_tile = [&](uint32_t tile) -> bool {
-    const uint32_t slot = tile % kVtRawSlots, ts = tile % kVtScRing;
-    bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag));
-    ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
-    raw_base = ptx::smem_u32(s.raw[slot]) + row_off;
-    sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 32 * q;
-    if (quad == 0) VT_EV(11, tile);
-    return __all_sync(~0u, ok);
-  };
-  // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scale byte pairs of each of its 2 blocks x 8 tokens
+  // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scales of each of its 2 blocks x 8 tokens
   auto load_unit = [&](uint32_t qt, int mb, int ch, VtUnitRegs& R) {
     const uint32_t chunk = 2 * quad + ch;
-#if VT_DBG & 32
-    VT_T(tl0_);
+#if VT_EXP & 1024
+    for (int i = 0; i < 4; ++i) R.rw[i] = chunk + qt + i;
+    R.sa[0] = R.sa[1] = R.sb[0] = R.sb[1] = make_uint4(qt, mb, ch, chunk);
+    return;
 #endif
     ptx::ldmatrix_x2_trans_b8(raw_base + qt * (32 * 128) + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
-#if VT_DBG & 32
-    asm volatile("mov.b32 %0, %0;" : "+r"(R.rw[0]));
-    VT_T(tl1_);
-    VT_ACC(4, tl0_, tl1_);
-#endif
     const uint32_t a = sc_base + qt * 4096 + (16 * mb + 2 * chunk) * 128;  // block row of the table: [4 q][2 halves][4 tokens] words
-    auto lds = [](uint4& d, uint32_t addr) {
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "r"(addr));
-    };
-    lds(R.sa[0], a), lds(R.sa[1], a + 16), lds(R.sb[0], a + 128), lds(R.sb[1], a + 144);
+    R.sa[0] = ptx::lds128(a), R.sa[1] = ptx::lds128(a + 16), R.sb[0] = ptx::lds128(a + 128), R.sb[1] = ptx::lds128(a + 144);
   };
-  uint32_t pending = ~0u;  // half of the V^T ring stored but not yet published
-  auto publish_pending = [&]() {
-    if (pending != ~0u) {
-      VT_WAIT(3, (ptx::tmem_wait_st(), true));
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.vt_full[pending]);
-      pending = ~0u;
-    }
-  };
-  // arithmetic and store of unit (mb, ch) of group g, whose loads are in R; false if a wait gave up
-  auto finish_unit = [&](uint32_t g, int mb, int ch, const VtUnitRegs& R) -> bool {
-    const uint32_t tile = it + (g >> 2), qt = g & 3, sl = 2 * qt + mb;
-    const bool new_half = mb == 0 && ch == 0 && (qt & 1) == 0;
-    // PV must have released this half of the ring (the previous tile's): the test is issued now, its answer used after the arithmetic
-    uint32_t probed = 0;
-    if (new_half) probed = ptx::mbar_probe(&s.vt_free[qt >> 1], (tile & 1) ^ 1);
-    uint32_t v[16];
+  // arithmetic and store of unit (mb, ch) of group qt, whose loads are in R
+  auto finish_unit = [&](uint32_t qt, int mb, int ch, const VtUnitRegs& R, uint32_t (&v)[16]) {
+#if VT_EXP & 2
+    for (int i = 0; i < 4; ++i) v[i] = R.rw[i], v[4 + i] = (&R.sa[0].x)[i], v[8 + i] = (&R.sb[0].x)[i], v[12 + i] = (&R.sa[1].x)[i] ^ (&R.sb[1].x)[i];
+    return;
+#endif
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
@@ -558,59 +528,69 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
         v[8 * tg + 2 * i + 1] = ptx::hmul2(eb[i], pb[i]);
       }
     }
-    if (mb == 0 && ch == 0) publish_pending();  // the previous half, if this group is the first after it
-    if (new_half) {
-      const bool ok = VT_WAIT(2, ptx::mbar_wait_probed(probed, &s.vt_free[qt >> 1], (tile & 1) ^ 1, &s.abort_flag));
-      ptx::tc_fence_after_sync();
-      if (!__all_sync(~0u, ok)) return false;
-      if (quad == 0 && qt == 0) VT_EV(12, tile);
-      if (quad == 0 && qt == 2) VT_EV(13, tile);
-    }
+  };
+  auto store_unit = [&](uint32_t qt, int mb, int ch, const uint32_t (&v)[16]) {
 #if VT_EXP & 1
-    {
-      uint32_t x = 0;
-      for (int i = 0; i < 16; ++i) x ^= v[i];
-      if (x == 0x12345678u) s.abort_flag = 2;  // keeps the arithmetic alive
-    }
+    uint32_t x = 0;
+    for (int i = 0; i < 16; ++i) x ^= v[i];
+    if (x == 0x12345678u) s.abort_flag = 2;  // keeps the values alive
 #else
-    ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(sl), v);
+    ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(2 * qt + mb), v);
 #endif
-    return true;
   };
   VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
-  if (!open_tile(it)) return;
-  load_unit(0, 0, 0, ra);
 #pragma unroll 1
-  for (uint32_t g = 0; g < n_groups; ++g) {
-    const uint32_t qt = g & 3, tile = it + (g >> 2);
-    load_unit(qt, 0, 1, rb);
-    if (!finish_unit(g, 0, 0, ra)) return;
-    load_unit(qt, 1, 0, ra);
-    if (!finish_unit(g, 0, 1, rb)) return;
-    load_unit(qt, 1, 1, rb);
-    if (!finish_unit(g, 1, 0, ra)) return;
-    if (qt == 3) {
-      // the last loads of the tile have been issued: the next tile's inputs, then its first loads
-      if (g + 1 < n_groups) {
-        if (!open_tile(tile + 1)) return;
-        load_unit(0, 0, 0, ra);
-      }
-    } else {
-      load_unit(qt + 1, 0, 0, ra);
+  for (int tl = 0; tl < total; ++tl) {
+    const uint32_t tile = it + uint32_t(tl);
+    const uint32_t slot = tile % kVtRawSlots, ts = tile % kVtScRing;
+    {  // the tile's scale table and raw bytes
+      bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag));
+      ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
+      if (!__all_sync(~0u, ok)) return;
     }
-    if (!finish_unit(g, 1, 1, rb)) return;
-    if (qt & 1) pending = qt >> 1;
-    if (qt == 3) {
-      // every input of the tile is in a register or stored: release the table and this warp's share of the raw slot
-      __syncwarp();
-      if (lane == 0) {
-        ptx::mbar_arrive(&s.sc_free[tile % kVtScRing]);
-        ptx::mbar_arrive(&s.raw_empty[tile % kVtRawSlots]);
+    // PV must have released this half of the ring (the previous tile's): the test is issued now, its answer used after
+    // the first unit's arithmetic
+    const uint32_t probed = ptx::mbar_probe(&s.vt_free[vw], (tile & 1) ^ 1);
+    raw_base = ptx::smem_u32(s.raw[slot]) + row_off;
+    sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 32 * q;
+    if (quad == 0 && vw == 0) VT_EV(11, tile);
+    load_unit(2 * vw, 0, 0, ra);
+#pragma unroll 1
+    for (uint32_t gi = 0; gi < 2; ++gi) {
+      const uint32_t qt = 2 * vw + gi;
+      uint32_t v[16];
+      load_unit(qt, 0, 1, rb);
+      finish_unit(qt, 0, 0, ra, v);
+      if (gi == 0) {
+        const bool ok = VT_WAIT(2, ptx::mbar_wait_probed(probed, &s.vt_free[vw], (tile & 1) ^ 1, &s.abort_flag));
+        ptx::tc_fence_after_sync();
+        if (!__all_sync(~0u, ok)) return;
+        if (quad == 0 && vw == 0) VT_EV(12, tile);
       }
-      if (quad == 0) VT_EV(14, tile);
+      store_unit(qt, 0, 0, v);
+      load_unit(qt, 1, 0, ra);
+      finish_unit(qt, 0, 1, rb, v);
+      store_unit(qt, 0, 1, v);
+      load_unit(qt, 1, 1, rb);
+      finish_unit(qt, 1, 0, ra, v);
+      store_unit(qt, 1, 0, v);
+      if (gi == 0) load_unit(qt + 1, 0, 0, ra);
+      finish_unit(qt, 1, 1, rb, v);
+      store_unit(qt, 1, 1, v);
     }
+    // every input of the half is in a register or stored: release the table and this warp's share of the raw slot, then
+    // hand the half to the PV warp once the stores have landed
+    __syncwarp();
+    if (lane == 0) {
+      ptx::mbar_arrive(&s.sc_free[ts]);
+      ptx::mbar_arrive(&s.raw_empty[slot]);
+    }
+    VT_WAIT(3, (ptx::tmem_wait_st(), true));
+    ptx::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&s.vt_full[vw]);
+    if (quad == 0 && vw == 1) VT_EV(14, tile);
   }
-  publish_pending();
   it += uint32_t(total);
 }
 
@@ -894,7 +874,7 @@ __device__ __forceinline__ void vt_run_role(VtSmem& s, const DecodeParams& P, co
     __syncthreads();
     if (ROLE == kVtSoftmax) vt_softmax_role(s, P, n_segs, it, seg_count);
     if (ROLE == kVtK) vt_k_role(s, P, n_segs, it, seg_count);
-    if (ROLE == kVtV) vt_v_role(s, P, n_segs, it);
+    if (ROLE == kVtV) vt_v_role(s, P, n_segs, it, (uint32_t(threadIdx.x) >> 7) - 2);
     if (ROLE == kVtQk) vt_qk_role(s, P, n_segs, it);
     if (ROLE == kVtProducer) vt_producer_role(s, P, ckv_map, sf_map, kpe_map, n_segs, it);
     if (ROLE == kVtPv) vt_pv_role(s, P, n_segs, it);
@@ -911,9 +891,9 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   const int warp = threadIdx.x >> 5;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kVtRawSlots; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 9);  // 4 K + 4 V warps + QK^T
+    for (int i = 0; i < kVtRawSlots; ++i) ptx::mbar_init(&s.raw_full[i], 1), ptx::mbar_init(&s.raw_empty[i], 13);  // 4 K + 8 V warps + QK^T
     for (int i = 0; i < 2; ++i) ptx::mbar_init(&s.vt_full[i], 4), ptx::mbar_init(&s.vt_free[i], 1);
-    for (int i = 0; i < kVtScRing; ++i) ptx::mbar_init(&s.sc_full[i], 4), ptx::mbar_init(&s.sc_free[i], 4);
+    for (int i = 0; i < kVtScRing; ++i) ptx::mbar_init(&s.sc_full[i], 4), ptx::mbar_init(&s.sc_free[i], 8);
     ptx::mbar_init(&s.rope_free, 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&s.k_full[i], 4), ptx::mbar_init(&s.k_free[i], 1);
@@ -924,7 +904,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&ckv_map), ptx::prefetch_tensormap(&sf_map), ptx::prefetch_tensormap(&kpe_map);
   }
-  if (warp == 12) {
+  if (warp == 16) {
     ptx::tmem_alloc(&s.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -939,22 +919,23 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   __syncthreads();
   const long long prof_t0 = clock64();
 #endif
-  // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 16 warps x 128.
-  constexpr int kSoftmaxRegs = 168, kKRegs = 152, kVRegs = 128;
-  static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 4 * kVRegs + 4 * 64 <= 16 * 128, "register budgets exceed the CTA's allocation");
+  // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
+  // what they were launched with.
+  constexpr int kSoftmaxRegs = 136, kKRegs = 112, kVRegs = 96, kMiscRegs = 40;
+  static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 8 * kVRegs + 4 * kMiscRegs <= 20 * 96, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
     ptx::reg_alloc<kSoftmaxRegs>();
     vt_run_role<kVtSoftmax>(s, P, &ckv_map, &sf_map, &kpe_map);
   } else if (warp < 8) {
     ptx::reg_alloc<kKRegs>();
     vt_run_role<kVtK>(s, P, &ckv_map, &sf_map, &kpe_map);
-  } else if (warp < 12) {
+  } else if (warp < 16) {
     vt_run_role<kVtV>(s, P, &ckv_map, &sf_map, &kpe_map);
   } else {
-    ptx::reg_dealloc<64>();
-    if (warp == 12) vt_run_role<kVtQk>(s, P, &ckv_map, &sf_map, &kpe_map);
-    else if (warp == 13) vt_run_role<kVtProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
-    else if (warp == 14) vt_run_role<kVtPv>(s, P, &ckv_map, &sf_map, &kpe_map);
+    ptx::reg_dealloc<kMiscRegs>();
+    if (warp == 16) vt_run_role<kVtQk>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 17) vt_run_role<kVtProducer>(s, P, &ckv_map, &sf_map, &kpe_map);
+    else if (warp == 18) vt_run_role<kVtPv>(s, P, &ckv_map, &sf_map, &kpe_map);
     else vt_run_role<kVtIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
   }
 
@@ -966,7 +947,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 #ifdef MLA_VT_PROF
   if (blockIdx.x == 1 && threadIdx.x < 160 && vt_prof_ptr) vt_prof_ptr[threadIdx.x] = reinterpret_cast<long long*>(s.prof)[threadIdx.x];
 #endif
-  if (warp == 12) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
+  if (warp == 16) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }
 
