@@ -630,13 +630,8 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
         for (int ks = 0; ks < 4; ++ks)  // rope: 64 channels as FP16 from tensor memory, into the columns of the even terms
           ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::KROPE + 8 * ks, qrope_desc + ((ks * 32) >> 4), idesc16, 1);
         ptx::mma_commit(&s.rope_free);
-#pragma unroll
-        for (int a = 1; a < 8; ++a) fp4(0, a, 1);
 #pragma unroll 1
-        for (int pp = 1; pp < ((VT_EXP & 128) ? 1 : kVtPasses); ++pp) {
-#pragma unroll
-          for (int a = 0; a < 8; ++a) fp4(pp, a, 1);
-        }
+        for (int a = 1; a < 8 * ((VT_EXP & 128) ? 1 : kVtPasses); ++a) fp4(a >> 3, a & 7, 1);  // (rolled: issue is not the bound, code size is)
         VT_T(tq1_);
         VT_ACC(4, tq0_, tq1_);
         ptx::mma_commit(&s.k_free[buf]);
@@ -666,7 +661,7 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
         ptx::tc_fence_after_sync();
         VT_T(tp0_);
         if (leader) {
-#pragma unroll
+#pragma unroll 1
           for (int k = 0; k < ((VT_EXP & 64) ? 0 : 4); ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
             const int sl = 4 * hf + k;
             const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
