@@ -361,6 +361,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return false;
   const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
   if (quad == 0) VT_EV(2, it);
+  // tests of the barriers needed further down, issued before the work that precedes them
+  const uint32_t pr_kfree = ptx::mbar_probe(&s.k_free[buf], ((it >> 1) & 1) ^ 1), pr_rope = ptx::mbar_probe(&s.rope_free, (it & 1) ^ 1);
 
   // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs
   uint32_t h[32];
@@ -394,8 +396,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
     f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
   }
   // QK^T of tile it - 2 must have finished with this scale-factor buffer, the rope MMAs of tile it - 1 with rope K
-  bool ok = VT_WAIT(1, ptx::mbar_wait(&s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag));
-  ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.rope_free, (it & 1) ^ 1, &s.abort_flag));
+  bool ok = VT_WAIT(1, ptx::mbar_wait_probed(pr_kfree, &s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag));
+  ok = ok && VT_WAIT(1, ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag));
   ptx::tc_fence_after_sync();
   if (!__all_sync(~0u, ok)) return false;
   ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
@@ -608,11 +610,16 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1, slot = it % kVtRawSlots;
-      // softmax of tile it - 2 must have read this S^T buffer
-      if (!__all_sync(~0u, it < 2 || VT_WAIT(0, ptx::mbar_wait(&s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag)))) return;
-      // the packed bytes (this thread's MMAs read them through the async proxy) and the K side in tensor memory
-      if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return;
-      if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.k_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
+      // softmax of tile it - 2 must have read this S^T buffer; the packed bytes (this thread's MMAs read them through
+      // the async proxy) and the K side in tensor memory must be there. The three tests are issued together.
+      {
+        const uint32_t p0 = ptx::mbar_probe(&s.s_free[buf], ((it >> 1) - 1) & 1), p1 = ptx::mbar_probe(&s.raw_full[slot], (it / kVtRawSlots) & 1),
+                       p2 = ptx::mbar_probe(&s.k_full[buf], (it >> 1) & 1);
+        bool ok = it < 2 || VT_WAIT(0, ptx::mbar_wait_probed(p0, &s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
+        ok = ok && VT_WAIT(2, ptx::mbar_wait_probed(p1, &s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag));
+        ok = ok && VT_WAIT(1, ptx::mbar_wait_probed(p2, &s.k_full[buf], (it >> 1) & 1, &s.abort_flag));
+        if (!__all_sync(~0u, ok)) return;
+      }
       ptx::tc_fence_after_sync();
       VT_EV(4, it);
       VT_T(tq0_);
@@ -916,7 +923,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 #endif
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
-  constexpr int kSoftmaxRegs = 136, kKRegs = 112, kVRegs = 96, kMiscRegs = 40;
+  constexpr int kSoftmaxRegs = 128, kKRegs = 112, kVRegs = 96, kMiscRegs = 48;
   static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 8 * kVRegs + 4 * kMiscRegs <= 20 * 96, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
     ptx::reg_alloc<kSoftmaxRegs>();
