@@ -295,7 +295,7 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
 
   mla::DecodeParams P;
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
-  P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
+  P.ckv = ckv_cache, P.sf = ckv_sf_cache, P.kpe = kpe_cache, P.page_table = page_table, P.pt_stride = page_table_stride;
   P.page_shift = __builtin_ctz(unsigned(page_size)), P.num_pages = int(num_pages), P.heads = heads, P.heads_per_cta = hpc;
   P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;

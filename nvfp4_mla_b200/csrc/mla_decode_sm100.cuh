@@ -47,6 +47,7 @@ constexpr int kTmemCols = 512;
 struct DecodeParams {
   const __nv_bfloat16* q_nope;
   const __nv_bfloat16* q_pe;
+  const uint8_t* ckv;
   const uint8_t* sf;
   const uint8_t* kpe;
   const int* page_table;

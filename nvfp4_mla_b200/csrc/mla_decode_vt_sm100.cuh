@@ -68,15 +68,19 @@ static_assert(kVtRawTileBytes % 1024 == 0, "raw tile alignment");
 
 #ifdef MLA_VT_PROF  // development builds: cycles spent in each kind of wait, per warp of one CTA
 __device__ long long* vt_prof_ptr;
+__device__ __forceinline__ uint32_t vt_clock() { uint32_t c; asm volatile("mov.u32 %0, %%clock;" : "=r"(c)); return c; }
+__device__ __forceinline__ void vt_prof_add(uint32_t* p, uint32_t v) {
+  if ((threadIdx.x & 31) == 0) asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(ptx::smem_u32(p)), "r"(v) : "memory");
+}
 #define VT_WAIT(slot, expr)                                                                        \
   ([&] {                                                                                           \
-    const long long t0_ = clock64();                                                               \
+    const uint32_t t0_ = vt_clock();                                                               \
     const bool r_ = (expr);                                                                        \
-    if ((threadIdx.x & 31) == 0) s.prof[threadIdx.x >> 5][slot] += clock64() - t0_;                \
+    vt_prof_add(&s.prof[threadIdx.x >> 5][slot], vt_clock() - t0_);                                \
     return r_;                                                                                     \
   }())
-#define VT_T(var) const long long var = clock64()
-#define VT_ACC(slot, a, b) do { if ((threadIdx.x & 31) == 0) s.prof[threadIdx.x >> 5][slot] += (b) - (a); } while (0)
+#define VT_T(var) const uint32_t var = vt_clock()
+#define VT_ACC(slot, a, b) vt_prof_add(&s.prof[threadIdx.x >> 5][slot], (b) - (a))
 #else
 #define VT_WAIT(slot, expr) (expr)
 #define VT_T(var) do {} while (0)
@@ -136,7 +140,7 @@ struct VtSmem {
   uint32_t tmem_base;
   int abort_flag;
 #ifdef MLA_VT_PROF
-  long long prof[20][8];
+  uint32_t prof[20][8];
 #endif
 };
 constexpr size_t vt_smem_bytes() { return sizeof(VtSmem) + 1024; }
@@ -174,21 +178,27 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
       nvalid = nvalid < 0 ? 0 : (nvalid > TILE ? TILE : nvalid);
       const int page[2] = {page_nx[0], page_nx[1]}, page_pf[2] = {pf_nx[0], pf_nx[1]};
       if (t + 1 < seg.ntiles) fetch_ids(tok + TILE, page_nx, pf_nx);
-      if (ps >= HALF && lane == 0) {  // the prefetches do not need the slot: issued before the wait for it
+      if (ps >= HALF) {
+        // The pages of the tile three ahead, into L2, by plain prefetch instructions of all lanes: a tensor-map prefetch
+        // costs the TMA unit as much as the load itself (it walks the box row by row), and the TMA unit is what
+        // bounds this warp. A page's 64 tokens are contiguous in each of the three arrays. Not waiting for the slot.
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if (uint32_t(page_pf[h]) < uint32_t(P.num_pages)) {
-            const int row2 = (page_pf[h] << P.page_shift) + ((tok + h * HALF + 3 * TILE) & (ps - 1));
-            ptx::tma_prefetch_l2_2d(ckv_map, 0, row2);
-            ptx::tma_prefetch_l2_2d(ckv_map, 128, row2);
-            ptx::tma_prefetch_l2_2d(sf_map, 0, row2);
-            ptx::tma_prefetch_l2_2d(kpe_map, 0, row2);
+          const int pf = __shfl_sync(~0u, page_pf[h], 0);
+          if (uint32_t(pf) < uint32_t(P.num_pages)) {
+            const long long row2 = ((long long)pf << P.page_shift) + ((tok + h * HALF + 3 * TILE) & (ps - 1));
+            const uint8_t* c = P.ckv + row2 * 256 + lane * 128;  // 16 KB = 128 lines
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ptx::prefetch_l2(c + k * 4096);
+            ptx::prefetch_l2(P.kpe + row2 * 64 + lane * 128);    // 4 KB = 32 lines
+            if (lane < 16) ptx::prefetch_l2(P.sf + row2 * 32 + lane * 128);  // 2 KB = 16 lines
           }
         }
       }
-      const bool ok = ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag);
+      const bool ok = VT_WAIT(0, ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag));
       if (!__all_sync(~0u, ok)) return;
       VT_EV(0, it);
+      VT_T(tpr0_);
       uint8_t* dst = s.raw[slot];
       uint64_t* bar = &s.raw_full[slot];
       if (nvalid == 0) {
@@ -206,8 +216,15 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
             const int row = bad ? (P.num_pages << P.page_shift) : (page[h] << P.page_shift) + (tk & (ps - 1));
             ptx::tma_load_2d(dst + h * HALF * 128, ckv_map, 0, row, bar);
             ptx::tma_load_2d(dst + kVtRawHi + h * HALF * 128, ckv_map, 128, row, bar);
-            ptx::tma_load_2d(dst + kVtRawSf + h * HALF * 32, sf_map, 0, row, bar);
-            ptx::tma_load_2d(dst + kVtRawKpe + h * HALF * 64, kpe_map, 0, row, bar);
+            if (!bad) {
+              // scales and rope: the half tile's rows are contiguous, one linear copy each (a tiled copy costs the TMA
+              // unit one request per ROW, however short the row)
+              ptx::bulk_load(dst + kVtRawSf + h * HALF * 32, P.sf + (long long)row * 32, HALF * 32, bar);
+              ptx::bulk_load(dst + kVtRawKpe + h * HALF * 64, P.kpe + (long long)row * 64, HALF * 64, bar);
+            } else {
+              ptx::tma_load_2d(dst + kVtRawSf + h * HALF * 32, sf_map, 0, row, bar);  // zeros (in any layout)
+              ptx::tma_load_2d(dst + kVtRawKpe + h * HALF * 64, kpe_map, 0, row, bar);
+            }
           }
         }
       } else {
@@ -241,6 +258,8 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
         }
       }
       __syncwarp();
+      VT_T(tpr1_);
+      VT_ACC(4, tpr0_, tpr1_);
       VT_EV(1, it);
     }
   }
@@ -367,7 +386,7 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs
   uint32_t h[32];
   {
-    const uint32_t x = (uint32_t(r) >> 1) & P.kpe_swz_mask;
+    const uint32_t x = 0;  // (rows arrive unswizzled)
 #if VT_EXP & 256
     for (int c = 0; c < 32; ++c) h[c] = c + r;
 #endif
@@ -390,7 +409,7 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
 #pragma unroll
   for (int j = 0; j < ((VT_EXP & 256) ? 0 : 4); ++j) {
     const int tk = 32 * j + lane;
-    const uint32_t x = (uint32_t(tk) >> 2) & P.sf_swz_mask;
+    const uint32_t x = 0;
     const uint4 a = ptx::lds128(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
     const uint4 b = ptx::lds128(raw + kVtRawSf + tk * 32 + ((1u ^ x) << 4));
     f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
@@ -411,7 +430,7 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   // beyond the request's end. Written last: the V warps are the furthest behind of all readers of the tile, and the wait
   // for a free table must not hold up QK^T.
   {
-    const uint32_t x = (uint32_t(r) >> 2) & P.sf_swz_mask;
+    const uint32_t x = 0;
     const uint4 a = ptx::lds128(raw + kVtRawSf + r * 32 + ((0u ^ x) << 4));
     const uint4 b = ptx::lds128(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -917,9 +936,9 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::grid_launch_dependents();
 
 #ifdef MLA_VT_PROF
-  if (threadIdx.x < 160) reinterpret_cast<long long*>(s.prof)[threadIdx.x] = 0;
+  if (threadIdx.x < 160) (&s.prof[0][0])[threadIdx.x] = 0;
   __syncthreads();
-  const long long prof_t0 = clock64();
+  const uint32_t prof_t0 = vt_clock();
 #endif
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
@@ -942,12 +961,12 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   }
 
 #ifdef MLA_VT_PROF
-  if ((threadIdx.x & 31) == 0) s.prof[warp][7] = clock64() - prof_t0;
+  if ((threadIdx.x & 31) == 0) s.prof[warp][7] = vt_clock() - prof_t0;
 #endif
   ptx::tc_fence_before_sync();
   __syncthreads();
 #ifdef MLA_VT_PROF
-  if (blockIdx.x == 1 && threadIdx.x < 160 && vt_prof_ptr) vt_prof_ptr[threadIdx.x] = reinterpret_cast<long long*>(s.prof)[threadIdx.x];
+  if (blockIdx.x == 1 && threadIdx.x < 160 && vt_prof_ptr) vt_prof_ptr[threadIdx.x] = (&s.prof[0][0])[threadIdx.x];
 #endif
   if (warp == 16) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
