@@ -125,7 +125,7 @@ struct VtSmem {
   alignas(16) uint32_t sc[kVtScRing][4][32][32];    // block scales as FP16 pairs (s, s): [tile][quarter][block][token slot], the slot
                                                     // of token 16 h + 4 q + i of the quarter being 8 q + 4 h + i
   Seg segs[kSegBatch];
-  float qa[4][16];                                  // per-head score scale, ring indexed by segment count
+  alignas(16) float qa[4][16];                      // per-head score scale, ring indexed by segment count
   float red[4][16];
   float corr[16];
   uint32_t sfb[kVtTerms][16];                       // scale word of (term, head) on its way to tensor memory
@@ -178,7 +178,7 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
       nvalid = nvalid < 0 ? 0 : (nvalid > TILE ? TILE : nvalid);
       const int page[2] = {page_nx[0], page_nx[1]}, page_pf[2] = {pf_nx[0], pf_nx[1]};
       if (t + 1 < seg.ntiles) fetch_ids(tok + TILE, page_nx, pf_nx);
-      if (ps >= HALF) {
+      if (ps >= HALF && !(VT_EXP & 4096)) {
         // The pages of the tile three ahead, into L2, by plain prefetch instructions of all lanes: a tensor-map prefetch
         // costs the TMA unit as much as the load itself (it walks the box row by row), and the TMA unit is what
         // bounds this warp. A page's 64 tokens are contiguous in each of the three arrays. Not waiting for the slot.
@@ -201,8 +201,8 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
       VT_T(tpr0_);
       uint8_t* dst = s.raw[slot];
       uint64_t* bar = &s.raw_full[slot];
-      if (nvalid == 0) {
-        if (lane == 0) ptx::mbar_arrive(bar);
+      if (nvalid == 0 || (VT_EXP & 2048)) {
+        ptx::mbar_arrive_if(bar, lane == 0);
       } else if (ps >= HALF) {
         if (lane == 0) {
           const int nh = nvalid > HALF ? 2 : 1;  // half tiles that hold a live token
@@ -419,12 +419,16 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   ok = ok && VT_WAIT(1, ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag));
   ptx::tc_fence_after_sync();
   if (!__all_sync(~0u, ok)) return false;
+#if !(VT_EXP & 8192)
   ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
   ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
+#else
+  if ((h[0] ^ f[0] ^ h[31] ^ f[31]) == 0x12345u) s.abort_flag = 2;
+#endif
   VT_WAIT(3, (ptx::tmem_wait_st(), true));
   ptx::tc_fence_before_sync();
   __syncwarp();
-  if (lane == 0) ptx::mbar_arrive(&s.k_full[buf]);
+  ptx::mbar_arrive_if(&s.k_full[buf], lane == 0);
   if (quad == 0) VT_EV(3, it);
   // ---- block scales of this token for the V warps, as FP16 pairs (s, s) ready to be multiplied with a converted byte; 0
   // beyond the request's end. Written last: the V warps are the furthest behind of all readers of the tile, and the wait
@@ -446,10 +450,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
       ptx::sts32(dst + (4 * j + 2) * 128, __byte_perm(hi, 0, 0x1010)), ptx::sts32(dst + (4 * j + 3) * 128, __byte_perm(hi, 0, 0x3232));
     }
     __syncwarp();
-    if (lane == 0) {
-      ptx::mbar_arrive(&s.sc_full[qs]);
-      ptx::mbar_arrive(&s.raw_empty[slot]);  // every byte this warp needs from the raw tile is in a register or stored
-    }
+    ptx::mbar_arrive_if(&s.sc_full[qs], lane == 0);
+    ptx::mbar_arrive_if(&s.raw_empty[slot], lane == 0);  // every byte this warp needs from the raw tile is in a register or stored
   }
   return true;
 }
@@ -602,14 +604,12 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     // every input of the half is in a register or stored: release the table and this warp's share of the raw slot, then
     // hand the half to the PV warp once the stores have landed
     __syncwarp();
-    if (lane == 0) {
-      ptx::mbar_arrive(&s.sc_free[ts]);
-      ptx::mbar_arrive(&s.raw_empty[slot]);
-    }
+    ptx::mbar_arrive_if(&s.sc_free[ts], lane == 0);
+    ptx::mbar_arrive_if(&s.raw_empty[slot], lane == 0);
     VT_WAIT(3, (ptx::tmem_wait_st(), true));
     ptx::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.vt_full[vw]);
+    ptx::mbar_arrive_if(&s.vt_full[vw], lane == 0);
     if (quad == 0 && vw == 1) VT_EV(14, tile);
   }
   it += uint32_t(total);
@@ -729,28 +729,38 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
     if (seg.ntiles <= 0) continue;
     const int par_q = seg_count & 3;
     ++seg_count;
+    // running maximum and sum per head. The maximum starts at a finite sentinel far below any score rather than at
+    // -inf: x - m and m - m' then never meet inf - inf, and no special case is needed anywhere below.
+    constexpr float kNoMax = -1e30f;
     float m[N], lsum[N];
 #pragma unroll
-    for (int h = 0; h < N; ++h) m[h] = -INFINITY, lsum[h] = 0.f;
-    bool scales_loaded = false;
-    float qa_r[N];
+    for (int h = 0; h < N; ++h) m[h] = kNoMax, lsum[h] = 0.f;
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
       const bool ok = VT_WAIT(0, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
       ptx::tc_fence_after_sync();
       if (warp == 0) VT_EV(6, it);
+      VT_T(ts0_);
       float x[N];
-      if (!scales_loaded) {  // written by the K warps before the segment's first K chunk was published
+      float qa_r[N];  // per-head score scales, written by the K warps before the segment's first K side was published
+      {
+        const uint32_t qa_addr = ptx::smem_u32(&s.qa[par_q][0]);
 #pragma unroll
-        for (int h = 0; h < N; ++h) qa_r[h] = s.qa[par_q][h];
-        scales_loaded = true;
+        for (int j = 0; j < N / 4; ++j) {
+          const uint4 v = ptx::lds128(qa_addr + 16 * j);
+          qa_r[4 * j] = __uint_as_float(v.x), qa_r[4 * j + 1] = __uint_as_float(v.y), qa_r[4 * j + 2] = __uint_as_float(v.z), qa_r[4 * j + 3] = __uint_as_float(v.w);
+        }
       }
       if (ok) {
         const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
         uint32_t sv[32];  // columns [0, 16): even terms + rope, [16, 32): odd terms
+#if VT_EXP & 16384
+        for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(float(i + r) * 0.01f);
+#else
         ptx::tmem_ld32(tm_lane + VtCols::s(buf), sv);
         ptx::tmem_wait_ld();
+#endif
 #pragma unroll
         for (int h = 0; h < N; ++h) x[h] = valid ? (__uint_as_float(sv[h]) + __uint_as_float(sv[16 + h])) * qa_r[h] : -INFINITY;
       } else {
@@ -759,10 +769,15 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.s_free[buf]);  // QK^T of tile it + 2 may overwrite this S^T buffer
-      bool need = !ok;
+      ptx::mbar_arrive_if(&s.s_free[buf], lane == 0);  // QK^T of tile it + 2 may overwrite this S^T buffer
+      VT_T(ts1_);
+      VT_ACC(3, ts0_, ts1_);
+      // does any score exceed its running maximum by more than the slack? (one maximum over the differences: a chain of
+      // sixteen predicate updates would be sixteen predicate latencies long; x = m = -inf gives NaN, which fmaxf drops)
+      float dmax[4];
 #pragma unroll
-      for (int h = 0; h < N; ++h) need |= x[h] > m[h] + kGrow;
+      for (int j = 0; j < 4; ++j) dmax[j] = fmaxf(fmaxf(x[j] - m[j], x[4 + j] - m[4 + j]), fmaxf(x[8 + j] - m[8 + j], x[12 + j] - m[12 + j]));
+      const bool need = !ok || fmaxf(fmaxf(dmax[0], dmax[1]), fmaxf(dmax[2], dmax[3])) > kGrow;
       if (VT_WAIT(2, ptx::bar_red_or(1, 128, need))) {
         if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
 #pragma unroll
@@ -778,7 +793,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
         for (int h = 0; h < N; ++h) {
           const float mx = fmaxf(fmaxf(s.red[0][h], s.red[1][h]), fmaxf(s.red[2][h], s.red[3][h]));
           const float mn = fmaxf(m[h], mx);
-          const float c = (m[h] == -INFINITY) ? 0.f : ptx::ex2(m[h] - mn);  // mn = -inf only if m = -inf
+          const float c = ptx::ex2(m[h] - mn);  // 0 when the first real score replaces the sentinel, 1 when nothing changes
           any_scale |= c != 1.f;
           lsum[h] *= c;
           m[h] = mn;
@@ -804,20 +819,30 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       }
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
+      VT_T(ts2_);
+      VT_ACC(4, ts1_, ts2_);
       if (it >= 2) VT_WAIT(1, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
+      VT_T(ts3_);
       const uint32_t p_base = ptx::smem_u32(s.p[buf][r >> 5]) + p_off;
+      uint32_t p_row[8];  // row n of the panel: base + 128 n + the swizzled chunk, which depends on n % 8 only
+#pragma unroll
+      for (int c = 0; c < 8; ++c) p_row[c] = p_base + ((p_chunk ^ uint32_t(c)) << 4);
 #pragma unroll
       for (int h = 0; h < ((VT_EXP & 512) ? 1 : N); ++h) {
-        const float pv = ptx::ex2(x[h] - (m[h] == -INFINITY ? 0.f : m[h]));  // x = -inf gives 0
+        const float pv = ptx::ex2(x[h] - m[h]);  // x = -inf gives 0
         lsum[h] += pv;
         const uint32_t w = ptx::f32x2_to_f16x2(pv, 0.f);  // (p, 0): the even channel of the pair
-        ptx::sts32(p_base + (2 * h) * 128 + ((p_chunk ^ uint32_t((2 * h) & 7)) << 4), w);
-        ptx::sts32(p_base + (2 * h + 1) * 128 + ((p_chunk ^ uint32_t((2 * h + 1) & 7)) << 4), w << 16);
+        ptx::sts32(p_row[(2 * h) & 7] + (2 * h) * 128, w);
+        ptx::sts32(p_row[(2 * h + 1) & 7] + (2 * h + 1) * 128, w << 16);
       }
+      VT_T(ts4_);
+      VT_ACC(5, ts3_, ts4_);
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.p_full[buf]);
+      ptx::mbar_arrive_if(&s.p_full[buf], lane == 0);
+      VT_T(ts5_);
+      VT_ACC(6, ts4_, ts5_);
       if (warp == 0) VT_EV(7, it);
     }
 
@@ -942,7 +967,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 #endif
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
-  constexpr int kSoftmaxRegs = 128, kKRegs = 112, kVRegs = 96, kMiscRegs = 48;
+  constexpr int kSoftmaxRegs = 104, kKRegs = 136, kVRegs = 96, kMiscRegs = 48;
   static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 8 * kVRegs + 4 * kMiscRegs <= 20 * 96, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
     ptx::reg_alloc<kSoftmaxRegs>();
