@@ -48,7 +48,7 @@ DeviceInfo g_devices[kMaxDevices];
 
 using DecodeKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const mla::DecodeParams);
 // staging slots of 64 tokens next to the V tile (one FP16 tile of 128 KB, or two E4M3 tiles of 64 KB)
-constexpr int kRawSlots16 = 3, kRawSlots8 = 3;
+constexpr int kRawSlots8 = 3;
 constexpr int kRawSlotsHm = 4;  // heads-as-M kernel: staging slots of 32 tokens
 // Heads per CTA (the N of both MMAs). One conversion of a tile serves all of the CTA's heads, so more heads per CTA
 // means less conversion work per head; 32 fit next to the tiles only in the 8-bit mode (tensor memory and shared memory).
@@ -67,24 +67,22 @@ DecodeKernel decode_kernel(int precision, int hpc) {
     return hpc == 128  ? mla::mla_decode_hm_kernel<kRawSlotsHm>
            : hpc == 32 ? mla::mla_decode_kernel<32, kRawSlots8, true>
                        : mla::mla_decode_kernel<16, kRawSlots8, true>;
-  if (getenv("NVFP4_MLA_OLD16")) return mla::mla_decode_kernel<16, kRawSlots16, false>;
   return mla::mla_decode_vt_kernel;
 }
 unsigned decode_threads(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8) return hpc == 128 ? mla::kHmThreads : mla::kDecodeThreads;
-  return getenv("NVFP4_MLA_OLD16") ? mla::kDecodeThreads : mla::kVtThreads;
+  return mla::kVtThreads;
 }
 size_t decode_smem(int precision, int hpc) {
   if (precision == NVFP4_MLA_PRECISION_FP8)
     return hpc == 128  ? mla::hm_smem_bytes<kRawSlotsHm>()
            : hpc == 32 ? mla::decode_smem_bytes<32, kRawSlots8, true>()
                        : mla::decode_smem_bytes<16, kRawSlots8, true>();
-  if (getenv("NVFP4_MLA_OLD16")) return mla::decode_smem_bytes<16, kRawSlots16, false>();
   return mla::vt_smem_bytes();
 }
 static_assert(mla::hm_smem_bytes<kRawSlotsHm>() <= 232448, "heads-as-M kernel exceeds the shared memory a CTA can opt in to");
 static_assert(mla::decode_smem_bytes<32, kRawSlots8, true>() <= 232448 && mla::decode_smem_bytes<16, kRawSlots8, true>() <= 232448 &&
-                  mla::decode_smem_bytes<16, kRawSlots16, false>() <= 232448 && mla::vt_smem_bytes() <= 232448,
+                  mla::vt_smem_bytes() <= 232448,
               "decode kernel exceeds the 227 KB of shared memory a CTA can opt in to");
 
 // Per-device one-time setup (SM count, opt-in shared memory). Must first run outside stream capture.
@@ -212,17 +210,6 @@ int problem_of(int batch, int heads, int max_kv_len, int num_splits, int n_cta, 
 }
 
 }  // namespace
-
-#ifdef MLA_VT_TRACE
-extern "C" NVFP4_MLA_API void nvfp4_mla_set_trace(long long* device_buffer) {
-  cudaMemcpyToSymbol(mla::vt_trace_ptr, &device_buffer, sizeof(device_buffer));
-}
-#endif
-#ifdef MLA_VT_PROF
-extern "C" NVFP4_MLA_API void nvfp4_mla_set_prof(long long* device_buffer) {
-  cudaMemcpyToSymbol(mla::vt_prof_ptr, &device_buffer, sizeof(device_buffer));
-}
-#endif
 
 extern "C" {
 

@@ -45,19 +45,10 @@
 
 namespace mla {
 
-#ifndef VT_DBG
-#define VT_DBG 0
-#endif
-#ifndef VT_EXP
-#define VT_EXP 0
-#endif
 constexpr int kVtRawSlots = 3;   // raw tiles in flight
 constexpr int kVtRing = 8;       // V^T slots (32 tokens x 128 channel pairs, 32 columns): one tile
 constexpr int kVtScRing = 2;     // scale tables of whole tiles (16 KB each)
-#ifndef VT_TERMS
-#define VT_TERMS 4
-#endif
-constexpr int kVtTerms = VT_TERMS;      // E2M1 terms of the query (even: two terms share an MMA)
+constexpr int kVtTerms = 4;      // E2M1 terms of the query (even: two terms share an MMA)
 constexpr int kVtPasses = kVtTerms / 2;
 static_assert(kVtTerms % 2 == 0, "terms are stacked in pairs along N");
 constexpr int kVtThreads = 640;  // 20 warps: 4 softmax, 4 K side, 8 V^T conversion, QK^T / producer / PV issue, one spare
@@ -65,45 +56,6 @@ constexpr int kVtThreads = 640;  // 20 warps: 4 softmax, 4 K side, 8 V^T convers
 constexpr int kVtRawHi = TILE * 128, kVtRawSf = 2 * TILE * 128, kVtRawKpe = kVtRawSf + TILE * 32;
 constexpr int kVtRawTileBytes = TILE * TOKEN_BYTES;
 static_assert(kVtRawTileBytes % 1024 == 0, "raw tile alignment");
-
-#ifdef MLA_VT_PROF  // development builds: cycles spent in each kind of wait, per warp of one CTA
-__device__ long long* vt_prof_ptr;
-__device__ __forceinline__ uint32_t vt_clock() { uint32_t c; asm volatile("mov.u32 %0, %%clock;" : "=r"(c)); return c; }
-__device__ __forceinline__ void vt_prof_add(uint32_t* p, uint32_t v) {
-  if ((threadIdx.x & 31) == 0) asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(ptx::smem_u32(p)), "r"(v) : "memory");
-}
-#define VT_WAIT(slot, expr)                                                                        \
-  ([&] {                                                                                           \
-    const uint32_t t0_ = vt_clock();                                                               \
-    const bool r_ = (expr);                                                                        \
-    vt_prof_add(&s.prof[threadIdx.x >> 5][slot], vt_clock() - t0_);                                \
-    return r_;                                                                                     \
-  }())
-#define VT_T(var) const uint32_t var = vt_clock()
-#define VT_ACC(slot, a, b) vt_prof_add(&s.prof[threadIdx.x >> 5][slot], (b) - (a))
-#else
-#define VT_WAIT(slot, expr) (expr)
-#define VT_T(var) do {} while (0)
-#define VT_ACC(slot, a, b) do {} while (0)
-#endif
-#ifdef MLA_VT_TRACE  // development builds: clock stamps of pipeline events of CTA 1's tiles 8..71
-__device__ long long* vt_trace_ptr;
-#define VT_EV(ev, tile)                                                                                              \
-  do {                                                                                                               \
-    if (vt_trace_ptr && blockIdx.x == 1 && (threadIdx.x & 31) == 0 && (tile) >= 8u && (tile) < 72u)                  \
-      vt_trace_ptr[(ev) * 64 + ((tile) - 8u)] = clock64();                                                           \
-  } while (0)
-// fine-grained: point p of unit u of tile 40, V warp of quadrant 0
-#define VT_EVU(p, tile, u)                                                                                          \
-  do {                                                                                                               \
-    if (vt_trace_ptr && blockIdx.x == 1 && threadIdx.x == 256 && (tile) == 40u)                                      \
-      vt_trace_ptr[24 * 64 + (u) * 8 + (p)] = clock64();                                                             \
-  } while (0)
-#else
-#define VT_EV(ev, tile) do {} while (0)
-#define VT_EVU(p, tile, u) do {} while (0)
-#endif
-#define VT_EVG(ev, g) VT_EV(ev, (g) - 100u)
 
 struct VtCols {
   // V^T ring | rope K | scale factors of A (two tiles) | scale factors of B (four columns per pass) | S^T (two tiles) | O^T
@@ -139,9 +91,6 @@ struct VtSmem {
   uint64_t sc_full[kVtScRing], sc_free[kVtScRing];
   uint32_t tmem_base;
   int abort_flag;
-#ifdef MLA_VT_PROF
-  uint32_t prof[20][8];
-#endif
 };
 constexpr size_t vt_smem_bytes() { return sizeof(VtSmem) + 1024; }
 
@@ -178,7 +127,7 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
       nvalid = nvalid < 0 ? 0 : (nvalid > TILE ? TILE : nvalid);
       const int page[2] = {page_nx[0], page_nx[1]}, page_pf[2] = {pf_nx[0], pf_nx[1]};
       if (t + 1 < seg.ntiles) fetch_ids(tok + TILE, page_nx, pf_nx);
-      if (ps >= HALF && !(VT_EXP & 4096)) {
+      if (ps >= HALF) {
         // The pages of the tile three ahead, into L2, by plain prefetch instructions of all lanes: a tensor-map prefetch
         // costs the TMA unit as much as the load itself (it walks the box row by row), and the TMA unit is what
         // bounds this warp. A page's 64 tokens are contiguous in each of the three arrays. Not waiting for the slot.
@@ -195,13 +144,11 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
           }
         }
       }
-      const bool ok = VT_WAIT(0, ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag));
+      const bool ok = ptx::mbar_wait(&s.raw_empty[slot], ((it / kVtRawSlots) & 1) ^ 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
-      VT_EV(0, it);
-      VT_T(tpr0_);
       uint8_t* dst = s.raw[slot];
       uint64_t* bar = &s.raw_full[slot];
-      if (nvalid == 0 || (VT_EXP & 2048)) {
+      if (nvalid == 0) {
         ptx::mbar_arrive_if(bar, lane == 0);
       } else if (ps >= HALF) {
         if (lane == 0) {
@@ -258,9 +205,6 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
         }
       }
       __syncwarp();
-      VT_T(tpr1_);
-      VT_ACC(4, tpr0_, tpr1_);
-      VT_EV(1, it);
     }
   }
 }
@@ -377,9 +321,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   const int slot = it % kVtRawSlots;
   const uint32_t raw = ptx::smem_u32(s.raw[slot]);
   const uint32_t buf = it & 1;
-  if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag)))) return false;
+  if (!__all_sync(~0u, ptx::mbar_wait(&s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag))) return false;
   const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
-  if (quad == 0) VT_EV(2, it);
   // tests of the barriers needed further down, issued before the work that precedes them
   const uint32_t pr_kfree = ptx::mbar_probe(&s.k_free[buf], ((it >> 1) & 1) ^ 1), pr_rope = ptx::mbar_probe(&s.rope_free, (it & 1) ^ 1);
 
@@ -387,11 +330,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   uint32_t h[32];
   {
     const uint32_t x = 0;  // (rows arrive unswizzled)
-#if VT_EXP & 256
-    for (int c = 0; c < 32; ++c) h[c] = c + r;
-#endif
 #pragma unroll
-    for (int c = 0; c < ((VT_EXP & 256) ? 0 : 4); ++c) {
+    for (int c = 0; c < 4; ++c) {
       const uint4 v = ptx::lds128(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -403,11 +343,8 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   }
   // ---- scale factors of A: lane l of this quadrant holds, for K step a, columns 4a + j = the scale word a of token 32 j + l
   uint32_t f[32];
-#if VT_EXP & 256
-  for (int c = 0; c < 32; ++c) f[c] = 0x38383838u;
-#endif
 #pragma unroll
-  for (int j = 0; j < ((VT_EXP & 256) ? 0 : 4); ++j) {
+  for (int j = 0; j < 4; ++j) {
     const int tk = 32 * j + lane;
     const uint32_t x = 0;
     const uint4 a = ptx::lds128(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
@@ -415,21 +352,16 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
     f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
   }
   // QK^T of tile it - 2 must have finished with this scale-factor buffer, the rope MMAs of tile it - 1 with rope K
-  bool ok = VT_WAIT(1, ptx::mbar_wait_probed(pr_kfree, &s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag));
-  ok = ok && VT_WAIT(1, ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag));
+  bool ok = ptx::mbar_wait_probed(pr_kfree, &s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag);
+  ok = ok && ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag);
   ptx::tc_fence_after_sync();
   if (!__all_sync(~0u, ok)) return false;
-#if !(VT_EXP & 8192)
   ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
   ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
-#else
-  if ((h[0] ^ f[0] ^ h[31] ^ f[31]) == 0x12345u) s.abort_flag = 2;
-#endif
-  VT_WAIT(3, (ptx::tmem_wait_st(), true));
+  ptx::tmem_wait_st();
   ptx::tc_fence_before_sync();
   __syncwarp();
   ptx::mbar_arrive_if(&s.k_full[buf], lane == 0);
-  if (quad == 0) VT_EV(3, it);
   // ---- block scales of this token for the V warps, as FP16 pairs (s, s) ready to be multiplied with a converted byte; 0
   // beyond the request's end. Written last: the V warps are the furthest behind of all readers of the tile, and the wait
   // for a free table must not hold up QK^T.
@@ -439,11 +371,11 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
     const uint4 b = ptx::lds128(raw + kVtRawSf + r * 32 + ((1u ^ x) << 4));
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     const uint32_t qs = it % kVtScRing;  // the tile's table; this warp writes its quarter
-    if (!__all_sync(~0u, VT_WAIT(2, ptx::mbar_wait(&s.sc_free[qs], ((it / kVtScRing) & 1) ^ 1, &s.abort_flag)))) return false;
+    if (!__all_sync(~0u, ptx::mbar_wait(&s.sc_free[qs], ((it / kVtScRing) & 1) ^ 1, &s.abort_flag))) return false;
     // token lane = 16 h + 4 q + i of the quarter -> slot 8 q + 4 h + i
     const uint32_t dst = ptx::smem_u32(&s.sc[qs][quad][0][8 * ((lane >> 2) & 3) + 4 * (lane >> 4) + (lane & 3)]);
 #pragma unroll
-    for (int j = 0; j < ((VT_EXP & 256) ? 0 : 8); ++j) {
+    for (int j = 0; j < 8; ++j) {
       const uint32_t wj = valid ? w[j] : 0u;
       const uint32_t lo = ptx::e4m3x2_to_f16x2(uint16_t(wj & 0xFFFF)), hi = ptx::e4m3x2_to_f16x2(uint16_t(wj >> 16));
       ptx::sts32(dst + (4 * j + 0) * 128, __byte_perm(lo, 0, 0x1010)), ptx::sts32(dst + (4 * j + 1) * 128, __byte_perm(lo, 0, 0x3232));
@@ -471,20 +403,6 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
     if (ptx::bar_red_or(2, 128, !ok)) return;
     ptx::tc_fence_after_sync();
     vt_load_query(s, P, seg, quad * 32 + lane, seg_count & 3, lane, quad);
-#if defined(MLA_VT_PROF) && (VT_DBG & 8)
-    if (vt_prof_ptr && seg.b == 0 && seg.hg == 0 && seg.tok0 == 0) {  // dump the query terms, their scales and the score scales
-      ptx::bar_sync(2, 128);
-      uint32_t* out = reinterpret_cast<uint32_t*>(vt_prof_ptr) + 1024;
-      const int kt = quad * 32 + lane;
-      for (int i = kt; i < kVtTerms * 2 * 16 * 128 / 4; i += 128) out[i] = reinterpret_cast<const uint32_t*>(s.q4)[i];
-      for (int i = kt; i < kVtTerms * 16; i += 128) out[4096 + i] = (&s.sfb[0][0])[i];
-      for (int i = kt; i < 16; i += 128) out[4096 + 64 + i] = __float_as_uint(s.qa[seg_count & 3][i]);
-      uint32_t sf[16];
-      ptx::tmem_ld16(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, sf);
-      ptx::tmem_wait_ld();
-      for (int i = 0; i < 16; ++i) out[4096 + 128 + kt * 16 + i] = sf[i];
-    }
-#endif
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       if (!vt_k_step(s, P, seg, t, it, lane, quad)) {
@@ -524,21 +442,12 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
   // unit (mb, ch) of group qt of the open tile: one ldmatrix and the scales of each of its 2 blocks x 8 tokens
   auto load_unit = [&](uint32_t qt, int mb, int ch, VtUnitRegs& R) {
     const uint32_t chunk = 2 * quad + ch;
-#if VT_EXP & 1024
-    for (int i = 0; i < 4; ++i) R.rw[i] = chunk + qt + i;
-    R.sa[0] = R.sa[1] = R.sb[0] = R.sb[1] = make_uint4(qt, mb, ch, chunk);
-    return;
-#endif
     ptx::ldmatrix_x2_trans_b8(raw_base + qt * (32 * 128) + mb * kVtRawHi + ((chunk ^ swz) << 4), R.rw);
     const uint32_t a = sc_base + qt * 4096 + (16 * mb + 2 * chunk) * 128;  // block row of the table: [4 q][2 halves][4 tokens] words
     R.sa[0] = ptx::lds128(a), R.sa[1] = ptx::lds128(a + 16), R.sb[0] = ptx::lds128(a + 128), R.sb[1] = ptx::lds128(a + 144);
   };
   // arithmetic and store of unit (mb, ch) of group qt, whose loads are in R
   auto finish_unit = [&](uint32_t qt, int mb, int ch, const VtUnitRegs& R, uint32_t (&v)[16]) {
-#if VT_EXP & 2
-    for (int i = 0; i < 4; ++i) v[i] = R.rw[i], v[4 + i] = (&R.sa[0].x)[i], v[8 + i] = (&R.sb[0].x)[i], v[12 + i] = (&R.sa[1].x)[i] ^ (&R.sb[1].x)[i];
-    return;
-#endif
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg) {
       uint32_t ea[4], eb[4];
@@ -553,13 +462,7 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     }
   };
   auto store_unit = [&](uint32_t qt, int mb, int ch, const uint32_t (&v)[16]) {
-#if VT_EXP & 1
-    uint32_t x = 0;
-    for (int i = 0; i < 16; ++i) x ^= v[i];
-    if (x == 0x12345678u) s.abort_flag = 2;  // keeps the values alive
-#else
     ptx::tmem_st_16x128b_x8(tm_q + (uint32_t(16 * ch) << 16) + VtCols::vt(2 * qt + mb), v);
-#endif
   };
   VtUnitRegs ra, rb;  // ping-pong: neither set is ever copied
 #pragma unroll 1
@@ -567,8 +470,8 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     const uint32_t tile = it + uint32_t(tl);
     const uint32_t slot = tile % kVtRawSlots, ts = tile % kVtScRing;
     {  // the tile's scale table and raw bytes
-      bool ok = VT_WAIT(0, ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag));
-      ok = ok && VT_WAIT(1, ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag));
+      bool ok = ptx::mbar_wait(&s.sc_full[ts], (tile / kVtScRing) & 1, &s.abort_flag);
+      ok = ok && ptx::mbar_wait(&s.raw_full[slot], (tile / kVtRawSlots) & 1, &s.abort_flag);
       if (!__all_sync(~0u, ok)) return;
     }
     // PV must have released this half of the ring (the previous tile's): the test is issued now, its answer used after
@@ -576,7 +479,6 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     const uint32_t probed = ptx::mbar_probe(&s.vt_free[vw], (tile & 1) ^ 1);
     raw_base = ptx::smem_u32(s.raw[slot]) + row_off;
     sc_base = ptx::smem_u32(&s.sc[ts][0][0][0]) + 32 * q;
-    if (quad == 0 && vw == 0) VT_EV(11, tile);
     load_unit(2 * vw, 0, 0, ra);
 #pragma unroll 1
     for (uint32_t gi = 0; gi < 2; ++gi) {
@@ -585,10 +487,9 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
       load_unit(qt, 0, 1, rb);
       finish_unit(qt, 0, 0, ra, v);
       if (gi == 0) {
-        const bool ok = VT_WAIT(2, ptx::mbar_wait_probed(probed, &s.vt_free[vw], (tile & 1) ^ 1, &s.abort_flag));
+        const bool ok = ptx::mbar_wait_probed(probed, &s.vt_free[vw], (tile & 1) ^ 1, &s.abort_flag);
         ptx::tc_fence_after_sync();
         if (!__all_sync(~0u, ok)) return;
-        if (quad == 0 && vw == 0) VT_EV(12, tile);
       }
       store_unit(qt, 0, 0, v);
       load_unit(qt, 1, 0, ra);
@@ -606,11 +507,10 @@ __device__ __forceinline__ void vt_v_role(VtSmem& s, const DecodeParams& P, int 
     __syncwarp();
     ptx::mbar_arrive_if(&s.sc_free[ts], lane == 0);
     ptx::mbar_arrive_if(&s.raw_empty[slot], lane == 0);
-    VT_WAIT(3, (ptx::tmem_wait_st(), true));
+    ptx::tmem_wait_st();
     ptx::tc_fence_before_sync();
     __syncwarp();
     ptx::mbar_arrive_if(&s.vt_full[vw], lane == 0);
-    if (quad == 0 && vw == 1) VT_EV(14, tile);
   }
   it += uint32_t(total);
 }
@@ -634,14 +534,12 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
       {
         const uint32_t p0 = ptx::mbar_probe(&s.s_free[buf], ((it >> 1) - 1) & 1), p1 = ptx::mbar_probe(&s.raw_full[slot], (it / kVtRawSlots) & 1),
                        p2 = ptx::mbar_probe(&s.k_full[buf], (it >> 1) & 1);
-        bool ok = it < 2 || VT_WAIT(0, ptx::mbar_wait_probed(p0, &s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
-        ok = ok && VT_WAIT(2, ptx::mbar_wait_probed(p1, &s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag));
-        ok = ok && VT_WAIT(1, ptx::mbar_wait_probed(p2, &s.k_full[buf], (it >> 1) & 1, &s.abort_flag));
+        bool ok = it < 2 || ptx::mbar_wait_probed(p0, &s.s_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
+        ok = ok && ptx::mbar_wait_probed(p1, &s.raw_full[slot], (it / kVtRawSlots) & 1, &s.abort_flag);
+        ok = ok && ptx::mbar_wait_probed(p2, &s.k_full[buf], (it >> 1) & 1, &s.abort_flag);
         if (!__all_sync(~0u, ok)) return;
       }
       ptx::tc_fence_after_sync();
-      VT_EV(4, it);
-      VT_T(tq0_);
       if (leader) {
         const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.raw[slot]), 16, 1024);
         // K step a = channels [64 a, +64): panel a / 4, 32 bytes per step. B of pass pp = rows [term 2 pp | term 2 pp + 1].
@@ -657,16 +555,11 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
           ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::KROPE + 8 * ks, qrope_desc + ((ks * 32) >> 4), idesc16, 1);
         ptx::mma_commit(&s.rope_free);
 #pragma unroll 1
-        for (int a = 1; a < 8 * ((VT_EXP & 128) ? 1 : kVtPasses); ++a) fp4(a >> 3, a & 7, 1);  // (rolled: issue is not the bound, code size is)
-        VT_T(tq1_);
-        VT_ACC(4, tq0_, tq1_);
+        for (int a = 1; a < 8 * kVtPasses; ++a) fp4(a >> 3, a & 7, 1);  // (rolled: issue is not the bound, code size is)
         ptx::mma_commit(&s.k_free[buf]);
         ptx::mma_commit(&s.s_full[buf]);
         ptx::mma_commit(&s.raw_empty[slot]);
-        VT_T(tq2_);
-        VT_ACC(5, tq1_, tq2_);
       }
-      VT_EV(5, it);
     }
   }
 }
@@ -679,16 +572,14 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
     const int ntiles = s.segs[si].ntiles;
     for (int t = 0; t < ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      if (!__all_sync(~0u, VT_WAIT(0, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag)))) return;
-      VT_EV(8, it);
+      if (!__all_sync(~0u, ptx::mbar_wait(&s.p_full[buf], (it >> 1) & 1, &s.abort_flag))) return;
 #pragma unroll 1
       for (int hf = 0; hf < 2; ++hf) {  // half of the ring = 64 tokens = slots 4 hf .. 4 hf + 3
-        if (!__all_sync(~0u, VT_WAIT(1, ptx::mbar_wait(&s.vt_full[hf], it & 1, &s.abort_flag)))) return;
+        if (!__all_sync(~0u, ptx::mbar_wait(&s.vt_full[hf], it & 1, &s.abort_flag))) return;
         ptx::tc_fence_after_sync();
-        VT_T(tp0_);
         if (leader) {
 #pragma unroll 1
-          for (int k = 0; k < ((VT_EXP & 64) ? 0 : 4); ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
+          for (int k = 0; k < 4; ++k) {  // slot = (32-token group sl / 2, channel-pair block sl % 2)
             const int sl = 4 * hf + k;
             const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.p[buf][sl >> 1]), 16, 1024);
 #pragma unroll
@@ -696,15 +587,9 @@ __device__ __forceinline__ void vt_pv_role(VtSmem& s, const DecodeParams& P, int
               ptx::mma_f16_ts(tm + VtCols::o(sl & 1), tm + VtCols::vt(sl) + 8 * ks, p_desc + ((ks * 32) >> 4), idesc,
                               (t | (sl >> 1) | ks) != 0);
           }
-          VT_T(tp1_);
-          VT_ACC(4, tp0_, tp1_);
           ptx::mma_commit(&s.vt_free[hf]);
           if (hf == 1) ptx::mma_commit(&s.p_free[buf]);
-          VT_T(tp2_);
-          VT_ACC(5, tp1_, tp2_);
         }
-        if (hf == 0) VT_EV(9, it);
-        if (hf == 1) VT_EV(10, it);
       }
     }
   }
@@ -738,10 +623,8 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
 
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const uint32_t buf = it & 1;
-      const bool ok = VT_WAIT(0, ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag));
+      const bool ok = ptx::mbar_wait(&s.s_full[buf], (it >> 1) & 1, &s.abort_flag);
       ptx::tc_fence_after_sync();
-      if (warp == 0) VT_EV(6, it);
-      VT_T(ts0_);
       float x[N];
       float qa_r[N];  // per-head score scales, written by the K warps before the segment's first K side was published
       {
@@ -755,12 +638,8 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       if (ok) {
         const bool valid = seg.tok0 + t * TILE + r < seg.tok_end;
         uint32_t sv[32];  // columns [0, 16): even terms + rope, [16, 32): odd terms
-#if VT_EXP & 16384
-        for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(float(i + r) * 0.01f);
-#else
         ptx::tmem_ld32(tm_lane + VtCols::s(buf), sv);
         ptx::tmem_wait_ld();
-#endif
 #pragma unroll
         for (int h = 0; h < N; ++h) x[h] = valid ? (__uint_as_float(sv[h]) + __uint_as_float(sv[16 + h])) * qa_r[h] : -INFINITY;
       } else {
@@ -770,15 +649,13 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       ptx::tc_fence_before_sync();
       __syncwarp();
       ptx::mbar_arrive_if(&s.s_free[buf], lane == 0);  // QK^T of tile it + 2 may overwrite this S^T buffer
-      VT_T(ts1_);
-      VT_ACC(3, ts0_, ts1_);
       // does any score exceed its running maximum by more than the slack? (one maximum over the differences: a chain of
       // sixteen predicate updates would be sixteen predicate latencies long; x = m = -inf gives NaN, which fmaxf drops)
       float dmax[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) dmax[j] = fmaxf(fmaxf(x[j] - m[j], x[4 + j] - m[4 + j]), fmaxf(x[8 + j] - m[8 + j], x[12 + j] - m[12 + j]));
       const bool need = !ok || fmaxf(fmaxf(dmax[0], dmax[1]), fmaxf(dmax[2], dmax[3])) > kGrow;
-      if (VT_WAIT(2, ptx::bar_red_or(1, 128, need))) {
+      if (ptx::bar_red_or(1, 128, need)) {
         if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
 #pragma unroll
         for (int h = 0; h < N; ++h) {
@@ -819,31 +696,23 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
       }
       // PV of tile it - 2 must have read this P^T buffer
       // (if this wait gives up the abort flag is raised and the next vote or the epilogue ends the role for all)
-      VT_T(ts2_);
-      VT_ACC(4, ts1_, ts2_);
-      if (it >= 2) VT_WAIT(1, ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag));
-      VT_T(ts3_);
+      if (it >= 2) ptx::mbar_wait(&s.p_free[buf], ((it >> 1) - 1) & 1, &s.abort_flag);
       const uint32_t p_base = ptx::smem_u32(s.p[buf][r >> 5]) + p_off;
       uint32_t p_row[8];  // row n of the panel: base + 128 n + the swizzled chunk, which depends on n % 8 only
 #pragma unroll
       for (int c = 0; c < 8; ++c) p_row[c] = p_base + ((p_chunk ^ uint32_t(c)) << 4);
 #pragma unroll
-      for (int h = 0; h < ((VT_EXP & 512) ? 1 : N); ++h) {
+      for (int h = 0; h < N; ++h) {
         const float pv = ptx::ex2(x[h] - m[h]);  // x = -inf gives 0
         lsum[h] += pv;
         const uint32_t w = ptx::f32x2_to_f16x2(pv, 0.f);  // (p, 0): the even channel of the pair
         ptx::sts32(p_row[(2 * h) & 7] + (2 * h) * 128, w);
         ptx::sts32(p_row[(2 * h + 1) & 7] + (2 * h + 1) * 128, w << 16);
       }
-      VT_T(ts4_);
-      VT_ACC(5, ts3_, ts4_);
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       __syncwarp();
       ptx::mbar_arrive_if(&s.p_full[buf], lane == 0);
-      VT_T(ts5_);
-      VT_ACC(6, ts4_, ts5_);
-      if (warp == 0) VT_EV(7, it);
     }
 
     // ---- segment epilogue: wait for the last PV, reduce the denominators, write the normalised partial
@@ -960,11 +829,6 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
   ptx::grid_launch_dependents();
 
-#ifdef MLA_VT_PROF
-  if (threadIdx.x < 160) (&s.prof[0][0])[threadIdx.x] = 0;
-  __syncthreads();
-  const uint32_t prof_t0 = vt_clock();
-#endif
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
   constexpr int kSoftmaxRegs = 104, kKRegs = 136, kVRegs = 96, kMiscRegs = 48;
@@ -985,14 +849,8 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
     else vt_run_role<kVtIdle>(s, P, &ckv_map, &sf_map, &kpe_map);
   }
 
-#ifdef MLA_VT_PROF
-  if ((threadIdx.x & 31) == 0) s.prof[warp][7] = vt_clock() - prof_t0;
-#endif
   ptx::tc_fence_before_sync();
   __syncthreads();
-#ifdef MLA_VT_PROF
-  if (blockIdx.x == 1 && threadIdx.x < 160 && vt_prof_ptr) vt_prof_ptr[threadIdx.x] = (&s.prof[0][0])[threadIdx.x];
-#endif
   if (warp == 16) ptx::tmem_dealloc(s.tmem_base, kTmemCols);
   if (threadIdx.x == 0 && s.abort_flag) atomicExch(P.header, int(kWaitTimeout));
 }
