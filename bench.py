@@ -51,7 +51,7 @@ BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
 # DRAM bytes (read + write) per cached token of the H=16 decode kernels, from ncu captures of a smaller case of the same
 # kernels (h16_b8_64k: 524 288 tokens); the kernels are persistent and stream each token once, so traffic grows with the
 # token count and the benchmark scales it to its own workload (roofline.traffic_kind says so).
-NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 401, "fp8": 398}
+NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 399, "fp8": 398}
 KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 
@@ -502,6 +502,51 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
     return res
 
 
+def reference_gpu_kernel(workload, precision, steps=20, warmup=3):
+    """Same-box timing of the reference's own CUDA kernel (its `mma.sync` split-KV decode, nvfp4_mla/csrc/mla_decode.cu),
+    called through its public `nvfp4_mla.decode` on the inputs the product arm gets. The unmodified package is taken
+    from baseline/_ref (installed there with pip, not part of this repository's sources) and JIT-compiles its
+    extension for the GPU it finds on first use. Opt-in (`--reference-gpu`): the build takes a minute or two."""
+    import importlib.util
+    import torch
+    import nvfp4_mla_b200 as mla
+    from nvfp4_mla_b200.testing import SM_SCALE, SyntheticCache
+    init = pathlib.Path(__file__).resolve().parent / "baseline" / "_ref" / "nvfp4_mla" / "__init__.py"
+    if not init.exists():
+        return {"unavailable": "baseline/_ref holds no installed reference package"}
+    try:
+        spec = importlib.util.spec_from_file_location("nvfp4_mla_reference", init, submodule_search_locations=[str(init.parent)])
+        ref = importlib.util.module_from_spec(spec)
+        sys.modules["nvfp4_mla_reference"] = ref
+        spec.loader.exec_module(ref)
+        B, H, kv_len, ps, _ = WORKLOADS[workload]
+        c = SyntheticCache(request_lengths(kv_len, B, 0), ps, H, None, None, seed=0, device="cuda")
+        max_len = max(c.kv_lens_list)
+        call = lambda: ref.decode(c.q_nope, c.q_pe, c.ckv_cache, c.ckv_sf_cache, c.kpe_cache, c.page_table, c.kv_lens, SM_SCALE,
+                                  c.ckv_scale, c.kpe_scale, max_kv_len=max_len, precision=precision)
+        t_build = time.time()
+        out_ref = call()
+        torch.cuda.synchronize()
+        t_build = time.time() - t_build
+        for _ in range(warmup):
+            call()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        ours = mla.decode(*c.args(), max_kv_len=max_len, precision=precision)
+        diff = (ours.float() - out_ref.float()).abs().max().item()
+        kv_bytes = TOKEN_BYTES * sum(c.kv_lens_list)
+        return {"kernel": "the reference's CUDA kernel (mma.sync, nvfp4_mla/csrc/mla_decode.cu) through nvfp4_mla.decode, built on this box",
+                "precision": precision, "ms_per_step": ms, "kv_tbps": kv_bytes / (ms * 1e-3) / 1e12, "steps": steps,
+                "first_call_s": t_build, "max_abs_vs_this_library": diff}
+    except Exception as e:  # a missing compiler, an unsupported GPU: report, do not fail the product arm
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -513,6 +558,8 @@ def main():
     ap.add_argument("--precision", default=None, choices=["bf16", "fp8"], help="override the workload's precision mode")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reference-gpu", action="store_true",
+                    help="also time the reference's own CUDA kernel from baseline/_ref on this GPU (one GPU only)")
     ap.add_argument("--no-seq-sharded", action="store_true",
                     help="skip the sequence-sharded long-context pass that the default workload appends")
     args = ap.parse_args()
@@ -621,7 +668,7 @@ def main():
         "metric": "nvfp4_mla_decode_kv_bandwidth", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if seq else "weak",
         "vs_baseline": (value / world / BASELINE_TBPS[args.workload]) if args.workload in BASELINE_TBPS and world == 1 else None,
-        "dtype": "f16 operands, f32 accumulate" if precision == "bf16" else "e4m3 operands, f32 accumulate",
+        "dtype": "QK^T: block-scaled e2m1 K (exact) x 4-term e2m1 query; PV: f16; f32 accumulate" if precision == "bf16" else "e4m3 operands, f32 accumulate",
         "data": "synthetic", "config": config,
         "decode_us": ms_step * 1e3, "frac_of_8tbps": value / world / 8.0,
         "e2e": {"value": m["kv_bytes_all"] / (m["e2e_ms"] * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": m["e2e_ms"],
@@ -635,6 +682,8 @@ def main():
         line["exchange_merge_us"] = (ms_step - m["local_decode_ms"]) * 1e3
     if seq_extra:
         line["seq_sharded"] = seq_extra
+    if args.reference_gpu and world == 1:
+        line["reference_gpu"] = reference_gpu_kernel(args.workload, precision)
     if world == 1 and not args.no_cpu_baseline:
         from nvfp4_mla_b200.testing import SyntheticCache
         n = args.cpu_sample_requests
