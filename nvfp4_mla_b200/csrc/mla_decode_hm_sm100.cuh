@@ -291,7 +291,7 @@ __device__ __forceinline__ void hm_qk_role(HmSmem<RAW_SLOTS>& s, const DecodePar
     if (!__all_sync(~0u, ptx::mbar_wait(&s.q_full, seg_count & 1, &s.abort_flag))) return;
     ++seg_count;
     for (int t = 0; t < ntiles; ++t, ++it) {
-      const uint32_t buf = it & 1, kb = it % kHmKvBufs;
+      const uint32_t kb = it % kHmKvBufs;
       // the softmax warps have read the scores of tile it - 1
       if (!__all_sync(~0u, it < 1 || ptx::mbar_wait(&s.s_free, (it - 1) & 1, &s.abort_flag))) return;
       if (!__all_sync(~0u, ptx::mbar_wait(&s.kv_full[kb], (it / kHmKvBufs) & 1, &s.abort_flag))) return;

@@ -1,23 +1,24 @@
-// Weight-absorbed MLA decode over the NVFP4 paged latent-KV cache for sm_100a.
+// Weight-absorbed MLA decode over the NVFP4 paged latent-KV cache for sm_100a: the 8-bit mode at 16 or 32 heads per
+// CTA (the 16-bit mode is mla_decode_vt_sm100.cuh, 128 heads in the 8-bit mode mla_decode_hm_sm100.cuh; this header
+// also holds what the three share: DecodeParams, the segment batch, the query's per-row maxima).
 //
 // Data path (one CTA per SM, persistent over the work the schedule kernel assigned to it):
 //
-//   HBM --TMA--> raw ring (smem) --convert warps--> K as FP16 in TENSOR MEMORY (tokens = lanes)  --QK^T--> S^T (TMEM)
-//                                              \--> V as FP16 in smem, [token][channel]           --PV----> O^T (TMEM)
+//   HBM --TMA--> raw ring (smem) --convert warps--> K as E4M3 in TENSOR MEMORY (tokens = lanes)  --QK^T--> S^T (TMEM)
+//                                              \--> V as E4M3 in smem, [token][channel]           --PV----> O^T (TMEM)
 //
 // Tokens are the M dimension of both MMAs (128 per tile); the heads of the CTA are N (16 or 32), so 16 heads are
 // never padded to the MMA's minimum M.
 //   QK^T : S^T[token, head] = K[token, 576] . Q^T          A = K from tensor memory, B = Q^T from smem (K-major)
 //   PV   : O^T[chan, head] += V^T[chan, token] . P^T       A = V from smem read MN-major (the [token][channel] tile
 //          IS V^T with M contiguous), B = P^T from smem (K-major), 4 blocks of 128 channels
-// One dequantisation (thread = token, registers = channels) feeds both. Phase A of a tile converts the token row
-// to FP16 and writes it to tensor memory with tcgen05.st, chunk by chunk, so QK^T chases the conversion. Phase B,
-// once the previous tile's PV has released the V tile, copies the same FP16 values from tensor memory to the
-// swizzled V tile (tcgen05.ld + st.shared): the expensive arithmetic never waits for the V buffer.
-// In the 16-bit mode the rope chunk and the first latent chunk of odd tiles live in the 96 columns that K, S^T and O^T
-// leave over, so phase A of a tile starts while QK^T of the previous tile is still reading K.
-// FP16 holds e2m1 x e4m3 exactly (6 significant bits, 2^-10 .. 2688), so K and V are the cache's values bit for
-// bit; the query is converted to FP16 after an exact per-row power-of-two scaling that the score scale undoes.
+// One dequantisation (thread = token, registers = channels) feeds both: K, V = E4M3((e2m1 x scale) / 8), the reference's
+// 8-bit rounding. Phase A of a tile converts the token row and writes it to tensor memory with tcgen05.st, chunk by
+// chunk, so QK^T chases the conversion. Phase B copies the same values from tensor memory to one of two swizzled V
+// tiles (tcgen05.ld + st.shared): the arithmetic never waits for the V buffer.
+// The template parameter P8 (8-bit operands) is always true in the instantiations that are built; its `false`
+// branches are the layout rules of the FP16 form of this data path (K 288 columns, one 128 KB V tile), which the
+// 16-bit mode used before it got a kernel of its own.
 //
 // Warp roles (512 threads): 0-3 softmax + epilogue (thread = token row of S^T / channel row of O^T),
 // 4-11 dequantise (warp%4 = TMEM lane quadrant, two warps per quadrant split the channel panels), 12 QK^T issue,
@@ -293,142 +294,6 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
   ptx::fence_proxy_async_smem();
 }
 
-// One pipeline step of a convert thread, interleaved form (16-bit mode, whose single V tile makes the copy wait for PV
-// in any case; interleaving hides that wait behind arithmetic): phase A of tile `it` (dequantise the thread's share of
-// the token row into tensor memory, chunk by chunk, so that QK^T chases the conversion) interleaved with phase B of
-// tile `it - 1` (copy that tile's FP16 values from tensor memory into the V tile, block by block, as PV of tile
-// `it - 2` releases it; PV of tile `it - 1` chases the copy). Per 64-channel panel g of this thread:
-//     load A's packed words -> store B's previous panel to the V tile -> start loading B's panel from tensor memory
-//     -> compute A's panel -> publish A's previous chunk and B's previous panel -> (B's load has landed)
-//     -> store A's panel over it.
-// The shared-memory loads come before the V stores because the load/store unit works in order: a load issued behind
-// the eight 16-byte stores would hold the arithmetic until they have drained; this way the arithmetic overlaps the drain.
-// FULL = every row of tile `it` is a live token (no masking). Returns false if a wait gave up.
-template <int N, int RAW_SLOTS, bool P8, bool FULL, bool has_a, bool has_b>
-__device__ __forceinline__ bool convert_step_interleaved(DecodeSmem<N, RAW_SLOTS, P8>& s, const DecodeParams& P, const Seg& seg, int t, uint32_t it,
-                                             int lane, int quad, int hf) {
-  static_assert(!P8, "the 8-bit mode uses convert_step");
-  const int r = quad * 32 + lane;        // token row of the tile = tensor-memory lane
-  const int half = r >> 6, rr = r & 63;
-  const uint32_t tm_lane = s.tmem_base + (uint32_t(quad * 32) << 16);
-  const uint32_t hidx = 2 * it + half;
-  const int slot = hidx % RAW_SLOTS;
-  const uint8_t* raw = s.raw[slot];
-  const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
-  const uint32_t swz = uint32_t(rr & 7) << 4, swz_v = uint32_t(r & 7) << 4;
-  constexpr int W = Cols<N, P8>::PANEL;  // 32-bit words of one converted panel row
-  bool ok, valid = true;
-  uint4 sf16 = make_uint4(0, 0, 0, 0);
-  if (has_a) {
-    ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
-    if (!__all_sync(~0u, ok)) return false;
-    valid = FULL || (seg.tok0 + t * TILE + r < seg.tok_end);
-    sf16 = *reinterpret_cast<const uint4*>(raw + kRawSf + rr * 32 + ((uint32_t(hf) ^ ((rr >> 2) & P.sf_swz_mask)) << 4));  // the 16 block scales of this half row
-    // ---- rope chunk: 32 channels of this thread's half
-    const uint32_t kswz = (rr >> 1) & P.kpe_swz_mask;
-    const uint4 rope0 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf) ^ kswz) << 4));
-    const uint4 rope1 = *reinterpret_cast<const uint4*>(raw + kRawKpe + rr * 64 + ((uint32_t(2 * hf + 1) ^ kswz) << 4));
-    // (no wait here: the rope chunk and chunk 0 of this tile have columns of their own, see Cols::kTwoHomes; the columns
-    // shared with the previous tile are first written at chunk 1, after the wait for that tile's QK^T)
-    static_assert(Cols<N, P8>::kTwoHomes, "the interleaved step relies on the second home of the rope chunk and chunk 0");
-    const uint32_t rw[8] = {rope0.x, rope0.y, rope0.z, rope0.w, rope1.x, rope1.y, rope1.z, rope1.w};
-    uint32_t h[16];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      h[2 * j] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] & 0xFFFF)) : 0u;
-      h[2 * j + 1] = valid ? ptx::e4m3x2_to_f16x2(uint16_t(rw[j] >> 16)) : 0u;
-    }
-    ptx::tmem_st16(tm_lane + Cols<N, P8>::krope(it & 1) + 16 * hf, h);
-  }
-  uint32_t hb[W];  // a panel of tile it - 1 on its way from tensor memory to the V tile
-  // stores panel g of tile it - 1 (in hb) to the V tile, once PV of tile it - 2 has finished with that 128-channel block
-  auto store_v = [&](int g) -> bool {
-    const uint32_t tb = it - 1;
-    const bool okv = tb < 1 || ptx::mbar_wait(&s.vb_free[g], (tb - 1) & 1, &s.abort_flag);
-    if (!__all_sync(~0u, okv)) return false;
-    uint8_t* vrow = s.v16[0][g + 4 * hf] + r * 128;
-#pragma unroll
-    for (int c = 0; c < W / 4; ++c)
-      *reinterpret_cast<uint4*>(vrow + ((uint32_t(c) << 4) ^ swz_v)) = make_uint4(hb[4 * c], hb[4 * c + 1], hb[4 * c + 2], hb[4 * c + 3]);
-    return true;
-  };
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const int p = g + 4 * hf;  // 64-channel panel = bytes [32p, 32p + 32) of the 256-byte row; hf = its 128-byte half
-    uint32_t h[W / 2];         // half a panel (32 channels) at a time
-    uint32_t wds[8] = {}, sc[4] = {};
-    if (has_a) {
-      const uint8_t* base = raw + hf * kRawCkvHi + rr * 128;
-      const uint32_t c0 = uint32_t(2 * g) << 4;
-      const uint4 n0 = *reinterpret_cast<const uint4*>(base + (c0 ^ swz));
-      const uint4 n1 = *reinterpret_cast<const uint4*>(base + ((c0 + 16) ^ swz));
-      wds[0] = n0.x, wds[1] = n0.y, wds[2] = n0.z, wds[3] = n0.w, wds[4] = n1.x, wds[5] = n1.y, wds[6] = n1.z, wds[7] = n1.w;
-      if (g == 3) {  // last read of the raw slot by this thread
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&s.raw_empty[slot]);
-      }
-    }
-    if (has_b && g > 0 && !store_v(g - 1)) return false;
-    if (has_b) ptx::tmem_ldn(tm_lane + Cols<N, P8>::kpanel(p, (it - 1) & 1), hb);
-    auto convert_half = [&](int j0) {  // words j0 .. j0 + 3 of the panel -> h
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {  // word j0 + j = channels [8 (j0 + j), + 8) of the panel, scale block (j0 + j) / 2
-        uint32_t e[4];
-        ptx::e2m1x8_to_f16x8(wds[j0 + j], e);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[4 * j + i] = valid ? ptx::hmul2(e[i], sc[(j0 + j) >> 1]) : 0u;
-      }
-    };
-    if (has_a) {
-      const uint32_t sfw = g == 0 ? sf16.x : g == 1 ? sf16.y : g == 2 ? sf16.z : sf16.w;
-      // block scales: 4 E4M3 bytes -> four FP16 pairs (s, s)
-      const uint32_t s01 = ptx::e4m3x2_to_f16x2(uint16_t(sfw & 0xFFFF)), s23 = ptx::e4m3x2_to_f16x2(uint16_t(sfw >> 16));
-      sc[0] = __byte_perm(s01, s01, 0x1010), sc[1] = __byte_perm(s01, s01, 0x3232);
-      sc[2] = __byte_perm(s23, s23, 0x1010), sc[3] = __byte_perm(s23, s23, 0x3232);
-      convert_half(0);
-      // publish the previous chunk (rope for g = 0), whose tensor-memory store has been in flight during the arithmetic
-      // above, and the V panel stored at the top of this trip
-      ptx::tmem_wait_st();
-      if (has_b && g > 0) ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        ptx::mbar_arrive(&s.k_full[it & 1][g == 0 ? 4 : g - 1]);
-        if (has_b && g > 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
-      }
-    } else if (has_b && g > 0) {
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s.vb_full[g - 1]);
-    }
-    if (has_b) ptx::tmem_wait_ld();  // tile it - 1's panel is in registers; its columns may be overwritten
-    if (has_a) {
-      if (g == 1) {  // from here on the tile overwrites columns of the previous one: its QK^T must have finished
-        ok = it == 0 || ptx::mbar_wait(s.kdone_bar(it - 1), s.kdone_phase(it - 1), &s.abort_flag);
-        if (!__all_sync(~0u, ok)) return false;
-        ptx::tc_fence_after_sync();
-      }
-      ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1), h);
-      convert_half(4);
-      ptx::tmem_st16(tm_lane + Cols<N, P8>::kpanel(p, it & 1) + W / 2, h);
-    }
-  }
-  if (has_b && !store_v(3)) return false;
-  if (has_a) {
-    ptx::tmem_wait_st();
-    ptx::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.k_full[it & 1][3]);
-  }
-  if (has_b) {
-    ptx::fence_proxy_async_smem();
-    ptx::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&s.vb_full[3]);
-  }
-  return true;
-}
-
 // One pipeline step of a convert thread, in two parts.
 //   Part B (tile it - 1): copy the thread's FP16 / E4M3 row from tensor memory into the V tile and publish it. It
 //   comes first: it needs nothing from QK^T of tile it - 1, whose last MMAs are still in flight when the step starts,
@@ -480,7 +345,6 @@ __device__ __forceinline__ bool convert_step(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   const uint32_t hidx = 2 * it + half;
   const int slot = hidx % RAW_SLOTS;
   const uint8_t* raw = s.raw[slot];
-  const uint32_t prev = (it - 1) & 1;  // parity of tile it - 1's phase on the per-tile barriers
   const uint32_t swz = uint32_t(rr & 7) << 4;
   ok = ptx::mbar_wait(&s.raw_full[slot], (hidx / RAW_SLOTS) & 1, &s.abort_flag);
   if (!__all_sync(~0u, ok)) return false;
@@ -579,14 +443,10 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       const bool full = seg.tok0 + (t + 1) * TILE <= seg.tok_end;
       bool ok_s;
-      if constexpr (P8)  // double-buffered V tile: copy first, then convert
-        ok_s = !pending ? convert_step<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
-               : full   ? convert_step<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
-                        : convert_step<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
-      else
-        ok_s = !pending ? convert_step_interleaved<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
-               : full   ? convert_step_interleaved<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
-                        : convert_step_interleaved<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
+      // double-buffered V tile: copy first, then convert
+      ok_s = !pending ? convert_step<N, RAW_SLOTS, P8, false, true, false>(s, P, seg, t, it, lane, quad, hf)
+             : full   ? convert_step<N, RAW_SLOTS, P8, true, true, true>(s, P, seg, t, it, lane, quad, hf)
+                      : convert_step<N, RAW_SLOTS, P8, false, true, true>(s, P, seg, t, it, lane, quad, hf);
       pending = true;
       if (!ok_s) {
         dead = true;
@@ -596,8 +456,7 @@ __device__ __forceinline__ void convert_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
   }
   // drain: the batch's last tile still has to reach the V tile
   if (pending && !dead) {
-    if constexpr (P8) convert_step<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
-    else convert_step_interleaved<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
+    convert_step<N, RAW_SLOTS, P8, true, false, true>(s, P, seg, 0, it, lane, quad, hf);
   }
 }
 
@@ -613,7 +472,6 @@ __device__ __forceinline__ void qk_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
   const uint32_t tm = s.tmem_base;
   constexpr uint32_t FMT = P8 ? ptx::FMT_E4M3 : ptx::FMT_F16;
   constexpr int KSTEPS = P8 ? 2 : 4;            // MMAs per 64-channel panel (K = 32 E4M3 or 16 FP16 per MMA, 8 columns)
-  constexpr uint32_t W = Cols<N, P8>::PANEL;
   const uint32_t idesc = ptx::instr_desc(128, N, FMT, FMT, false, false);
   const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(s.q[0]), 16, 1024);
   // byte offset of (64-channel panel p, K step ks) inside Q^T: 16-bit: panel p, 32 bytes per step;
@@ -922,6 +780,7 @@ template <int N, int RAW_SLOTS, bool P8>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_constant__ CUtensorMap sf_map,
                   const __grid_constant__ CUtensorMap kpe_map, const DecodeParams P) {
+  static_assert(P8, "only the 8-bit mode is built from this template: the 16-bit mode is mla_decode_vt_kernel");
   extern __shared__ uint8_t smem_raw[];
   using Smem = DecodeSmem<N, RAW_SLOTS, P8>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
