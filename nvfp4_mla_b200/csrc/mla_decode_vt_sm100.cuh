@@ -9,10 +9,11 @@
 //          accumulation): A = the packed ckv bytes exactly as TMA delivered them (K-major, 128-byte swizzle), its scale
 //          factors = the cache's E4M3 block scales, so K enters the product EXACTLY (e2m1 x e4m3, no rounding). The
 //          BF16 query cannot be an FP4 operand as it is; it is written once per request as a sum of four E2M1 terms,
-//          q * 2^k = sum_t s_t . c_t with one E4M3 scale s_t per row and term (a quarter of the residual's maximum, so
-//          the codes stay in [-4, 4] where E2M1 is spaced by at most 1) and c_t the nearest E2M1 codes of the residual:
-//          the residual shrinks by 8 per term, five terms reproduce q to 2^-15 of the row maximum (finer than the
-//          rounding of an FP16 operand), and the terms are five MMA chains into one accumulator.
+//          q * 2^k = sum_t s_t . c_t, with E4M3 scales s_t per row, term and 32-channel group (a quarter of the group's
+//          residual maximum, so the codes stay in [-4, 4] where E2M1 is spaced by at most 1) and c_t the nearest E2M1
+//          codes of the residual: the residual shrinks by 8 per term, four terms reproduce q to 2^-12 of the group's
+//          maximum (the rounding of an FP16 operand is 2^-11 of the element), and the terms are MMA chains into one
+//          accumulator, two terms stacked along N per chain.
 //          The rope part (64 E4M3 channels) is converted to FP16 and multiplied with kind::f16 into the same
 //          accumulator, with the rope rows of Q pre-multiplied by kpe_scale / ckv_scale.
 //   PV   : a byte of the cache holds one token's channels 2c and 2c + 1, and the conversion instruction turns it
@@ -27,18 +28,20 @@
 //   (column 16 tg + 4 (t % 4) + (t % 16) / 4 for token 16 tg + t % 16); P^T uses the same order, and a contraction
 //   does not care about the order of its index.
 //
-// Tensor memory (512 columns): V^T ring 8 x 32 | rope K 2 x 32 | scale factors of A 2 x 32 | of B 16 | S^T 2 x 16 | O^T 2 x 32.
+// Tensor memory (all 512 columns): V^T ring 8 x 32 | rope K 32 | scale factors of A 2 x 32 | of B 32 | S^T 2 x 32 | O^T 2 x 32.
 //   V^T is a ring of eight slots of 32 tokens x 128 channel pairs = one tile: V^T(j) can be complete before P(j)
-//   exists, and the V warps of tile j + 1 follow PV of tile j slot by slot. Scale factors: the word of the four blocks
-//   of one K = 64 step of operand row r sits in lane r % 32 of every lane quadrant, column 4 step + r / 32.
+//   exists, and the V warps of tile j + 1 follow PV of tile j half by half (64 tokens). Scale factors: the word of the
+//   four blocks of one K = 64 step of operand row r sits in lane r % 32 of every lane quadrant, column 4 step + r / 32
+//   (A side); the B side has a word per row, pass and 128-channel quarter at column 16 pass + 4 quarter.
 // Shared memory: raw ring of three 128-token tiles (packed low / high halves, block scales, rope), the query terms,
-//   P^T (two tiles), and the block scales as FP16 pairs (s, s) for the V warps: a ring of ten quarter tiles
-//   ([block][32 tokens] each), written by the K warps; rows beyond the request's end get scale 0 there, so V is 0 and
-//   finite wherever P is 0.
+//   P^T (two tiles), and the block scales as FP16 pairs (s, s) for the V warps: two tables of a whole tile
+//   ([quarter][block][32 token slots] each), written by the K warps; rows beyond the request's end get scale 0 there,
+//   so V is 0 and finite wherever P is 0.
 //
-// Warp roles (512 threads): 0-3 softmax + epilogue, 4-7 K side (thread = token: scale factors and rope into tensor
-// memory, scale table for the V warps; the query terms at the start of a request), 8-11 V^T conversion (warp % 4 = lane
-// quadrant = 32 channel pairs of each block), 12 QK^T issue, 13 TMA producer, 14 PV issue.
+// Warp roles (640 threads): 0-3 softmax + epilogue, 4-7 K side (thread = token: scale factors and rope into tensor
+// memory, scale table for the V warps; the query terms at the start of a request), 8-15 V^T conversion (warp % 4 = lane
+// quadrant = 32 channel pairs of each block, warps 8-11 the first 64 tokens of a tile, 12-15 the second), 16 QK^T
+// issue, 17 TMA producer, 18 PV issue.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel reports kWaitTimeout.
 #pragma once
 #include "mla_decode_sm100.cuh"
@@ -58,14 +61,14 @@ constexpr int kVtRawTileBytes = TILE * TOKEN_BYTES;
 static_assert(kVtRawTileBytes % 1024 == 0, "raw tile alignment");
 
 struct VtCols {
-  // V^T ring | rope K | scale factors of A (two tiles) | scale factors of B (four columns per pass) | S^T (two tiles) | O^T
-  static constexpr uint32_t VT = 0, KROPE = 32 * kVtRing, SFA = KROPE + 32, SFB = SFA + 64, S = SFB + 4 * kVtPasses, O = S + 64;
+  // V^T ring | rope K | scale factors of A (two tiles) | scale factors of B (per pass: four channel quarters x four columns) | S^T (two tiles) | O^T
+  static constexpr uint32_t VT = 0, KROPE = 32 * kVtRing, SFA = KROPE + 32, SFB = SFA + 64, S = SFB + 16 * kVtPasses, O = S + 64;
   __host__ __device__ static constexpr uint32_t vt(uint32_t ring) { return VT + 32 * ring; }
   __host__ __device__ static constexpr uint32_t sfa(uint32_t buf) { return SFA + 32 * buf; }
   __host__ __device__ static constexpr uint32_t s(uint32_t buf) { return S + 32 * buf; }
   __host__ __device__ static constexpr uint32_t o(uint32_t mb) { return O + 32 * mb; }
   static_assert(O + 64 <= kTmemCols, "tensor memory overflow");
-  static_assert(SFA % 4 == 0 && SFB % 4 == 0 && kVtPasses <= 2, "scale-factor columns must be multiples of four (the B side is stored as eight)");
+  static_assert(SFA % 4 == 0 && SFB % 4 == 0 && kVtPasses == 2, "scale-factor columns must be multiples of four (the B side is stored as 32 columns)");
 };
 
 struct VtSmem {
@@ -80,7 +83,7 @@ struct VtSmem {
   alignas(16) float qa[4][16];                      // per-head score scale, ring indexed by segment count
   float red[4][16];
   float corr[16];
-  uint32_t sfb[kVtTerms][16];                       // scale word of (term, head) on its way to tensor memory
+  uint32_t sfb[kVtTerms][4][16];                    // scale word of (term, channel quarter, head) on its way to tensor memory
   alignas(8) uint64_t raw_full[kVtRawSlots];
   uint64_t raw_empty[kVtRawSlots];
   uint64_t k_full[2], k_free[2];                    // K side of the tile in tensor memory / QK^T of the tile complete
@@ -213,10 +216,14 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
 // role: K side (4 warps; thread = token row of the tile)
 // ---------------------------------------------------------------------------------------------------------------
 // The query of a segment, by the 128 K threads: row n = thread / 8, channels [64 sub, 64 sub + 64) with sub = thread % 8.
-// The row (latent part, and rope part times kpe_scale / ckv_scale) is scaled by 2^(6 - e), e = floor(log2(row maximum)).
-// Latent part: E2M1 terms; term t has ONE E4M3 scale per row, amax(residual) / 4 rounded, the codes are the nearest
-// E2M1 of residual / scale (saturating), and the residual is updated with what the codes decode to, so every term
-// corrects the rounding of the ones before it. Rope part: FP16, K-major with the 128-byte swizzle.
+// The row (latent part, and rope part times kpe_scale / ckv_scale) is scaled by 2^(9 - e), e = floor(log2(row maximum)).
+// Latent part: E2M1 terms. A term has sixteen E4M3 scales per row: one per (128-channel quarter, position j of the
+// 16-channel block inside its 64-channel MMA step), i.e. per 32 channels {128 qd + 64 a + 16 j ..}: that is how far the
+// 32 tensor-memory columns left for the B side's scale factors go (the MMA takes a scale word per step; a quarter's two
+// steps share theirs). A scale is a quarter of its group's residual maximum, rounded; the codes are the nearest E2M1 of
+// residual / scale (saturating), and the residual is updated with what the codes decode to, so every term corrects the
+// rounding of the ones before it, and an outlier channel coarsens only its own group.
+// Rope part: FP16, K-major with the 128-byte swizzle.
 __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, const Seg& seg, int kt, int par, int lane, int quad) {
   const int n = kt >> 3, sub = kt & 7;
   const long long row = (long long)seg.b * P.heads + (long long)seg.hg * 16 + n;
@@ -253,12 +260,13 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
 #pragma unroll
   for (int i = 0; i < 64; ++i) m = max(m, finite(r[i]));
   m = row_max(m), m_pe = row_max(m_pe);
-  // e = floor(log2(latent maximum)), so that the four E4M3 term scales stay in the format's normal range; raised if the rope
-  // part (FP16, at most 2^15 after scaling) is more than 2^8 times larger
+  // e = floor(log2(latent maximum)): the first term's scales are then at most 256 and the last term's still E4M3 normals
+  // for groups 64 times smaller than the row; raised if the rope part (FP16, at most 2^15 after scaling) is more than 2^5
+  // times larger
   int e = int(m >> 23) - 127, e_pe = int(m_pe >> 23) - 127;
-  e = e > e_pe - 8 ? e : e_pe - 8;
+  e = e > e_pe - 5 ? e : e_pe - 5;
   e = e < -100 ? -100 : e;
-  const float up = __uint_as_float(uint32_t(6 - e + 127) << 23);  // 2^(6 - e), exact: the row maximum lands in [64, 128)
+  const float up = __uint_as_float(uint32_t(9 - e + 127) << 23);  // 2^(9 - e), exact: the row maximum lands in [512, 1024)
 #pragma unroll
   for (int i = 0; i < 64; ++i) {
     r[i] *= up;
@@ -267,32 +275,37 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
   const uint32_t panel = uint32_t(sub) >> 2, c0 = 2 * (uint32_t(sub) & 3);
 #pragma unroll
   for (int t = 0; t < kVtTerms; ++t) {
-    uint32_t mt = 0;
+    uint32_t sc8[4];
+    float scf[4], inv[4];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) mt = max(mt, __float_as_uint(r[i]) & 0x7FFFFFFFu);
-    mt = row_max(mt);
-    const uint32_t sc8 = ptx::f32x2_to_e4m3x2(__uint_as_float(mt) * 0.25f, 0.f) & 0xFFu;  // E4M3 (positive), round to nearest
-    const float scf = __half2float(__ushort_as_half(uint16_t(ptx::e4m3x2_to_f16x2(uint16_t(sc8)) & 0xFFFFu)));
-    const float inv = scf > 0.f ? 1.f / scf : 0.f;
+    for (int j = 0; j < 4; ++j) {
+      uint32_t mt = 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mt = max(mt, __float_as_uint(r[16 * j + i]) & 0x7FFFFFFFu);
+      mt = max(mt, __shfl_xor_sync(~0u, mt, 1));  // the other step of this 128-channel quarter
+      sc8[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(mt) * 0.25f, 0.f) & 0xFFu;  // E4M3 (positive), round to nearest
+      scf[j] = __half2float(__ushort_as_half(uint16_t(ptx::e4m3x2_to_f16x2(uint16_t(sc8[j])) & 0xFFFFu)));
+      inv[j] = scf[j] > 0.f ? 1.f / scf[j] : 0.f;
+    }
     uint32_t cw[8];
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
       float y[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = r[8 * w + i] * inv;
+      for (int i = 0; i < 8; ++i) y[i] = r[8 * w + i] * inv[w >> 1];
       uint32_t h[4];
       cw[w] = ptx::f32x8_to_e2m1x8(y, h);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
-        r[8 * w + 2 * i] = fmaf(-d.x, scf, r[8 * w + 2 * i]);
-        r[8 * w + 2 * i + 1] = fmaf(-d.y, scf, r[8 * w + 2 * i + 1]);
+        r[8 * w + 2 * i] = fmaf(-d.x, scf[w >> 1], r[8 * w + 2 * i]);
+        r[8 * w + 2 * i + 1] = fmaf(-d.y, scf[w >> 1], r[8 * w + 2 * i + 1]);
       }
     }
     uint8_t* dst = s.q4[t >> 1][panel] + (16 * (t & 1) + n) * 128;  // (the swizzle term of row 16 + n is that of row n)
     *reinterpret_cast<uint4*>(dst + (((c0) ^ uint32_t(n & 7)) << 4)) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
     *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ uint32_t(n & 7)) << 4)) = make_uint4(cw[4], cw[5], cw[6], cw[7]);
-    if (sub == 0) s.sfb[t][n] = sc8 * 0x01010101u;
+    if ((sub & 1) == 0) s.sfb[t][sub >> 1][n] = sc8[0] | (sc8[1] << 8) | (sc8[2] << 16) | (sc8[3] << 24);  // byte j = block j of the step
   }
   {
     uint32_t h[4];
@@ -300,17 +313,19 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
     for (int j = 0; j < 4; ++j) h[j] = ptx::f32x2_to_f16x2(pe[2 * j] * up, pe[2 * j + 1] * up);
     *reinterpret_cast<uint4*>(s.qrope + n * 128 + (uint32_t(sub ^ (n & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
   }
-  if (sub == 0) s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * __uint_as_float(uint32_t(e - 6 + 127) << 23);
+  if (sub == 0) s.qa[par][n] = P.sm_scale_log2 * P.ckv_scale * __uint_as_float(uint32_t(e - 9 + 127) << 23);
   ptx::fence_proxy_async_smem();
   ptx::bar_sync(2, 128);
-  // scale factors of B: pass p multiplies K with B rows [terms 2p | 2p + 1] x 16 heads; the scale word of row i goes to
-  // lane i of every lane quadrant, column 4 p
-  uint32_t w[8];
+  // scale factors of B: pass p multiplies K with B rows [terms 2p | 2p + 1] x 16 heads; the scale word of row i for the
+  // steps of quarter qd goes to lane i of every lane quadrant, column 16 p + 4 qd
+  uint32_t w[32];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) w[i] = 0u;
+  for (int i = 0; i < 32; ++i) w[i] = 0u;
 #pragma unroll
-  for (int pp = 0; pp < kVtPasses; ++pp) w[4 * pp] = s.sfb[2 * pp + (lane >> 4)][lane & 15];
-  ptx::tmem_st8(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, w);
+  for (int pp = 0; pp < kVtPasses; ++pp)
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) w[16 * pp + 4 * qd] = s.sfb[2 * pp + (lane >> 4)][qd][lane & 15];
+  ptx::tmem_st32(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, w);
   ptx::tmem_wait_st();
 }
 
@@ -547,7 +562,7 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
           const uint32_t off = uint32_t(a >> 2) * kVtRawHi + uint32_t(a & 3) * 32;
           const uint32_t qoff = uint32_t(pp * 2 + (a >> 2)) * (32 * 128) + uint32_t(a & 3) * 32;
           ptx::mma_mxf4nvf4_ss(tm + VtCols::s(buf), k_desc + (off >> 4), q4_desc + (qoff >> 4), idesc4, tm + VtCols::sfa(buf) + 4 * a,
-                               tm + VtCols::SFB + 4 * pp, accum);
+                               tm + VtCols::SFB + 16 * pp + 4 * (a >> 1), accum);
         };
         fp4(0, 0, 0);  // the first MMA of the tile overwrites all 32 columns of the accumulator
 #pragma unroll

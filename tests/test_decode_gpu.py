@@ -158,6 +158,26 @@ def test_calibrated_scales():
     check(c, out, None, "calibrated")
 
 
+@pytest.mark.parametrize("factor", [8.0, 16.0])
+def test_query_with_outlier_channels(factor):
+    """The 16-bit mode multiplies QK^T with the query written as FP4 terms whose scales cover 32 channels each: a few
+    channels far above the rest of their row (as absorbed queries have) must not cost the other channels their
+    precision. Same bounds as every 16-bit case (max-abs 2e-2, rel-L2 4e-3, LSE 1e-3); at 32 times the LSE error measured
+    1.2e-3 (output bounds still met): the coding keeps 2^-12 of a 32-channel group's maximum, not of each element."""
+    c = SyntheticCache([2000, 777, 4096, 130], 64, 16, None, None, seed=11)
+    g = torch.Generator().manual_seed(3)
+    for b in range(c.q_nope.shape[0]):
+        for h in range(16):
+            idx = torch.randperm(512, generator=g)[:4]
+            c.q_nope[b, h, idx] *= factor
+    c.q_pe[:, ::3, :5] *= factor / 2
+    c.to("cuda")
+    out = mla.decode(*c.args(), max_kv_len=c.max_kv_len)
+    _, lse2 = mla.decode_partial(*c.args(), max_kv_len=c.max_kv_len)
+    check_status()
+    check(c, out, lse2, f"outlier channels x{factor}")
+
+
 SCALES = {"scale 0.5": (0.5, 2.0), "calibrated": (2.0 ** -9, 2.0 ** -6)}
 
 
