@@ -273,7 +273,7 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
     if (!(fabsf(r[i]) < INFINITY)) r[i] = 0.f;  // a non-finite query element has no meaningful result anyway; keep the rest of the row intact
   }
   const uint32_t panel = uint32_t(sub) >> 2, c0 = 2 * (uint32_t(sub) & 3);
-#pragma unroll
+#pragma unroll 1  // (a term is some 700 instructions; unrolled, the routine is a third of the kernel's code and is fetched afresh at every request)
   for (int t = 0; t < kVtTerms; ++t) {
     uint32_t sc8[4];
     float scf[4], inv[4];
@@ -285,7 +285,7 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
       mt = max(mt, __shfl_xor_sync(~0u, mt, 1));  // the other step of this 128-channel quarter
       sc8[j] = ptx::f32x2_to_e4m3x2(__uint_as_float(mt) * 0.25f, 0.f) & 0xFFu;  // E4M3 (positive), round to nearest
       scf[j] = __half2float(__ushort_as_half(uint16_t(ptx::e4m3x2_to_f16x2(uint16_t(sc8[j])) & 0xFFFFu)));
-      inv[j] = scf[j] > 0.f ? 1.f / scf[j] : 0.f;
+      inv[j] = scf[j] > 0.f ? __fdividef(1.f, scf[j]) : 0.f;  // (only steers the choice of codes: the residual is updated with what they decode to)
     }
     uint32_t cw[8];
 #pragma unroll
@@ -750,7 +750,7 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
 #pragma unroll
     for (int h = 0; h < N; ++h) {
       const float l = (s.red[0][h] + s.red[1][h]) + (s.red[2][h] + s.red[3][h]);
-      inv[h] = l > 0.f ? P.ckv_scale / l : 0.f;
+      inv[h] = l > 0.f ? __fdividef(P.ckv_scale, l) : 0.f;  // (2 ulp; the IEEE division is twenty instructions, sixteen times)
       lsum[h] = l;
     }
     const long long slot = (long long)seg.cta + seg.w;
