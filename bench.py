@@ -51,7 +51,7 @@ BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
 # DRAM bytes (read + write) per cached token of the H=16 decode kernels, from ncu captures of a smaller case of the same
 # kernels (h16_b8_64k: 524 288 tokens); the kernels are persistent and stream each token once, so traffic grows with the
 # token count and the benchmark scales it to its own workload (roofline.traffic_kind says so).
-NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 399, "fp8": 398}
+NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 401, "fp8": 398}
 KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 
