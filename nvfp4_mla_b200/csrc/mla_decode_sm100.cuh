@@ -565,6 +565,49 @@ __device__ __forceinline__ void pv_role(DecodeSmem<N, RAW_SLOTS, P8>& s, const D
   }
 }
 
+// Reduces 16 (or 32) per-lane values over the warp in 16 (31) shuffles instead of 80 (160): every step exchanges the
+// half of the values that the partner lane keeps. With 16 values lane l ends with the result of value (l / 2) % 16
+// (lanes l and l ^ 1 hold the same one), with 32 values with that of value l. Deterministic. A shuffle costs about eight
+// instructions of code here, and the kernel's code size shows in its speed (instruction fetch).
+template <class Op>
+__device__ __forceinline__ float warp_reduce16(const float (&x)[16], int lane, Op op) {
+  float a[8], b[4], c[2];
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = op(b4 ? x[j + 8] : x[j], __shfl_xor_sync(~0u, b4 ? x[j] : x[j + 8], 16));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) b[j] = op(b3 ? a[j + 4] : a[j], __shfl_xor_sync(~0u, b3 ? a[j] : a[j + 4], 8));
+#pragma unroll
+  for (int j = 0; j < 2; ++j) c[j] = op(b2 ? b[j + 2] : b[j], __shfl_xor_sync(~0u, b2 ? b[j] : b[j + 2], 4));
+  const float d = op(b1 ? c[1] : c[0], __shfl_xor_sync(~0u, b1 ? c[0] : c[1], 2));
+  return op(d, __shfl_xor_sync(~0u, d, 1));
+}
+template <class Op>
+__device__ __forceinline__ float warp_reduce32(const float (&x)[32], int lane, Op op) {
+  float a[16], b[8], c[4], d[2];
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2, b0 = lane & 1;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) a[j] = op(b4 ? x[j + 16] : x[j], __shfl_xor_sync(~0u, b4 ? x[j] : x[j + 16], 16));
+#pragma unroll
+  for (int j = 0; j < 8; ++j) b[j] = op(b3 ? a[j + 8] : a[j], __shfl_xor_sync(~0u, b3 ? a[j] : a[j + 8], 8));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) c[j] = op(b2 ? b[j + 4] : b[j], __shfl_xor_sync(~0u, b2 ? b[j] : b[j + 4], 4));
+#pragma unroll
+  for (int j = 0; j < 2; ++j) d[j] = op(b1 ? c[j + 2] : c[j], __shfl_xor_sync(~0u, b1 ? c[j] : c[j + 2], 2));
+  return op(b0 ? d[1] : d[0], __shfl_xor_sync(~0u, b0 ? d[0] : d[1], 1));
+}
+// stores the warp's reduction of the N per-lane values x[] to dst[0 .. N)
+template <int N, class Op>
+__device__ __forceinline__ void warp_reduce_to(float* dst, const float (&x)[N], int lane, Op op) {
+  static_assert(N == 16 || N == 32, "16 or 32 values");
+  if constexpr (N == 16) {
+    const float v = warp_reduce16(x, lane, op);
+    if ((lane & 1) == 0) dst[(lane >> 1) & 15] = v;
+  } else {
+    dst[lane] = warp_reduce32(x, lane, op);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // role: softmax + epilogue (4 warps; thread r = token row of S^T and channel row of O^T)
 // ---------------------------------------------------------------------------------------------------------------
@@ -631,13 +674,7 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
       if (ptx::bar_red_or(1, 128, need)) {
         if (ptx::bar_red_or(1, 128, s.abort_flag != 0)) return;  // uniform decision, whoever raised the flag
         // new running max per head over the 128 token rows
-#pragma unroll
-        for (int h = 0; h < N; ++h) {
-          float v = x[h];
-#pragma unroll
-          for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(~0u, v, o));
-          if (lane == 0) s.red[warp][h] = v;
-        }
+        warp_reduce_to<N>(s.red[warp], x, lane, [](float p, float q) { return fmaxf(p, q); });
         ptx::bar_sync(1, 128);
         // The correction factors are the same in every thread (the running max is shared by all rows); they are parked
         // in shared memory (every thread stores the same values and reads back its own store) to keep this rare path
@@ -698,23 +735,13 @@ __device__ __forceinline__ void softmax_role(DecodeSmem<N, RAW_SLOTS, P8>& s, co
     bool ok = ptx::mbar_wait(&s.p_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag);  // PV of the last tile
     if (ptx::bar_red_or(1, 128, !ok)) return;
     ptx::tc_fence_after_sync();
-#pragma unroll
-    for (int h = 0; h < N; ++h) {
-      float v = lsum[h];
-#pragma unroll
-      for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
-      lsum[h] = v;
-    }
-    if (lane == 0) {
-#pragma unroll
-      for (int h = 0; h < N; ++h) s.red[warp][h] = lsum[h];
-    }
+    warp_reduce_to<N>(s.red[warp], lsum, lane, [](float p, float q) { return p + q; });
     ptx::bar_sync(1, 128);
     float inv[N];
 #pragma unroll
     for (int h = 0; h < N; ++h) {
       const float l = (s.red[0][h] + s.red[1][h]) + (s.red[2][h] + s.red[3][h]);
-      inv[h] = l > 0.f ? (P8 ? 8.f : 1.f) * P.ckv_scale / l : 0.f;
+      inv[h] = l > 0.f ? __fdividef((P8 ? 8.f : 1.f) * P.ckv_scale, l) : 0.f;  // (2 ulp; an IEEE division is twenty instructions, N times)
       lsum[h] = l;
     }
     const long long slot = (long long)seg.cta + seg.w;
