@@ -274,7 +274,7 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
       }
     } else {
       const float an = fmaxf(__uint_as_float(s.qamax[n]), 1e-30f), ap = fmaxf(__uint_as_float(s.qamax_pe[n]), 1e-30f);
-      const float inv = 448.f / (c < 64 ? an : ap);
+      const float inv = __fdividef(448.f, c < 64 ? an : ap);  // (2 ulp: it only steers the rounding of the codes; the score scale below is exact)
       uint32_t b[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
