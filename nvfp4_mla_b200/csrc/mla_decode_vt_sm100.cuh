@@ -341,13 +341,14 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
   // tests of the barriers needed further down, issued before the work that precedes them
   const uint32_t pr_kfree = ptx::mbar_probe(&s.k_free[buf], ((it >> 1) & 1) ^ 1), pr_rope = ptx::mbar_probe(&s.rope_free, (it & 1) ^ 1);
 
-  // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs
-  uint32_t h[32];
+  // The two 32-register payloads (rope, scale factors) are built and stored one after the other, so that only one of
+  // them is live at a time.
+  // ---- rope: 64 E4M3 bytes -> 32 columns of FP16 pairs; the rope MMAs of tile it - 1 must be done with rope K
   {
-    const uint32_t x = 0;  // (rows arrive unswizzled)
+    uint32_t h[32];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const uint4 v = ptx::lds128(raw + kVtRawKpe + r * 64 + ((uint32_t(c) ^ x) << 4));
+      const uint4 v = ptx::lds128(raw + kVtRawKpe + r * 64 + (uint32_t(c) << 4));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -355,24 +356,26 @@ __device__ __forceinline__ bool vt_k_step(VtSmem& s, const DecodeParams& P, cons
         h[8 * c + 2 * j + 1] = ptx::e4m3x2_to_f16x2(uint16_t(w[j] >> 16));
       }
     }
+    const bool ok = ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag);
+    ptx::tc_fence_after_sync();
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
   }
-  // ---- scale factors of A: lane l of this quadrant holds, for K step a, columns 4a + j = the scale word a of token 32 j + l
-  uint32_t f[32];
+  // ---- scale factors of A: lane l of this quadrant holds, for K step a, columns 4a + j = the scale word a of token
+  // 32 j + l; QK^T of tile it - 2 must have finished with this scale-factor buffer
+  {
+    uint32_t f[32];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int tk = 32 * j + lane;
-    const uint32_t x = 0;
-    const uint4 a = ptx::lds128(raw + kVtRawSf + tk * 32 + ((0u ^ x) << 4));
-    const uint4 b = ptx::lds128(raw + kVtRawSf + tk * 32 + ((1u ^ x) << 4));
-    f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
+    for (int j = 0; j < 4; ++j) {
+      const int tk = 32 * j + lane;
+      const uint4 a = ptx::lds128(raw + kVtRawSf + tk * 32), b = ptx::lds128(raw + kVtRawSf + tk * 32 + 16);
+      f[j] = a.x, f[4 + j] = a.y, f[8 + j] = a.z, f[12 + j] = a.w, f[16 + j] = b.x, f[20 + j] = b.y, f[24 + j] = b.z, f[28 + j] = b.w;
+    }
+    const bool ok = ptx::mbar_wait_probed(pr_kfree, &s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag);
+    ptx::tc_fence_after_sync();
+    if (!__all_sync(~0u, ok)) return false;
+    ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
   }
-  // QK^T of tile it - 2 must have finished with this scale-factor buffer, the rope MMAs of tile it - 1 with rope K
-  bool ok = ptx::mbar_wait_probed(pr_kfree, &s.k_free[buf], ((it >> 1) & 1) ^ 1, &s.abort_flag);
-  ok = ok && ptx::mbar_wait_probed(pr_rope, &s.rope_free, (it & 1) ^ 1, &s.abort_flag);
-  ptx::tc_fence_after_sync();
-  if (!__all_sync(~0u, ok)) return false;
-  ptx::tmem_st32(tm_lane + VtCols::KROPE, h);
-  ptx::tmem_st32(tm_lane + VtCols::sfa(buf), f);
   ptx::tmem_wait_st();
   ptx::tc_fence_before_sync();
   __syncwarp();
@@ -846,7 +849,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
 
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
-  constexpr int kSoftmaxRegs = 104, kKRegs = 136, kVRegs = 96, kMiscRegs = 48;
+  constexpr int kSoftmaxRegs = 128, kKRegs = 112, kVRegs = 96, kMiscRegs = 48;
   static_assert(4 * kSoftmaxRegs + 4 * kKRegs + 8 * kVRegs + 4 * kMiscRegs <= 20 * 96, "register budgets exceed the CTA's allocation");
   if (warp < 4) {
     ptx::reg_alloc<kSoftmaxRegs>();
