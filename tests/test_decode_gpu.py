@@ -178,6 +178,31 @@ def test_query_with_outlier_channels(factor):
     check(c, out, lse2, f"outlier channels x{factor}")
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_shapes_are_deterministic_and_clean(seed):
+    """A dozen random (batch, heads, page size, lengths, splits) per seed, both modes: repeated calls give identical
+    bits, the status word stays 0, and the 16-bit result of the smaller cases is held against the oracle."""
+    import random
+    rnd = random.Random(seed)
+    for rep in range(12):
+        B = rnd.choice([1, 2, 3, 8, 17, 32])
+        H = rnd.choice([16, 16, 32, 128])
+        ps = rnd.choice([16, 32, 64, 64, 128, 256])
+        maxlen = rnd.choice([1, 130, 700, 4096, 9000])
+        lens = [rnd.randint(0 if rnd.random() < 0.1 else 1, maxlen) for _ in range(B)]
+        if H == 128:
+            lens = lens[:3]
+        c = SyntheticCache(lens, ps, H, None, None, seed=100 * seed + rep).to("cuda")
+        for prec in ("bf16", "fp8"):
+            splits = rnd.choice([0, 1, 2, 5])
+            outs = [mla.decode(*c.args(), max_kv_len=max(lens + [1]), num_splits=splits, precision=prec) for _ in range(3)]
+            check_status()
+            assert not outs[0].isnan().any()
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (B, H, ps, prec, splits)
+            if prec == "bf16" and sum(lens) * H <= 400000:
+                check(c, outs[0], None, f"random shape B={B} H={H} ps={ps} splits={splits}")
+
+
 SCALES = {"scale 0.5": (0.5, 2.0), "calibrated": (2.0 ** -9, 2.0 ** -6)}
 
 
