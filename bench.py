@@ -13,8 +13,11 @@ value is the bytes all ranks streamed divided by the slowest rank's time (weak s
              is device-resident state written by earlier steps of a serving engine, not a per-step input.
   roofline   the decode kernel alone (timed by the library's own event pair around it) against the measured HBM peak
   cpu_baseline / --impl reference
-             the reference's CPU path (dequantize, then fp32 attention) as restated by oracle/mla_oracle.py, timed on
-             this box's host cores over a bounded sample of the same workload
+             the reference's CPU path (dequantize, then fp32 attention: its own torch functions from the unmodified
+             package under baseline/_ref, else their numpy restatement oracle/mla_oracle.py), timed on this box's host
+             cores over a bounded sample of the same workload
+  reference_gpu (--reference-gpu)
+             the reference's own CUDA kernel from baseline/_ref on the same GPU and inputs
 """
 import argparse
 import ctypes
@@ -138,17 +141,58 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(chosen), "window": window}
 
 
-def cpu_reference_sample(cache, n_requests, repeats=1):
-    """Times the oracle (dequantize + fp32 attention on host cores) on `n_requests` requests of the workload.
+_REF_TESTING = None
 
-    Returns (seconds per pass, KV bytes per pass, threads). The sample's pages are copied to the host first; the
+
+def reference_torch_path():
+    """The reference's own torch test path (`nvfp4_mla/testing.py`: dequantize, attention) from the unmodified package
+    installed under baseline/_ref, or None if it is absent or does not import (the module imports flashinfer at its top)."""
+    global _REF_TESTING
+    if _REF_TESTING is None:
+        _REF_TESTING = False
+        f = ROOT / "baseline" / "_ref" / "nvfp4_mla" / "testing.py"
+        if f.exists():
+            try:
+                import importlib.util
+                spec = importlib.util.spec_from_file_location("nvfp4_mla_reference_testing", f)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                _REF_TESTING = mod
+            except Exception:
+                _REF_TESTING = False
+    return _REF_TESTING or None
+
+
+def cpu_reference_sample(cache, n_requests, repeats=1):
+    """Times the reference's CPU path (dequantize + fp32 attention on host cores) on `n_requests` requests of the
+    workload: the reference's own torch functions when baseline/_ref holds the package (kind "reference"), else the
+    numpy port under oracle/ (kind "port").
+
+    Returns (seconds per pass, KV bytes per pass, threads, kind). The sample's pages are copied to the host first; the
     copy is not timed."""
-    sys.path.insert(0, str(ROOT / "oracle"))
     import numpy as np
     import torch
-    import mla_oracle as O
     ps = cache.page_size
     reqs = list(range(min(n_requests, len(cache.kv_lens_list))))
+    nbytes = TOKEN_BYTES * sum(cache.kv_lens_list[b] for b in reqs)
+    ref = reference_torch_path()
+    if ref is not None:
+        inputs = []
+        for b in reqs:
+            L = cache.kv_lens_list[b]
+            pages = cache.page_table[b, :(L + ps - 1) // ps].long()
+            inputs.append((cache.q_nope[b:b + 1].cpu(), cache.q_pe[b:b + 1].cpu(), cache.ckv_cache[pages].cpu(),
+                           cache.ckv_sf_cache[pages].cpu(), cache.kpe_cache[pages].cpu(),
+                           torch.arange(pages.numel(), dtype=torch.int32)[None], torch.tensor([L], dtype=torch.int32)))
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            for q_nope, q_pe, ckv8, sf8, kpe8, pt, lens in inputs:
+                ckv, kpe = ref.dequantize(ckv8, sf8, kpe8, cache.ckv_scale, cache.kpe_scale)
+                ref.attention(q_nope, q_pe, ckv, kpe, pt, lens, ref.SM_SCALE)
+        dt = (time.perf_counter() - t0) / repeats
+        return dt, nbytes, torch.get_num_threads(), "reference"
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import mla_oracle as O
     inputs = []
     for b in reqs:
         L = cache.kv_lens_list[b]
@@ -164,8 +208,11 @@ def cpu_reference_sample(cache, n_requests, repeats=1):
             ckv, kpe = O.dequantize(a["ckv"], a["sf"], a["kpe"], cache.ckv_scale, cache.kpe_scale)
             O.attention(a["q_nope"], a["q_pe"], ckv, kpe, a["pt"], a["L"], O.SM_SCALE)
     dt = (time.perf_counter() - t0) / repeats
-    nbytes = TOKEN_BYTES * sum(cache.kv_lens_list[b] for b in reqs)
-    return dt, nbytes, os.cpu_count()
+    return dt, nbytes, os.cpu_count(), "port"
+
+
+CPU_ARM_TEXT = {"reference": "the reference's own torch path (nvfp4_mla/testing.py from baseline/_ref) on host cores",
+                "port": "numpy port of the reference torch path"}
 
 
 def bench_writer(args):
@@ -599,19 +646,19 @@ def main():
             cpu_reference_sample(cache, 1)
         times, budget_s = [], 90.0  # the CPU arm stops after about a minute and a half, whatever --steps asks for
         for _ in range(args.steps):
-            dt, nbytes, threads = cpu_reference_sample(cache, n)
+            dt, nbytes, threads, kind = cpu_reference_sample(cache, n)
             times.append(dt)
             if sum(times) + dt > budget_s:
                 break
         t = sum(times) / len(times)
         val = nbytes / t / 1e12
-        sample = f"{n} of {B} requests per step ({nbytes // TOKEN_BYTES} tokens), numpy port of the reference torch path"
+        sample = f"{n} of {B} requests per step ({nbytes // TOKEN_BYTES} tokens), {CPU_ARM_TEXT[kind]}"
         print(json.dumps({
             "impl": "reference", "metric": "nvfp4_mla_decode_kv_bandwidth", "value": val, "unit": "TB/s",
             "n_gpus": args.gpus, "steps": len(times), "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config,
-            "cpu_baseline": {"value": val, "unit": "TB/s", "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "TB/s", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
@@ -688,10 +735,10 @@ def main():
         from nvfp4_mla_b200.testing import SyntheticCache
         n = args.cpu_sample_requests
         cache = SyntheticCache(request_lengths(kv_len, B, 0)[:n], ps, H, None, None, seed=0, device="cpu")
-        dt, nbytes, threads = cpu_reference_sample(cache, n)
-        line["cpu_baseline"] = {"value": nbytes / dt / 1e12, "unit": "TB/s", "cores": threads, "kind": "port",
+        dt, nbytes, threads, kind = cpu_reference_sample(cache, n)
+        line["cpu_baseline"] = {"value": nbytes / dt / 1e12, "unit": "TB/s", "cores": threads, "kind": kind,
                                 "seconds": dt,
-                                "sample": f"{n} of {B} requests ({nbytes // TOKEN_BYTES} tokens), numpy port of the reference torch path"}
+                                "sample": f"{n} of {B} requests ({nbytes // TOKEN_BYTES} tokens), {CPU_ARM_TEXT[kind]}"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
