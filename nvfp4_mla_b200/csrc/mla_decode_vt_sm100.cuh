@@ -573,7 +573,9 @@ __device__ __forceinline__ void vt_qk_role(VtSmem& s, const DecodeParams& P, int
           ptx::mma_f16_ts(tm + VtCols::s(buf), tm + VtCols::KROPE + 8 * ks, qrope_desc + ((ks * 32) >> 4), idesc16, 1);
         ptx::mma_commit(&s.rope_free);
 #pragma unroll 1
-        for (int a = 1; a < 8 * kVtPasses; ++a) fp4(a >> 3, a & 7, 1);  // (rolled: issue is not the bound, code size is)
+        // (rolled on purpose: unrolled, the 20 + 32 MMAs of the two issue warps with their descriptor arithmetic made the
+        // whole kernel 15 % slower; the issue warps share schedulers and instruction caches with the working warps)
+        for (int a = 1; a < 8 * kVtPasses; ++a) fp4(a >> 3, a & 7, 1);
         ptx::mma_commit(&s.k_free[buf]);
         ptx::mma_commit(&s.s_full[buf]);
         ptx::mma_commit(&s.raw_empty[slot]);
