@@ -224,7 +224,11 @@ __device__ __forceinline__ void vt_producer_role(VtSmem& s, const DecodeParams& 
 // residual / scale (saturating), and the residual is updated with what the codes decode to, so every term corrects the
 // rounding of the ones before it, and an outlier channel coarsens only its own group.
 // Rope part: FP16, K-major with the 128-byte swizzle.
-__device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, const Seg& seg, int kt, int par, int lane, int quad) {
+// `must_wait`: QK^T of the previous tile (barrier `prev_done`, `prev_parity`) still reads the old query; the rows are
+// fetched and scaled first, and the wait sits before the first store. Returns false if the wait gave up (`dead`: an
+// earlier one already has).
+__device__ __forceinline__ bool vt_load_query(VtSmem& s, const DecodeParams& P, const Seg& seg, int kt, int par, int lane, int quad,
+                                              bool dead, bool must_wait, uint64_t* prev_done, uint32_t prev_parity) {
   const int n = kt >> 3, sub = kt & 7;
   const long long row = (long long)seg.b * P.heads + (long long)seg.hg * 16 + n;
   float r[64];
@@ -271,6 +275,11 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
   for (int i = 0; i < 64; ++i) {
     r[i] *= up;
     if (!(fabsf(r[i]) < INFINITY)) r[i] = 0.f;  // a non-finite query element has no meaningful result anyway; keep the rest of the row intact
+  }
+  {
+    const bool ok = !dead && (!must_wait || ptx::mbar_wait(prev_done, prev_parity, &s.abort_flag));
+    if (ptx::bar_red_or(2, 128, !ok)) return false;
+    ptx::tc_fence_after_sync();
   }
   const uint32_t panel = uint32_t(sub) >> 2, c0 = 2 * (uint32_t(sub) & 3);
 #pragma unroll 1  // (a term is some 700 instructions; unrolled, the routine is a third of the kernel's code and is fetched afresh at every request)
@@ -327,6 +336,7 @@ __device__ __forceinline__ void vt_load_query(VtSmem& s, const DecodeParams& P, 
     for (int qd = 0; qd < 4; ++qd) w[16 * pp + 4 * qd] = s.sfb[2 * pp + (lane >> 4)][qd][lane & 15];
   ptx::tmem_st32(s.tmem_base + (uint32_t(quad * 32) << 16) + VtCols::SFB, w);
   ptx::tmem_wait_st();
+  return true;
 }
 
 // One tile of a K thread. Returns false if a wait gave up.
@@ -416,11 +426,10 @@ __device__ __forceinline__ void vt_k_role(VtSmem& s, const DecodeParams& P, int 
   for (int si = 0; si < n_segs; ++si) {
     const Seg seg = s.segs[si];
     if (seg.ntiles <= 0) continue;
-    // the previous tile's QK^T must be done reading the query before the new one overwrites it
-    const bool ok = !dead && (it == 0 || ptx::mbar_wait(&s.k_free[(it - 1) & 1], ((it - 1) >> 1) & 1, &s.abort_flag));
-    if (ptx::bar_red_or(2, 128, !ok)) return;
-    ptx::tc_fence_after_sync();
-    vt_load_query(s, P, seg, quad * 32 + lane, seg_count & 3, lane, quad);
+    // the previous tile's QK^T must be done reading the query before the new one overwrites it (waited for inside,
+    // after the rows have been fetched)
+    if (!vt_load_query(s, P, seg, quad * 32 + lane, seg_count & 3, lane, quad, dead, it != 0, &s.k_free[(it - 1) & 1], ((it - 1) >> 1) & 1))
+      return;
     ++seg_count;
     for (int t = 0; t < seg.ntiles; ++t, ++it) {
       if (!vt_k_step(s, P, seg, t, it, lane, quad)) {
