@@ -509,9 +509,11 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
            "steps": steps, "kv_bytes": kv_bytes}
     res["ms_step"] = max_over_ranks(total_ms / steps)
     res["kernel_ms"] = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
-    if seq and world > 1:  # the local split-KV decode alone (no exchange, no merge): what the collective adds on top
-        local_ms, _ = timed_pass(lambda: mla.decode_partial(*dargs, **kw))
+    if seq and world > 1:  # the local split-KV decode alone (no exchange, no merge): what the exchange adds on top
+        local_ms, _ = timed_pass(lambda: mla.decode_partial(*dargs, into=(merger.o, merger.lse), **kw))  # same buffers as the full step
         res["local_decode_ms"] = max_over_ranks(local_ms / steps)
+        res["merge"] = ("peer reads: one barrier between the GPUs, then the merge kernel loads the other GPUs' records over NVLink"
+                        if merger.handles is not None else "one NCCL all-gather of the packed records, then the merge kernel")
     if world > 1:
         t = torch.tensor([float(kv_bytes)], dtype=torch.float64, device=dev)
         dist.all_reduce(t)
@@ -683,6 +685,8 @@ def main():
                      "n_gpus": world, "steps": sm["steps"], "ms_per_step": sm["ms_step"], "decode_ms": sm["kernel_ms"],
                      "exchange_merge_us": (sm["ms_step"] - sm["local_decode_ms"]) * 1e3 if "local_decode_ms" in sm else 0.0,
                      "kv_tbps": sm["kv_bytes_all"] / (sm["ms_step"] * 1e-3) / 1e12, "parity_check": sm["parity_check"]}
+        if "merge" in sm:
+            seq_extra["merge"] = sm["merge"]
 
     if rank != 0:
         if world > 1:
@@ -727,6 +731,7 @@ def main():
     }
     if seq and "local_decode_ms" in m:
         line["exchange_merge_us"] = (ms_step - m["local_decode_ms"]) * 1e3
+        line["merge"] = m.get("merge")
     if seq_extra:
         line["seq_sharded"] = seq_extra
     if args.reference_gpu and world == 1:

@@ -163,6 +163,14 @@ NVFP4_MLA_API int nvfp4_mla_combine_strided(const float* o_part, const float* ls
                                             int64_t o_part_stride, int64_t lse_part_stride, void* out, float* out_f32,
                                             float* lse, void* stream);
 
+/* The same merge over `parts` (at most 16) packed records [o (rows x 512) | lse (rows)] at unrelated addresses:
+ * records is a HOST array of device pointers, 16-byte aligned, which may point into other GPUs' memory mapped into this
+ * process (peer access, symmetric memory). Used by the sequence-sharded decode to merge the GPUs' partial results where
+ * their owners wrote them, without a collective; the caller orders this call after the owners' writes (a barrier
+ * between the GPUs on the stream). Same reference counterpart as nvfp4_mla_combine. */
+NVFP4_MLA_API int nvfp4_mla_combine_records(const float* const* records, int parts, int64_t rows, void* out, float* out_f32,
+                                            float* lse, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,7 +8,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["decode", "dequantize", "decode_partial", "combine", "combine_packed", "workspace_status", "quantize_append_paged_mla_kv_cache",
+__all__ = ["decode", "dequantize", "decode_partial", "combine", "combine_packed", "combine_records", "workspace_status", "quantize_append_paged_mla_kv_cache",
            "get_batch_indices_positions"]
 __version__ = "0.1.0"
 
@@ -166,6 +166,25 @@ def combine_packed(packed, rows, out_dtype=torch.bfloat16):
             packed.data_ptr(), packed.data_ptr() + rows * CKV * 4, packed.shape[0], rows, stride, stride,
             _ptr(out) if out_dtype == torch.bfloat16 else None, _ptr(out) if out_dtype == torch.float32 else None, None,
             torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
+def combine_records(record_ptrs, rows, device, out_dtype=torch.bfloat16):
+    """Merge of packed records ``[o (rows x 512) | lse (rows)]`` (float32) given by their device addresses, one per
+    part (at most 16): the partial results of the GPUs of a sequence-sharded decode, read where their owners wrote them
+    (addresses of peers' symmetric-memory buffers included). The caller orders the call after the owners' writes.
+    Returns ``[rows, 512]`` in ``out_dtype`` on ``device``."""
+    import ctypes
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"out_dtype must be bfloat16 or float32, got {out_dtype}")
+    dev = torch.device(device)
+    out = torch.empty(rows, CKV, dtype=out_dtype, device=dev)
+    ptrs = (ctypes.c_void_p * len(record_ptrs))(*[int(p) for p in record_ptrs])
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        _lib.check(lib.nvfp4_mla_combine_records(
+            ptrs, len(record_ptrs), rows, _ptr(out) if out_dtype == torch.bfloat16 else None,
+            _ptr(out) if out_dtype == torch.float32 else None, None, torch.cuda.current_stream(dev).cuda_stream))
     return out
 
 

@@ -27,6 +27,7 @@ SIGNATURES = {
     "nvfp4_mla_dequantize": (_i32, [_vp, _vp, _vp, _i64, _f32, _f32, _i32, _vp, _vp, _vp]),
     "nvfp4_mla_combine": (_i32, [_vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp]),
     "nvfp4_mla_combine_strided": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "nvfp4_mla_combine_records": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp]),
     "nvfp4_mla_quantize_append": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _f32, _f32,
                                          _vp, _vp]),
 }

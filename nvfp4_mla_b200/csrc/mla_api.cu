@@ -505,6 +505,29 @@ int nvfp4_mla_combine_strided(const float* o_part, const float* lse_part, int pa
   return 0;
 }
 
+int nvfp4_mla_combine_records(const float* const* records, int parts, int64_t rows, void* out, float* out_f32, float* lse,
+                              void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(parts > 0 && rows >= 0, "parts must be positive and rows non-negative");
+  MLA_CHECK(parts <= mla::kCombineMaxRecords, "at most %d records, got %d", mla::kCombineMaxRecords, parts);
+  if (rows == 0) return 0;
+  MLA_CHECK(records, "null pointer argument");
+  MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
+  MLA_CHECK(aligned(out, 8) && aligned(out_f32, 16), "out_f32 must be 16-byte, out 8-byte aligned");
+  MLA_CHECK(rows < (int64_t(1) << 31), "rows must be below 2^31");
+  mla::RecordPtrs recs = {};
+  for (int i = 0; i < parts; ++i) {
+    MLA_CHECK(records[i] && aligned(records[i], 16), "record %d is null or not 16-byte aligned", i);
+    recs.p[i] = records[i];
+  }
+  if (rows <= 296)
+    mla::mla_combine_records_kernel<4><<<unsigned(rows), 512, 0, static_cast<cudaStream_t>(stream)>>>(recs, parts, rows, out, out_f32, lse);
+  else
+    mla::mla_combine_records_kernel<1><<<unsigned(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(recs, parts, rows, out, out_f32, lse);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32, float* lse,
                       void* stream) {
   return nvfp4_mla_combine_strided(o_part, lse_part, parts, rows, rows * mla::CKV, rows, out, out_f32, lse, stream);

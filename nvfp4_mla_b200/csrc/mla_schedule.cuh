@@ -284,4 +284,22 @@ mla_combine_dense_kernel(const float* __restrict__ o_part, const float* __restri
       [&](int i) { return o_part + (long long)i * o_stride + row * CKV; }, row, out_bf16, out_f32, lse_out, weights, partial);
 }
 
+// The same merge over packed records [o (rows x 512) | lse (rows)] that live at unrelated addresses, one per part: the
+// partial results of the GPUs of a sequence-sharded decode, read where their owners wrote them (a peer's record is read
+// over NVLink with ordinary loads; the caller orders the reads after the writes, e.g. with a barrier between the GPUs).
+constexpr int kCombineMaxRecords = 16;
+struct RecordPtrs {
+  const float* p[kCombineMaxRecords];
+};
+template <int GROUPS>
+__global__ void __launch_bounds__(128 * GROUPS)
+mla_combine_records_kernel(RecordPtrs recs, int parts, long long rows, void* out_bf16, float* out_f32, float* lse_out) {
+  __shared__ float weights[kCombineMaxParts];
+  __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
+  const long long row = blockIdx.x;
+  merge_row<GROUPS>(
+      parts, [&](int i) { return recs.p[i][rows * CKV + row]; }, [&](int i) { return recs.p[i] + row * CKV; }, row, out_bf16,
+      out_f32, lse_out, weights, partial);
+}
+
 }  // namespace mla

@@ -9,7 +9,9 @@ Two shardings follow the path's natural units (the reference itself is single-GP
   per rank; each rank runs the normal split-KV decode over its range in "partial" mode, producing for every
   (request, head) an output normalised by its own softmax sum and a log2-domain log-sum-exp, exactly the pair the
   in-GPU split merge consumes (reference contract: nvfp4_mla/csrc/mla_decode.cu:478-492). The pairs (513 KiB per GPU at
-  B=2, H=128) are all-gathered over NCCL / NVLink and merged on every rank with the library's combine kernel.
+  B=2, H=128) are merged on every rank with the library's combine kernel, which reads the other GPUs' records over
+  NVLink where they were written (symmetric memory, one barrier per step), or after one NCCL all-gather where that
+  cannot be set up.
 """
 import math
 
@@ -62,26 +64,73 @@ def merge_partials(o, lse, group=None, combine=None, out_dtype=torch.bfloat16):
 class PartialMerger:
     """Buffers of the cross-GPU merge, allocated once and reused by every decode step.
 
-    ``send`` is this rank's packed record ``[o (batch x heads x 512) | lse (batch x heads)]`` (float32); the decode
-    kernels write their partial result straight into it (``o`` and ``lse`` are views). ``recv [world, record]`` is the
-    target of ONE ``all_gather_into_tensor`` per step (the exchange is latency-bound: 513 KiB per rank at B=2, H=128),
-    and the library's combine kernel merges the records where they landed."""
+    A rank's partial result is one packed record ``[o (batch x heads x 512) | lse (batch x heads)]`` (float32) that the
+    decode kernels write directly (``o`` and ``lse`` are views of it). Two ways to merge the ranks' records:
 
-    def __init__(self, batch, heads, device, group=None):
-        self.group, self.rows = group, batch * heads
+    * **peer reads** (default where it can be set up): the records live in symmetric memory, every rank maps every
+      other rank's buffer, and after one barrier between the GPUs the library's merge kernel reads the peers' records
+      over NVLink with ordinary loads where their owners wrote them: no collective, no copy. Two records alternate
+      from step to step, so that a rank that is one step ahead never writes what a slower rank still reads (the barrier
+      of step s + 1 is passed only when every rank has finished the merge of step s).
+    * **all-gather** (``peer=False``, or when symmetric memory is unavailable: one GPU, a gloo group, an older torch):
+      ONE ``all_gather_into_tensor`` of the record per step into ``recv [world, record]``, merged where it landed.
+
+    The exchange is latency-bound either way (513 KiB per rank at B=2, H=128)."""
+
+    def __init__(self, batch, heads, device, group=None, peer=None):
+        import os
+        self.group, self.rows, self.shape = group, batch * heads, (batch, heads)
         self.world = dist.get_world_size(group)
+        self.device = torch.device(device)
         n = self.rows * 513
-        self.send = torch.empty(n, dtype=torch.float32, device=device)
-        self.recv = torch.empty(self.world, n, dtype=torch.float32, device=device)
-        self.o = self.send[:self.rows * 512].view(batch, heads, 512)
-        self.lse = self.send[self.rows * 512:].view(batch, heads)
+        self.step, self.handles = 0, None
+        if peer is None:
+            peer = os.environ.get("NVFP4_MLA_PEER_MERGE", "1") != "0"
+        if peer and self.world > 1 and self.world <= 16 and self.device.type == "cuda":
+            try:
+                import torch.distributed._symmetric_memory as symm
+                bufs = [symm.empty(n, dtype=torch.float32, device=self.device) for _ in range(2)]
+                self.handles = [symm.rendezvous(b, group if group is not None else dist.group.WORLD) for b in bufs]
+                self.records = bufs
+                self.peer_ptrs = [[int(h.buffer_ptrs[r]) for r in range(self.world)] for h in self.handles]
+            except Exception:  # no symmetric memory on this system / backend: the collective does the exchange
+                self.handles = None
+        if self.handles is None:
+            self.records = [torch.empty(n, dtype=torch.float32, device=device)]
+            self.recv = torch.empty(self.world, n, dtype=torch.float32, device=device)
+
+    @property
+    def send(self):
+        """The record the current step's decode writes."""
+        return self.records[self.step % len(self.records)]
+
+    @property
+    def o(self):
+        return self.send[:self.rows * 512].view(*self.shape, 512)
+
+    @property
+    def lse(self):
+        return self.send[self.rows * 512:].view(*self.shape)
 
     def merge(self, out_dtype=torch.bfloat16, combine_packed=None):
-        """One all-gather, one merge kernel. ``combine_packed(recv, rows, out_dtype)`` defaults to the library's kernel."""
+        """Merges the ranks' records of the current step; every rank returns the full ``[batch, heads, 512]`` result.
+        ``combine_packed(recv, rows, out_dtype)`` replaces the library's kernel on the all-gather path (tests)."""
+        if self.handles is not None and combine_packed is None:
+            from . import combine_records
+            k = self.step % 2
+            self.handles[k].barrier()  # every rank's record of this step is written and visible
+            out = combine_records(self.peer_ptrs[k], self.rows, self.device, out_dtype)
+            self.step += 1
+            return out.view(*self.shape, 512)
         if combine_packed is None:
             from . import combine_packed  # the CUDA kernel; there is no host implementation
-        dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
-        return combine_packed(self.recv, self.rows, out_dtype).view(*self.o.shape)
+        if self.handles is not None:  # a caller-supplied merge on the peer set-up: gather the records first
+            recv = torch.empty(self.world, self.rows * 513, dtype=torch.float32, device=self.device)
+        else:
+            recv = self.recv
+        dist.all_gather_into_tensor(recv.view(-1), self.send, group=self.group)
+        self.step += 1 if self.handles is not None else 0
+        return combine_packed(recv, self.rows, out_dtype).view(*self.shape, 512)
 
 
 def decode_sequence_sharded(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens, sm_scale,

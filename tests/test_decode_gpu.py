@@ -105,6 +105,26 @@ def test_combine_vs_oracle():
     assert out16.dtype == torch.bfloat16 and np.abs(out16.float().cpu().numpy() - want).max() < 2e-2
 
 
+def test_combine_records_equals_packed_merge():
+    """The merge over records at unrelated addresses (what the cross-GPU merge reads from the peers' buffers) against the
+    merge over one packed buffer, bit for bit, with an empty partial (lse = -inf) among them."""
+    g = torch.Generator().manual_seed(5)
+    rows, parts = 48, 5
+    recs = [torch.empty(rows * 513, dtype=torch.float32, device="cuda") for _ in range(parts)]
+    for i, r in enumerate(recs):
+        r[:rows * 512] = torch.randn(rows * 512, generator=g).cuda()
+        r[rows * 512:] = (torch.randn(rows, generator=g) * 3).cuda()
+    recs[2][rows * 512:] = float("-inf")
+    recs[2][:rows * 512] = float("nan")  # a partial of weight 0 may hold anything
+    want = mla.combine_packed(torch.stack(recs), rows, torch.float32)
+    got = mla.combine_records([r.data_ptr() for r in recs], rows, "cuda", torch.float32)
+    torch.cuda.synchronize()
+    assert not got.isnan().any()
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        mla.combine_records([r.data_ptr() for r in recs] * 4, rows, "cuda")  # 20 records: over the limit of 16
+
+
 @pytest.mark.parametrize("parts,rows_shape", [(3, (2, 16)), (9, (40, 16)), (70, (2, 16)), (70, (40, 16))])
 def test_combine_ignores_empty_partials(parts, rows_shape):
     """A partial of weight 0 (lse = -inf) may hold anything, NaN included: it must not reach the result. Covers the rows

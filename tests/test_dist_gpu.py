@@ -67,13 +67,20 @@ def _rank(rank, world, port, ret):
                                             c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32)
         torch.cuda.synchronize()
         err_seq = float(np.abs(out.cpu().numpy() - want).max())
-        # the same through preallocated buffers: the kernels write into the send record, one packed all-gather per step
-        mg = mdist.PartialMerger(len(c.kv_lens_list), 16, dev)
-        for _ in range(2):  # twice: the buffers are reused
-            out = mdist.decode_sequence_sharded(c.q_nope.to(dev), c.q_pe.to(dev), ckv, sf, kpe, pt, lens, SM_SCALE, c.ckv_scale,
-                                                c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32, merger=mg)
-            torch.cuda.synchronize()
-            err_seq = max(err_seq, float(np.abs(out.cpu().numpy() - want).max()))
+        # the same through preallocated buffers, both ways of merging: the peers' records read where they were written
+        # (symmetric memory; falls back to the collective by itself where that cannot be set up) and one packed
+        # all-gather per step. Three steps each: the buffers are reused, the peer records alternate.
+        modes = []
+        for peer in (True, False):
+            mg = mdist.PartialMerger(len(c.kv_lens_list), 16, dev, peer=peer)
+            modes.append("peer" if mg.handles is not None else "all-gather")
+            for _ in range(3):
+                out = mdist.decode_sequence_sharded(c.q_nope.to(dev), c.q_pe.to(dev), ckv, sf, kpe, pt, lens, SM_SCALE, c.ckv_scale,
+                                                    c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32, merger=mg)
+                torch.cuda.synchronize()
+                err_seq = max(err_seq, float(np.abs(out.cpu().numpy() - want).max()))
+        if rank == 0:
+            print("merge modes exercised:", modes)
         # ---- batch sharded: this rank's requests only
         mine = mdist.shard_batch(c.kv_lens_list, world)[rank]
         sub = SyntheticCache.__new__(SyntheticCache)
