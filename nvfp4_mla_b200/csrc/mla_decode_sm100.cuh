@@ -229,6 +229,7 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
   const long long row0 = (long long)seg.b * P.heads + (long long)seg.hg * N;
   constexpr int CH = (CKV + KPE) / 8;              // 72 chunks of 8 channels per row
   constexpr int PER = (N * CH + 255) / 256;        // chunks per thread: all loaded up front (one memory latency), kept for pass 2
+  const int lane_of_warp = ptx::lane_id();
   uint4 q8[PER];
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
@@ -249,7 +250,13 @@ __device__ __forceinline__ void load_query(DecodeSmem<N, RAW_SLOTS, P8>& s, cons
       const unsigned int lo = (w[j] << 16) & 0x7FFFFFFFu, hi = w[j] & 0x7FFF0000u;
       m = max(m, max(lo, hi));
     }
-    if (m < 0x7F800000u) atomicMax(c < 64 || !P8 ? &s.qamax[n] : &s.qamax_pe[n], m);  // ignore inf / nan for the scale
+    // One shared-memory atomic per (row, part) and warp instead of one per thread: the lanes that hold chunks of the
+    // same row part (a warp's 32 consecutive chunks belong to at most three) reduce among themselves first.
+    if (m >= 0x7F800000u) m = 0;  // ignore inf / nan for the scale
+    const bool pe = P8 && c >= 64;
+    const unsigned peers = __match_any_sync(__activemask(), 2 * n + int(pe));
+    m = __reduce_max_sync(peers, m);
+    if (lane_of_warp == __ffs(peers) - 1) atomicMax(pe ? &s.qamax_pe[n] : &s.qamax[n], m);
   }
   ptx::bar_sync(2, 256);
 #pragma unroll
