@@ -40,6 +40,7 @@ WORKLOADS = {
     "c1_h16_b32_8k": (32, 16, 8192, 64, "bf16"),     # a DeepSeek-V3 TP8 shard at 8K context
     "h16_b64_16k": (64, 16, 16384, 64, "bf16"),
     "h16_b8_64k": (8, 16, 65536, 64, "bf16"),        # small case for ncu captures (185 MB of KV, still larger than L2)
+    "h16_b148_128": (148, 16, 128, 64, "bf16"),      # one 128-token tile per CTA: the fixed costs of a call
     "h128_b64_16k": (64, 128, 16384, 64, "bf16"),
     # the compute-bound configuration: ragged lengths drawn uniformly from [1024, 32768] (seeded, per rank), 8-bit mode; tensor-bound
     "c3_h128_b64_ragged_fp8": (64, 128, (1024, 32768), 64, "fp8"),
