@@ -513,8 +513,12 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
     if seq and world > 1:  # the local split-KV decode alone (no exchange, no merge): what the exchange adds on top
         local_ms, _ = timed_pass(lambda: mla.decode_partial(*dargs, into=(merger.o, merger.lse), **kw))  # same buffers as the full step
         res["local_decode_ms"] = max_over_ranks(local_ms / steps)
-        res["merge"] = ("peer reads: one barrier between the GPUs, then the merge kernel loads the other GPUs' records over NVLink"
-                        if merger.handles is not None else "one NCCL all-gather of the packed records, then the merge kernel")
+        merger.check()  # raises if a hand-shake of the timed steps gave up waiting for a rank
+        res["merge"] = {"peer-signal": "peer reads: the merge kernel announces this GPU's record, waits for the others' "
+                                       "announcements (flag words in symmetric memory) and loads their records over NVLink",
+                        "peer-barrier": "peer reads: one barrier between the GPUs, then the merge kernel loads the other GPUs' "
+                                        "records over NVLink",
+                        "all-gather": "one NCCL all-gather of the packed records, then the merge kernel"}[merger.mode]
     if world > 1:
         t = torch.tensor([float(kv_bytes)], dtype=torch.float64, device=dev)
         dist.all_reduce(t)

@@ -171,6 +171,21 @@ NVFP4_MLA_API int nvfp4_mla_combine_strided(const float* o_part, const float* ls
 NVFP4_MLA_API int nvfp4_mla_combine_records(const float* const* records, int parts, int64_t rows, void* out, float* out_f32,
                                             float* lse, void* stream);
 
+/* nvfp4_mla_combine_records with the hand-shake between the GPUs inside the kernel, so that no barrier has to be
+ * launched in front of it. GPU `rank` (0 <= rank < parts) owns an array of `parts` 32-bit words that every GPU can
+ * write (flags[g] = address, in this process, of GPU g's array; flags is a HOST array), zero before the first call.
+ * The call announces "my record of step `epoch` is written" by storing `epoch` into word `rank` of every GPU's array,
+ * waits until all `parts` words of its own array carry `epoch` or a later one, and then merges. Every GPU makes the
+ * same sequence of calls with epoch = 1, 2, 3, ... (wrap-around is handled). A GPU may overwrite the record it
+ * announced at step s once its own call of step s + 1 has completed (work queued behind that call on the same stream
+ * qualifies): every GPU has finished reading step s by then, so two records that alternate are enough. The
+ * wait gives up after wait_us microseconds (> 0): the kernel then raises status 4 (peer time-out) in *status (device
+ * int, may be NULL; the larger of the old and new value is kept) and merges whatever the records hold, so the
+ * context stays usable. The reference is single-GPU: no counterpart. */
+NVFP4_MLA_API int nvfp4_mla_combine_records_signalled(const float* const* records, uint32_t* const* flags, int rank,
+                                                      uint32_t epoch, int64_t wait_us, int parts, int64_t rows, void* out,
+                                                      float* out_f32, float* lse, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,7 +8,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["decode", "dequantize", "decode_partial", "combine", "combine_packed", "combine_records", "workspace_status", "quantize_append_paged_mla_kv_cache",
+__all__ = ["decode", "dequantize", "decode_partial", "combine", "combine_packed", "combine_records", "combine_records_signalled", "workspace_status", "quantize_append_paged_mla_kv_cache",
            "get_batch_indices_positions"]
 __version__ = "0.1.0"
 
@@ -185,6 +185,34 @@ def combine_records(record_ptrs, rows, device, out_dtype=torch.bfloat16):
         _lib.check(lib.nvfp4_mla_combine_records(
             ptrs, len(record_ptrs), rows, _ptr(out) if out_dtype == torch.bfloat16 else None,
             _ptr(out) if out_dtype == torch.float32 else None, None, torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
+def combine_records_signalled(record_ptrs, flag_ptrs, rank, epoch, rows, device, out_dtype=torch.bfloat16, status=None,
+                              wait_us=2_000_000):
+    """``combine_records`` with the hand-shake between the GPUs inside the merge kernel (no barrier in front of it).
+    ``flag_ptrs[g]`` is the address, in this process, of GPU ``g``'s array of ``len(record_ptrs)`` uint32 words (zero
+    before the first call); the call announces this GPU's record of step ``epoch`` (1, 2, 3, ... on every GPU alike) in
+    word ``rank`` of every array, waits at most ``wait_us`` microseconds for the other GPUs' announcements and merges.
+    ``status``: int32 CUDA tensor of one element that receives 4 when the wait ran out (the output is then not to be
+    used). Returns ``[rows, 512]`` in ``out_dtype`` on ``device``."""
+    import ctypes
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"out_dtype must be bfloat16 or float32, got {out_dtype}")
+    if len(flag_ptrs) != len(record_ptrs):
+        raise ValueError("one flag array per record")
+    dev = torch.device(device)
+    if status is not None and not (status.is_cuda and status.dtype == torch.int32 and status.numel() >= 1):
+        raise RuntimeError("status must be an int32 CUDA tensor")
+    out = torch.empty(rows, CKV, dtype=out_dtype, device=dev)
+    recs = (ctypes.c_void_p * len(record_ptrs))(*[int(p) for p in record_ptrs])
+    flags = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        _lib.check(lib.nvfp4_mla_combine_records_signalled(
+            recs, flags, int(rank), int(epoch) & 0xFFFFFFFF, int(wait_us), len(record_ptrs), rows,
+            _ptr(out) if out_dtype == torch.bfloat16 else None, _ptr(out) if out_dtype == torch.float32 else None, None,
+            _ptr(status), torch.cuda.current_stream(dev).cuda_stream))
     return out
 
 

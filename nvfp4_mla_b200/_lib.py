@@ -8,7 +8,7 @@ import pathlib
 
 LIB_PATH = pathlib.Path(__file__).resolve().parent / "libnvfp4_mla_b200.so"
 
-_vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+_vp, _i32, _i64, _f32, _u32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_uint32
 
 # name -> (restype, argtypes); mirrors include/nvfp4_mla_b200.h
 SIGNATURES = {
@@ -28,6 +28,7 @@ SIGNATURES = {
     "nvfp4_mla_combine": (_i32, [_vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp]),
     "nvfp4_mla_combine_strided": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "nvfp4_mla_combine_records": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp]),
+    "nvfp4_mla_combine_records_signalled": (_i32, [_vp, _vp, _i32, _u32, _i64, _i32, _i64, _vp, _vp, _vp, _vp, _vp]),
     "nvfp4_mla_quantize_append": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _f32, _f32,
                                          _vp, _vp]),
 }

@@ -528,6 +528,36 @@ int nvfp4_mla_combine_records(const float* const* records, int parts, int64_t ro
   return 0;
 }
 
+int nvfp4_mla_combine_records_signalled(const float* const* records, uint32_t* const* flags, int rank, uint32_t epoch,
+                                        int64_t wait_us, int parts, int64_t rows, void* out, float* out_f32, float* lse,
+                                        int* status, void* stream) {
+  g_error[0] = 0;
+  MLA_CHECK(parts > 0 && rows > 0, "parts and rows must be positive (every GPU has to run the hand-shake)");
+  MLA_CHECK(parts <= mla::kCombineMaxRecords, "at most %d records, got %d", mla::kCombineMaxRecords, parts);
+  MLA_CHECK(rank >= 0 && rank < parts, "rank %d outside [0, %d)", rank, parts);
+  MLA_CHECK(wait_us > 0, "wait_us must be positive: an unbounded wait is not offered");
+  MLA_CHECK(records && flags, "null pointer argument");
+  MLA_CHECK(out || out_f32 || lse, "at least one of out, out_f32 and lse must be given");
+  MLA_CHECK(aligned(out, 8) && aligned(out_f32, 16), "out_f32 must be 16-byte, out 8-byte aligned");
+  MLA_CHECK(aligned(status, 4), "status must be 4-byte aligned");
+  MLA_CHECK(rows < (int64_t(1) << 31), "rows must be below 2^31");
+  mla::RecordPtrs recs = {};
+  mla::FlagPtrs fl = {};
+  for (int i = 0; i < parts; ++i) {
+    MLA_CHECK(records[i] && aligned(records[i], 16), "record %d is null or not 16-byte aligned", i);
+    MLA_CHECK(flags[i] && aligned(flags[i], 4), "flag array %d is null or not 4-byte aligned", i);
+    recs.p[i] = records[i], fl.p[i] = flags[i];
+  }
+  const unsigned long long wait_ns = (unsigned long long)wait_us * 1000ull;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (rows <= 296)
+    mla::mla_combine_records_signalled_kernel<4><<<unsigned(rows), 512, 0, st>>>(recs, fl, rank, epoch, wait_ns, parts, rows, out, out_f32, lse, status);
+  else
+    mla::mla_combine_records_signalled_kernel<1><<<unsigned(rows), 128, 0, st>>>(recs, fl, rank, epoch, wait_ns, parts, rows, out, out_f32, lse, status);
+  MLA_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int nvfp4_mla_combine(const float* o_part, const float* lse_part, int parts, int64_t rows, void* out, float* out_f32, float* lse,
                       void* stream) {
   return nvfp4_mla_combine_strided(o_part, lse_part, parts, rows, rows * mla::CKV, rows, out, out_f32, lse, stream);

@@ -55,6 +55,7 @@ enum Status : int {
   kWaitTimeout = 1,   // a bounded wait inside the decode kernel gave up
   kBadSchedule = 2,   // schedule kernel: batch * splits exceeds its scan capacity
   kBadPage = 3,       // a page id of a request's live range lies outside [0, num_pages): its rows were not loaded
+  kPeerTimeout = 4,   // cross-GPU merge: another GPU's record was not announced within the wait limit
 };
 
 }  // namespace mla

@@ -302,4 +302,50 @@ mla_combine_records_kernel(RecordPtrs recs, int parts, long long rows, void* out
       out_f32, lse_out, weights, partial);
 }
 
+// The same merge with the hand-shake between the GPUs inside the kernel: no barrier launch in front of it. GPU `rank`
+// owns a word per GPU (`flags.p[rank][r]` is written by GPU r alone); the first CTA of each GPU's merge stores the
+// step's epoch into its word on every GPU (release at system scope: the record this GPU's earlier kernels wrote is
+// visible to whoever then reads the word), every CTA polls this GPU's own words until all of them carry the epoch,
+// and then reads the records. Epochs only grow, so a GPU that is one step ahead passes the test as well; it cannot be
+// two ahead, because its next merge waits for this GPU's next epoch. The wait is bounded by `wait_ns` of the global
+// timer: when it runs out the CTA raises kPeerTimeout in *status and merges what is there, so that the context stays
+// usable and the host learns of the missing GPU from the status word.
+struct FlagPtrs {
+  uint32_t* p[kCombineMaxRecords];
+};
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+template <int GROUPS>
+__global__ void __launch_bounds__(128 * GROUPS)
+mla_combine_records_signalled_kernel(RecordPtrs recs, FlagPtrs flags, int rank, uint32_t epoch, unsigned long long wait_ns,
+                                     int parts, long long rows, void* out_bf16, float* out_f32, float* lse_out, int* status) {
+  __shared__ float weights[kCombineMaxParts];
+  __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
+  if (int(threadIdx.x) < parts) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[threadIdx.x] + rank), "r"(epoch) : "memory");
+    }
+    const uint32_t* mine = flags.p[rank] + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (int(v - epoch) >= 0) break;
+      if (global_timer_ns() - t0 > wait_ns) {
+        if (status) atomicMax(status, int(kPeerTimeout));
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const long long row = blockIdx.x;
+  merge_row<GROUPS>(
+      parts, [&](int i) { return recs.p[i][rows * CKV + row]; }, [&](int i) { return recs.p[i] + row * CKV; }, row, out_bf16,
+      out_f32, lse_out, weights, partial);
+}
+
 }  // namespace mla

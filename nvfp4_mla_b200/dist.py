@@ -68,36 +68,67 @@ class PartialMerger:
     decode kernels write directly (``o`` and ``lse`` are views of it). Two ways to merge the ranks' records:
 
     * **peer reads** (default where it can be set up): the records live in symmetric memory, every rank maps every
-      other rank's buffer, and after one barrier between the GPUs the library's merge kernel reads the peers' records
-      over NVLink with ordinary loads where their owners wrote them: no collective, no copy. Two records alternate
-      from step to step, so that a rank that is one step ahead never writes what a slower rank still reads (the barrier
-      of step s + 1 is passed only when every rank has finished the merge of step s).
+      other rank's buffer, and the library's merge kernel reads the peers' records over NVLink with ordinary loads
+      where their owners wrote them: no collective, no copy. The ranks' hand-shake ("my record of this step is
+      written") runs inside the merge kernel itself (``nvfp4_mla_combine_records_signalled``: one flag word per pair of
+      ranks in symmetric memory, a bounded wait), or, with ``peer="barrier"``, as symmetric memory's own barrier launched
+      in front of the plain merge kernel. Two records alternate from step to step, so that a rank that is one step
+      ahead never writes what a slower rank still reads (the hand-shake of step s + 1 is passed only when every rank
+      has finished the merge of step s).
     * **all-gather** (``peer=False``, or when symmetric memory is unavailable: one GPU, a gloo group, an older torch):
       ONE ``all_gather_into_tensor`` of the record per step into ``recv [world, record]``, merged where it landed.
 
-    The exchange is latency-bound either way (513 KiB per rank at B=2, H=128)."""
+    The exchange is latency-bound either way (513 KiB per rank at B=2, H=128). ``check()`` synchronises and raises if a
+    hand-shake ever ran out of time (a rank that never arrived)."""
 
-    def __init__(self, batch, heads, device, group=None, peer=None):
+    def __init__(self, batch, heads, device, group=None, peer=None, wait_us=2_000_000):
         import os
         self.group, self.rows, self.shape = group, batch * heads, (batch, heads)
         self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
         self.device = torch.device(device)
+        self.wait_us = wait_us
         n = self.rows * 513
-        self.step, self.handles = 0, None
+        self.step, self.handles, self.flag_ptrs, self.status = 0, None, None, None
         if peer is None:
-            peer = os.environ.get("NVFP4_MLA_PEER_MERGE", "1") != "0"
+            env = os.environ.get("NVFP4_MLA_PEER_MERGE", "1")
+            peer = False if env == "0" else ("barrier" if env == "barrier" else True)
         if peer and self.world > 1 and self.world <= 16 and self.device.type == "cuda":
             try:
                 import torch.distributed._symmetric_memory as symm
+                g = group if group is not None else dist.group.WORLD
                 bufs = [symm.empty(n, dtype=torch.float32, device=self.device) for _ in range(2)]
-                self.handles = [symm.rendezvous(b, group if group is not None else dist.group.WORLD) for b in bufs]
+                self.handles = [symm.rendezvous(b, g) for b in bufs]
                 self.records = bufs
                 self.peer_ptrs = [[int(h.buffer_ptrs[r]) for r in range(self.world)] for h in self.handles]
+                if peer != "barrier":
+                    self.flags = symm.empty(32, dtype=torch.int32, device=self.device)
+                    self.flags.zero_()
+                    fh = symm.rendezvous(self.flags, g)
+                    self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+                    torch.cuda.synchronize(self.device)
+                    dist.barrier(group)  # every rank's words are zero before anyone announces a step
+                    self.flag_ptrs = [int(fh.buffer_ptrs[r]) for r in range(self.world)]
+                    self._flag_handle = fh
             except Exception:  # no symmetric memory on this system / backend: the collective does the exchange
-                self.handles = None
+                self.handles, self.flag_ptrs = None, None
         if self.handles is None:
             self.records = [torch.empty(n, dtype=torch.float32, device=device)]
             self.recv = torch.empty(self.world, n, dtype=torch.float32, device=device)
+
+    @property
+    def mode(self):
+        """How the ranks' records meet: "peer-signal", "peer-barrier" or "all-gather"."""
+        if self.handles is None:
+            return "all-gather"
+        return "peer-signal" if self.flag_ptrs is not None else "peer-barrier"
+
+    def check(self):
+        """Synchronises and raises if a hand-shake of the in-kernel merge gave up waiting for another rank."""
+        if self.status is not None:
+            st = int(self.status.item())
+            if st:
+                raise RuntimeError(f"cross-GPU merge: status {st} (4 = a rank's record was not announced within {self.wait_us} us)")
 
     @property
     def send(self):
@@ -116,10 +147,14 @@ class PartialMerger:
         """Merges the ranks' records of the current step; every rank returns the full ``[batch, heads, 512]`` result.
         ``combine_packed(recv, rows, out_dtype)`` replaces the library's kernel on the all-gather path (tests)."""
         if self.handles is not None and combine_packed is None:
-            from . import combine_records
+            from . import combine_records, combine_records_signalled
             k = self.step % 2
-            self.handles[k].barrier()  # every rank's record of this step is written and visible
-            out = combine_records(self.peer_ptrs[k], self.rows, self.device, out_dtype)
+            if self.flag_ptrs is not None:  # announce, wait and merge in one kernel
+                out = combine_records_signalled(self.peer_ptrs[k], self.flag_ptrs, self.rank, self.step + 1, self.rows,
+                                                self.device, out_dtype, self.status, self.wait_us)
+            else:
+                self.handles[k].barrier()  # every rank's record of this step is written and visible
+                out = combine_records(self.peer_ptrs[k], self.rows, self.device, out_dtype)
             self.step += 1
             return out.view(*self.shape, 512)
         if combine_packed is None:

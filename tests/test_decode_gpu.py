@@ -125,6 +125,40 @@ def test_combine_records_equals_packed_merge():
         mla.combine_records([r.data_ptr() for r in recs] * 4, rows, "cuda")  # 20 records: over the limit of 16
 
 
+@pytest.mark.parametrize("rows", [48, 400])
+def test_combine_records_signalled_on_one_gpu(rows):
+    """The merge kernel that carries the GPUs' hand-shake, driven as "GPU 0 of 3" on one device: the words the other
+    GPUs would write are set by the host. With all of them announced the result is the plain merge, bit for bit, and
+    the kernel has announced itself in word 0 of every GPU's array; with one GPU missing the bounded wait runs out,
+    status 4 is raised, and the context stays usable (a wait that ends by itself: nothing hangs or faults)."""
+    g = torch.Generator().manual_seed(6)
+    parts = 3
+    recs = [torch.empty(rows * 513, dtype=torch.float32, device="cuda") for _ in range(parts)]
+    for r in recs:
+        r[:rows * 512] = torch.randn(rows * 512, generator=g).cuda()
+        r[rows * 512:] = (torch.randn(rows, generator=g) * 3).cuda()
+    want = mla.combine_records([r.data_ptr() for r in recs], rows, "cuda", torch.float32)
+    flags = [torch.zeros(parts, dtype=torch.int32, device="cuda") for _ in range(parts)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ptrs, fptrs = [r.data_ptr() for r in recs], [f.data_ptr() for f in flags]
+    epoch = 7
+    flags[0][1], flags[0][2] = epoch, epoch + 1  # GPU 2 is one step ahead: allowed
+    got = mla.combine_records_signalled(ptrs, fptrs, 0, epoch, rows, "cuda", torch.float32, status, wait_us=500_000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(got, want)
+    assert [int(f[0]) for f in flags] == [epoch] * parts and int(flags[1][1]) == 0
+    # GPU 1 never announces the next step
+    flags[0][2] = epoch + 1
+    mla.combine_records_signalled(ptrs, fptrs, 0, epoch + 1, rows, "cuda", torch.float32, status, wait_us=2_000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4
+    assert torch.equal(mla.combine_records(ptrs, rows, "cuda", torch.float32), want)  # the context is intact
+    with pytest.raises(RuntimeError):
+        mla.combine_records_signalled(ptrs, fptrs, 3, epoch, rows, "cuda")  # rank outside [0, parts)
+    with pytest.raises(RuntimeError):
+        mla.combine_records_signalled(ptrs, fptrs, 0, epoch, rows, "cuda", wait_us=0)  # an unbounded wait is not offered
+
+
 @pytest.mark.parametrize("parts,rows_shape", [(3, (2, 16)), (9, (40, 16)), (70, (2, 16)), (70, (40, 16))])
 def test_combine_ignores_empty_partials(parts, rows_shape):
     """A partial of weight 0 (lse = -inf) may hold anything, NaN included: it must not reach the result. Covers the rows

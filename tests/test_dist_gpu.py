@@ -1,7 +1,8 @@
 """Multi-GPU paths on real devices: two NCCL ranks (skipped on a box with fewer than two GPUs).
 
 Sequence sharding: every rank holds a contiguous slice of each request's pages, decodes it with the normal split-KV
-kernel in partial mode, and the (o, lse) pairs are all-gathered and merged with the library's combine kernel; the result
+kernel in partial mode, and the (o, lse) pairs are merged with the library's combine kernels (peers' records read in place with the hand-shake in
+the merge kernel or a barrier in front of it, or one all-gather); the result
 must match whole-sequence attention (oracle) within the bf16-mode tolerances. Batch sharding: each rank decodes its own
 requests; no collective."""
 import math
@@ -67,18 +68,25 @@ def _rank(rank, world, port, ret):
                                             c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32)
         torch.cuda.synchronize()
         err_seq = float(np.abs(out.cpu().numpy() - want).max())
-        # the same through preallocated buffers, both ways of merging: the peers' records read where they were written
-        # (symmetric memory; falls back to the collective by itself where that cannot be set up) and one packed
-        # all-gather per step. Three steps each: the buffers are reused, the peer records alternate.
+        # the same through preallocated buffers, every way of merging: the peers' records read where they were written
+        # (symmetric memory, hand-shake inside the merge kernel or as a barrier in front of it; falls back to the
+        # collective by itself where that cannot be set up) and one packed all-gather per step. Five steps each: the
+        # buffers are reused, the peer records alternate.
         modes = []
-        for peer in (True, False):
+        for peer in (True, "barrier", False):
             mg = mdist.PartialMerger(len(c.kv_lens_list), 16, dev, peer=peer)
-            modes.append("peer" if mg.handles is not None else "all-gather")
-            for _ in range(3):
+            modes.append(mg.mode)
+            for step in range(5):
+                if rank == step % world:
+                    torch.cuda._sleep(2_000_000)  # about a millisecond: the ranks reach the merge at different times
                 out = mdist.decode_sequence_sharded(c.q_nope.to(dev), c.q_pe.to(dev), ckv, sf, kpe, pt, lens, SM_SCALE, c.ckv_scale,
                                                     c.kpe_scale, max_kv_len=int(lens.max()), out_dtype=torch.float32, merger=mg)
-                torch.cuda.synchronize()
-                err_seq = max(err_seq, float(np.abs(out.cpu().numpy() - want).max()))
+                if step % 2:  # odd steps are queued behind the even ones without a host synchronisation in between
+                    torch.cuda.synchronize()
+                    mg.check()
+                    err_seq = max(err_seq, float(np.abs(out.cpu().numpy() - want).max()))
+            torch.cuda.synchronize()
+            mg.check()
         if rank == 0:
             print("merge modes exercised:", modes)
         # ---- batch sharded: this rank's requests only
