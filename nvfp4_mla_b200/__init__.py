@@ -189,7 +189,7 @@ def combine_records(record_ptrs, rows, device, out_dtype=torch.bfloat16):
 
 
 def combine_records_signalled(record_ptrs, flag_ptrs, rank, epoch, rows, device, out_dtype=torch.bfloat16, status=None,
-                              wait_us=2_000_000):
+                              wait_us=10_000_000):
     """``combine_records`` with the hand-shake between the GPUs inside the merge kernel (no barrier in front of it).
     ``flag_ptrs[g]`` is the address, in this process, of GPU ``g``'s array of ``len(record_ptrs)`` uint32 words (zero
     before the first call); the call announces this GPU's record of step ``epoch`` (1, 2, 3, ... on every GPU alike) in

@@ -10,8 +10,8 @@ Two shardings follow the path's natural units (the reference itself is single-GP
   (request, head) an output normalised by its own softmax sum and a log2-domain log-sum-exp, exactly the pair the
   in-GPU split merge consumes (reference contract: nvfp4_mla/csrc/mla_decode.cu:478-492). The pairs (513 KiB per GPU at
   B=2, H=128) are merged on every rank with the library's combine kernel, which reads the other GPUs' records over
-  NVLink where they were written (symmetric memory, one barrier per step), or after one NCCL all-gather where that
-  cannot be set up.
+  NVLink where they were written (symmetric memory; the ranks' hand-shake runs inside that kernel), or after one NCCL
+  all-gather where that cannot be set up.
 """
 import math
 
@@ -81,7 +81,7 @@ class PartialMerger:
     The exchange is latency-bound either way (513 KiB per rank at B=2, H=128). ``check()`` synchronises and raises if a
     hand-shake ever ran out of time (a rank that never arrived)."""
 
-    def __init__(self, batch, heads, device, group=None, peer=None, wait_us=2_000_000):
+    def __init__(self, batch, heads, device, group=None, peer=None, wait_us=10_000_000):
         import os
         self.group, self.rows, self.shape = group, batch * heads, (batch, heads)
         self.world = dist.get_world_size(group)
@@ -175,8 +175,9 @@ def decode_sequence_sharded(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, pa
 
     ``ckv_cache`` / ``ckv_sf_cache`` / ``kpe_cache`` / ``page_table`` / ``kv_lens`` describe the LOCAL slice (local page
     ids, local token counts; a rank may hold zero tokens of a request); the queries are replicated. Returns the full
-    ``[batch, heads, 512]`` output on every rank. Pass a ``PartialMerger`` to reuse its buffers across steps (one
-    packed all-gather per step); without one the (o, lse) pair is gathered into fresh tensors."""
+    ``[batch, heads, 512]`` output on every rank. Pass a ``PartialMerger`` to reuse its buffers across steps (peer
+    reads of the records, or one packed all-gather per step); without one the (o, lse) pair is gathered into fresh
+    tensors."""
     from . import decode_partial
     if merger is not None:
         decode_partial(q_nope, q_pe, ckv_cache, ckv_sf_cache, kpe_cache, page_table, kv_lens, sm_scale, ckv_scale, kpe_scale,
