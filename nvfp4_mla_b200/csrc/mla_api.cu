@@ -277,8 +277,15 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
   float* o_part = reinterpret_cast<float*>(ws + L.o_part);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  mla::mla_schedule_kernel<<<1, mla::kSchedThreads, 0, st>>>(kv_lens, pb, header, cta_range, item_range, segs);
-  MLA_CUDA(cudaGetLastError());
+  // The 16-bit kernel derives its schedule by itself when one thread per (request, split) pair is enough; the other
+  // kernels, and larger batches, read the output of the schedule kernel.
+  const long long bz = (long long)pb.batch * pb.splits;
+  const bool inline_sched = precision == NVFP4_MLA_PRECISION_BF16 && bz <= mla::kVtThreads &&
+                            bz * ((pb.chunk + mla::TILE - 1) / mla::TILE + 1) * pb.head_groups < (1ll << 31);  // its 32-bit arithmetic
+  if (!inline_sched) {
+    mla::mla_schedule_kernel<<<1, mla::kSchedThreads, 0, st>>>(kv_lens, pb, header, cta_range, item_range, segs);
+    MLA_CUDA(cudaGetLastError());
+  }
 
   mla::DecodeParams P;
   P.q_nope = static_cast<const __nv_bfloat16*>(q_nope), P.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
@@ -287,6 +294,8 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
   P.sf_swz_mask = page_size >= slot_rows ? 1u : 0u, P.kpe_swz_mask = page_size >= slot_rows ? 3u : 0u;
   P.sm_scale_log2 = sm_scale * 1.4426950408889634f, P.ckv_scale = ckv_scale, P.kpe_scale = kpe_scale;
   P.cta_range = cta_range, P.segs = segs, P.lse_part = lse_part, P.o_part = o_part, P.header = header;
+  P.kv_lens = kv_lens, P.pb = pb, P.inline_sched = inline_sched ? 1 : 0, P.item_range = item_range;
+  P.cta_range_out = cta_range, P.segs_out = segs;
   Profile* prof = g_profile && g_profile->used < int(g_profile->start.size()) ? g_profile : nullptr;
   if (prof) MLA_CUDA(cudaEventRecord(prof->start[prof->used], st));
   MLA_CUDA(launch_dependent_cluster(decode_kernel(precision, hpc), dim3(pb.n_cta * ctas_per_unit(hpc)),
@@ -298,11 +307,13 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
   const unsigned rows = unsigned(batch) * unsigned(heads);
   if (rows <= 2u * unsigned(d->sm_count))
     MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel<4>, dim3(rows), dim3(512), 0, st, pb,
-                              static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
+                              static_cast<const int2*>(item_range), static_cast<const int*>(inline_sched ? kv_lens : nullptr),
+                              static_cast<const float*>(lse_part),
                               static_cast<const float*>(o_part), out, out_f32, lse));
   else
     MLA_CUDA(launch_dependent(mla::mla_combine_sched_kernel<1>, dim3(rows), dim3(128), 0, st, pb,
-                              static_cast<const int2*>(item_range), static_cast<const float*>(lse_part),
+                              static_cast<const int2*>(item_range), static_cast<const int*>(inline_sched ? kv_lens : nullptr),
+                              static_cast<const float*>(lse_part),
                               static_cast<const float*>(o_part), out, out_f32, lse));
   return 0;
 }

@@ -50,6 +50,14 @@ struct Problem {
   __host__ __device__ long long items() const { return (long long)batch * splits * head_groups; }
 };
 
+// 128-token tiles of (request, split) pair bz = b * splits + z: the split covers tokens [z * chunk, (z + 1) * chunk) of the request.
+__device__ __forceinline__ int sched_tiles(const int* kv_lens, const Problem& pb, int bz) {
+  const int b = bz / pb.splits, z = bz % pb.splits;
+  long long n = (long long)kv_lens[b] - (long long)z * pb.chunk;
+  n = n < 0 ? 0 : (n > pb.chunk ? pb.chunk : n);
+  return int((n + TILE - 1) / TILE);
+}
+
 enum Status : int {
   kOk = 0,
   kWaitTimeout = 1,   // a bounded wait inside the decode kernel gave up

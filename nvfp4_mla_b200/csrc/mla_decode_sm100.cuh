@@ -67,6 +67,14 @@ struct DecodeParams {
   float* lse_part;
   float* o_part;
   int* header;
+  // Schedule computed by the decode kernel itself (16-bit kernel, batch * splits up to its thread count): every CTA
+  // scans the lengths and derives its own items; cta_range and segs are then unused and no schedule kernel runs.
+  const int* kv_lens;
+  Problem pb;
+  int inline_sched;
+  int2* item_range;  // written by the CTA that holds an item's first tile (read by the combine kernel)
+  int2* cta_range_out;
+  Seg* segs_out;
 };
 
 template <int N, int RAW_SLOTS, bool P8>

@@ -225,25 +225,35 @@ __device__ __forceinline__ void merge_row(int n_parts, LseOf lse_of, OOf o_of, l
 // Partials addressed through the schedule (what the decode kernel wrote).
 template <int GROUPS>
 __global__ void __launch_bounds__(128 * GROUPS)
-mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const float* __restrict__ lse_part,
-                         const float* __restrict__ o_part, void* out_bf16, float* out_f32, float* lse_out) {
+mla_combine_sched_kernel(Problem pb, const int2* __restrict__ item_range, const int* __restrict__ kv_lens,
+                         const float* __restrict__ lse_part, const float* __restrict__ o_part, void* out_bf16, float* out_f32,
+                         float* lse_out) {
   __shared__ int slots[kCombineMaxParts];
   __shared__ int n_parts_s;
   __shared__ float weights[kCombineMaxParts];
   __shared__ float4 partial[GROUPS > 1 ? (GROUPS - 1) * 128 : 1];
   // Launched as a programmatic dependent of the decode kernel, which lets its dependents start only after it has seen
-  // the schedule kernel complete: the schedule's output (item_range) may be read at once, the partials only after the wait.
+  // the schedule kernel complete: the schedule kernel's output (item_range) may be read at once, the partials (and an
+  // item_range written by the decode kernel itself) only after the wait.
   const long long row = blockIdx.x;
   const int b = int(row / pb.heads), h = int(row % pb.heads);
   const int N = pb.heads_per_cta, hg = h / N, n = h % N;
   if (threadIdx.x < 32) {  // enumerate the row's partial slots: splits z, CTAs c0..c1 of item (b, z, hg)
+    // Without a schedule kernel (kv_lens given: the decode kernel derived its schedule by itself) the CTA that holds
+    // the first tile of an item has written the item's CTA range; an item without tiles has none, which the lengths tell.
     int count = 0;
     for (int z0 = 0; z0 < pb.splits; z0 += 32) {
       const int z = z0 + threadIdx.x;
       int c0 = 0, c1 = -1;
       long long w = 0;
-      if (z < pb.splits) {
-        w = ((long long)b * pb.splits + z) * pb.head_groups + hg;
+      if (z < pb.splits) w = ((long long)b * pb.splits + z) * pb.head_groups + hg;
+      if (kv_lens) {
+        // the two loads are independent (a stale range is read and dropped): one memory latency, not two in a row
+        const int t = z < pb.splits ? sched_tiles(kv_lens, pb, b * pb.splits + z) : 0;
+        ptx::grid_dependency_wait();  // item_range is the decode kernel's output here
+        const int2 r = z < pb.splits ? item_range[w] : make_int2(0, -1);
+        if (t > 0) c0 = r.x, c1 = r.y;
+      } else if (z < pb.splits) {
         const int2 r = item_range[w];
         c0 = r.x, c1 = r.y;
       }
