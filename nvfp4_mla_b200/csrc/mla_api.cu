@@ -277,10 +277,10 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
   float* o_part = reinterpret_cast<float*>(ws + L.o_part);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  // The 16-bit kernel derives its schedule by itself when one thread per (request, split) pair is enough; the other
-  // kernels, and larger batches, read the output of the schedule kernel.
+  // The decode kernels derive their schedule by themselves when one thread per (request, split) pair is enough; larger
+  // batches read the output of the schedule kernel.
   const long long bz = (long long)pb.batch * pb.splits;
-  const bool inline_sched = precision == NVFP4_MLA_PRECISION_BF16 && bz <= mla::kVtThreads &&
+  const bool inline_sched = bz <= (long long)decode_threads(precision, hpc) &&
                             bz * ((pb.chunk + mla::TILE - 1) / mla::TILE + 1) * pb.head_groups < (1ll << 31);  // its 32-bit arithmetic
   if (!inline_sched) {
     mla::mla_schedule_kernel<<<1, mla::kSchedThreads, 0, st>>>(kv_lens, pb, header, cta_range, item_range, segs);

@@ -600,7 +600,9 @@ mla_decode_hm_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
   ptx::tc_fence_after_sync();
   ptx::grid_dependency_wait();
-  ptx::grid_launch_dependents();  // after the wait: the combine kernel reads the schedule kernel's output as soon as it starts
+  ptx::grid_launch_dependents();  // after the wait: the combine kernel reads a schedule kernel's output as soon as it starts
+  // the staging buffers are filled by this CTA's own loads only (the peer writes to kv), so the first one is free until then
+  if (P.inline_sched) publish_own_schedule<kHmThreads>(reinterpret_cast<int*>(s.raw[0]), P, blockIdx.x >> 1);
 
   // 640 threads are launched with 96 registers each (65536 / 640 rounded down to a multiple of 8); that allocation is
   // the pool the role budgets must fit in, warp group by warp group (4 warps each): 2 softmax, 2 convert, 1 issue.

@@ -77,6 +77,75 @@ struct DecodeParams {
   Seg* segs_out;
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// The schedule, derived by every decode CTA (or CTA pair: `unit`) for itself, so that no schedule kernel runs in
+// front of the decode kernel. Thread bz takes the (request, split) pair bz; a block scan gives the exclusive prefix
+// of their tile counts; the unit's piece [unit q, (unit + 1) q) of the flattened (pair, head group) tile range gives
+// its items. The unit's part of the schedule goes to the workspace in the form mla_schedule_kernel writes (its
+// cta_range entry, one Seg per item of its range in slot unit + w, and the CTA range of every item whose first tile it
+// holds, for the combine kernel), and the roles read it from there as they do after a schedule kernel: writes and
+// reads of one CTA, ordered by the CTA-wide barrier (the two CTAs of a pair write the same values). 32-bit arithmetic:
+// the host takes this path only when batch * splits <= THREADS and the flattened tile count is below 2^31.
+// `scratch`: THREADS + THREADS / 32 + 4 ints of shared memory that nothing else uses yet (a staging buffer).
+// ---------------------------------------------------------------------------------------------------------------
+template <int THREADS>
+__device__ __forceinline__ void publish_own_schedule(int* scratch, const DecodeParams& P, int unit) {
+  int* pre = scratch;                     // [BZ + 1] exclusive prefix of the tiles of the (request, split) pairs
+  int* warp_tot = scratch + THREADS + 1;  // [THREADS / 32]
+  int* misc = warp_tot + THREADS / 32;    // first item, last item + 1, tiles per unit
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int BZ = P.pb.batch * P.pb.splits, HG = P.pb.head_groups;
+  const int t = tid < BZ ? sched_tiles(P.kv_lens, P.pb, tid) : 0;
+  int incl = t;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(~0u, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int base = 0, total = 0;
+  for (int i = 0; i < THREADS / 32; ++i) {
+    const int v = warp_tot[i];
+    base += i < warp ? v : 0, total += v;
+  }
+  const int mine = base + incl - t;
+  if (tid < BZ) pre[tid] = mine;
+  const uint32_t T = uint32_t(total) * uint32_t(HG);
+  const uint32_t q = T > 0 ? (T + P.pb.n_cta - 1) / P.pb.n_cta : 1u;
+  const uint32_t g0 = uint32_t(unit) * q, g1 = g0 + q < T ? g0 + q : T;
+  if (tid == 0) {
+    pre[BZ] = total, misc[2] = int(q);
+    if (g0 >= g1) misc[0] = 0, misc[1] = 0;
+  }
+  if (g0 < g1 && t > 0) {
+    const uint32_t lo = uint32_t(HG) * uint32_t(mine), hi = lo + uint32_t(HG) * uint32_t(t);
+    if (g0 >= lo && g0 < hi) misc[0] = tid * HG + int((g0 - lo) / uint32_t(t));
+    if (g1 - 1 >= lo && g1 - 1 < hi) misc[1] = tid * HG + int((g1 - 1 - lo) / uint32_t(t)) + 1;
+  }
+  __syncthreads();
+  const int2 range = make_int2(misc[0], misc[1]);
+  for (int w = range.x + tid; w < range.y; w += THREADS) {
+    const int bz = w / HG, hg = w % HG, tw = pre[bz + 1] - pre[bz];
+    const int b = bz / P.pb.splits, z = bz % P.pb.splits;
+    Seg g;
+    g.b = b, g.hg = hg, g.tok0 = 0, g.ntiles = 0, g.tok_end = 0, g.w = w, g.cta = unit, g.pad = 0;
+    if (tw > 0) {
+      const uint32_t Pw = uint32_t(HG) * uint32_t(pre[bz]) + uint32_t(hg) * uint32_t(tw);
+      const uint32_t lo = (g0 > Pw ? g0 : Pw) - Pw, hi = (g0 + q < Pw + tw ? g0 + q : Pw + tw) - Pw;
+      if (hi > lo) {
+        if (lo == 0) P.item_range[w] = make_int2(unit, int((Pw + tw - 1) / q));
+        const int len = P.kv_lens[b];
+        const long long end = (long long)(z + 1) * P.pb.chunk;
+        g.tok0 = z * P.pb.chunk + int(lo) * TILE, g.ntiles = int(hi - lo), g.tok_end = int(end < len ? end : len);
+      }
+    }
+    P.segs_out[(long long)unit + w] = g;
+  }
+  if (tid == 0) P.cta_range_out[unit] = range;
+  __syncthreads();
+}
+
 template <int N, int RAW_SLOTS, bool P8>
 struct DecodeSmem {
   // Operand tiles, all with the 128-byte swizzle, one 128-byte row per token (V) or head (Q^T, P^T).
@@ -849,10 +918,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
-  ptx::grid_dependency_wait();  // the schedule kernel's output (and the previous call's use of the workspace) is settled
-  // The combine kernel may be scheduled from here on: it reads the schedule at once (settled, as this grid has just
-  // seen) and waits for this grid before it reads partials.
+  ptx::grid_dependency_wait();  // whatever precedes the call in the stream (the lengths' producer, a schedule kernel, the
+                                // previous call's use of the workspace) is settled
+  // The combine kernel may be scheduled from here on: it reads a schedule kernel's output at once (settled, as this
+  // grid has just seen) and waits for this grid before it reads partials.
   ptx::grid_launch_dependents();
+  if (P.inline_sched) publish_own_schedule<kDecodeThreads>(reinterpret_cast<int*>(s.raw[0]), P, blockIdx.x);
 
   // Each role lives entirely inside its own branch, so that the register budget set at the top of the branch
   // (setmaxnreg) governs the role's code: the light issue / producer warps hand registers to the softmax and convert
