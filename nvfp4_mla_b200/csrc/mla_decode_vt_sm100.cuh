@@ -94,11 +94,6 @@ struct VtSmem {
   uint64_t sc_full[kVtScRing], sc_free[kVtScRing];
   uint32_t tmem_base;
   int abort_flag;
-  // the CTA's own schedule: exclusive prefix of the tiles of the (request, split) pairs, its item range, tiles per CTA
-  int pre[kVtThreads + 1];
-  int warp_tot[kVtThreads / 32];
-  int2 range;
-  int sched_q;
 };
 constexpr size_t vt_smem_bytes() { return sizeof(VtSmem) + 1024; }
 
@@ -798,81 +793,6 @@ __device__ __forceinline__ void vt_softmax_role(VtSmem& s, const DecodeParams& P
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// The schedule, computed by every CTA for itself (no schedule kernel in front of the decode kernel): thread bz takes
-// the (request, split) pair bz, a block scan gives the exclusive prefix of their tile counts, and the CTA's piece
-// [c q, (c + 1) q) of the flattened (pair, head group) tile range gives its items. Same arithmetic as
-// mla_schedule_kernel, which remains for batch * splits beyond the thread count and for the other decode kernels.
-// ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void vt_inline_schedule(VtSmem& s, const DecodeParams& P) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int BZ = P.pb.batch * P.pb.splits, HG = P.pb.head_groups;
-  const int t = tid < BZ ? sched_tiles(P.kv_lens, P.pb, tid) : 0;
-  int incl = t;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int v = __shfl_up_sync(~0u, incl, o);
-    if (lane >= o) incl += v;
-  }
-  if (lane == 31) s.warp_tot[warp] = incl;
-  __syncthreads();
-  int base = 0, total = 0;
-  for (int i = 0; i < kVtThreads / 32; ++i) {
-    const int v = s.warp_tot[i];
-    base += i < warp ? v : 0, total += v;
-  }
-  const int pre = base + incl - t;
-  if (tid < BZ) s.pre[tid] = pre;
-  // 32-bit arithmetic: the host takes this path only when batch * splits * tiles per split * head groups is below 2^31
-  const uint32_t T = uint32_t(total) * uint32_t(HG);
-  const uint32_t q = T > 0 ? (T + gridDim.x - 1) / gridDim.x : 1u;
-  const uint32_t g0 = blockIdx.x * q, g1 = g0 + q < T ? g0 + q : T;
-  if (tid == 0) {
-    s.pre[BZ] = total, s.sched_q = int(q);
-    if (g0 >= g1) s.range = make_int2(0, 0);
-  }
-  if (g0 < g1 && t > 0) {
-    const uint32_t lo = uint32_t(HG) * uint32_t(pre), hi = lo + uint32_t(HG) * uint32_t(t);
-    if (g0 >= lo && g0 < hi) s.range.x = tid * HG + int((g0 - lo) / uint32_t(t));
-    if (g1 - 1 >= lo && g1 - 1 < hi) s.range.y = tid * HG + int((g1 - 1 - lo) / uint32_t(t)) + 1;
-  }
-  __syncthreads();
-}
-
-// The piece of item w that lies in this CTA's tile range (ntiles = 0: none, e.g. an empty request inside the range).
-__device__ __forceinline__ Seg vt_inline_seg(const VtSmem& s, const DecodeParams& P, int w);
-
-// The CTA's part of the schedule goes to the workspace in the form the schedule kernel writes (its cta_range entry,
-// one Seg per item of its range in slot cta + w, the CTA range of every item whose first tile it holds), and the roles
-// read it from there as they do after a schedule kernel: writes and reads of one CTA, ordered by the CTA-wide barrier.
-__device__ __forceinline__ void vt_publish_schedule(VtSmem& s, const DecodeParams& P) {
-  const int2 range = s.range;
-  for (int w = range.x + int(threadIdx.x); w < range.y; w += kVtThreads) P.segs_out[(long long)blockIdx.x + w] = vt_inline_seg(s, P, w);
-  if (threadIdx.x == 0) P.cta_range_out[blockIdx.x] = range;
-  __syncthreads();
-}
-
-// The CTA that holds the item's first tile also records which CTAs hold the item, for the combine kernel.
-__device__ __forceinline__ Seg vt_inline_seg(const VtSmem& s, const DecodeParams& P, int w) {
-  const int HG = P.pb.head_groups, bz = w / HG, hg = w % HG;
-  const int t = s.pre[bz + 1] - s.pre[bz], q = s.sched_q;
-  const int b = bz / P.pb.splits, z = bz % P.pb.splits;
-  Seg g;
-  g.b = b, g.hg = hg, g.tok0 = 0, g.ntiles = 0, g.tok_end = 0, g.w = w, g.cta = int(blockIdx.x), g.pad = 0;
-  if (t > 0) {
-    const long long Pw = (long long)HG * s.pre[bz] + (long long)hg * t;
-    const long long c0 = (long long)blockIdx.x * q, c1 = c0 + q;
-    const long long lo = (c0 > Pw ? c0 : Pw) - Pw, hi = (c1 < Pw + t ? c1 : Pw + t) - Pw;
-    if (hi > lo) {
-      if (lo == 0) P.item_range[w] = make_int2(int(blockIdx.x), int(uint32_t(Pw + t - 1) / uint32_t(q)));
-      const int len = P.kv_lens[b];
-      const long long end = (long long)(z + 1) * P.pb.chunk;
-      g.tok0 = z * P.pb.chunk + int(lo) * TILE, g.ntiles = int(hi - lo), g.tok_end = int(end < len ? end : len);
-    }
-  }
-  return g;
-}
-
-// ---------------------------------------------------------------------------------------------------------------
 // The CTA's segments are staged through shared memory in batches; every thread takes part in the two CTA-wide
 // barriers around a batch, whatever its role.
 // ---------------------------------------------------------------------------------------------------------------
@@ -933,10 +853,7 @@ mla_decode_vt_kernel(const __grid_constant__ CUtensorMap ckv_map, const __grid_c
   ptx::grid_dependency_wait();  // whatever precedes the call in the stream (the lengths' producer, the schedule kernel, the
                                 // previous call's use of the workspace) is settled
   ptx::grid_launch_dependents();
-  if (P.inline_sched) {
-    vt_inline_schedule(s, P);
-    vt_publish_schedule(s, P);
-  }
+  if (P.inline_sched) publish_own_schedule<kVtThreads>(reinterpret_cast<int*>(s.raw[0]), P, blockIdx.x);  // raw[0] is free until the first load
 
   // Register budgets per warp group (setmaxnreg); the pool is the launch allocation, 20 warps x 96, and the V warps keep
   // what they were launched with.
