@@ -56,7 +56,6 @@ BASELINE_TBPS = {"c2_h16_b64_64k": 4.77}
 # kernels (h16_b8_64k: 524 288 tokens); the kernels are persistent and stream each token once, so traffic grows with the
 # token count and the benchmark scales it to its own workload (roofline.traffic_kind says so).
 NCU_TRAFFIC_BYTES_PER_TOKEN = {"bf16": 401, "fp8": 398}
-KERNELS_PER_DECODE = 3  # schedule, decode, combine
 
 
 def measured_peak():
@@ -509,6 +508,11 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
     res = {"workload": workload, "precision": precision, "B": B, "H": H, "kv_len": kv_len, "ps": ps, "seq": seq, "l2": l2,
            "steps": steps, "kv_bytes": kv_bytes}
     res["ms_step"] = max_over_ranks(total_ms / steps)
+    # kernels per decode call: 2 (decode, merge of the partials), 3 when a schedule kernel runs in front (large batches)
+    res["launches_per_decode"] = lib.nvfp4_mla_decode_launches(len(cache.kv_lens_list), H, kv_len_local, args.num_splits,
+                                                               0 if precision == "bf16" else 1)
+    if res["launches_per_decode"] < 0:
+        raise RuntimeError(lib.nvfp4_mla_last_error().decode())
     res["kernel_ms"] = max_over_ranks(sum(kern_ms[:n_k]) / max(n_k, 1))
     if seq and world > 1:  # the local split-KV decode alone (no exchange, no merge): what the exchange adds on top
         local_ms, _ = timed_pass(lambda: mla.decode_partial(*dargs, into=(merger.o, merger.lse), **kw))  # same buffers as the full step
@@ -729,7 +733,7 @@ def main():
         "decode_us": ms_step * 1e3, "frac_of_8tbps": value / world / 8.0,
         "e2e": {"value": m["kv_bytes_all"] / (m["e2e_ms"] * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": m["e2e_ms"],
                 "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
-        "gpu_launches": (KERNELS_PER_DECODE + (1 if seq and world > 1 else 0)) * args.steps,
+        "gpu_launches": (m["launches_per_decode"] + (1 if seq and world > 1 else 0)) * args.steps,
         "roofline": roofline,
         "parity_check": m["parity_check"],
         "clocks": clocks,

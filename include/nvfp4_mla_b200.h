@@ -34,6 +34,12 @@ NVFP4_MLA_API int nvfp4_mla_version(void);
 /* Message of the calling thread's most recent failed call ("" if none). */
 NVFP4_MLA_API const char* nvfp4_mla_last_error(void);
 
+/* Kernels one nvfp4_mla_decode call with these arguments launches on the current device: 2 (decode, merge of the
+ * partials) when the decode kernel derives the split-KV schedule by itself (batch x splits up to its thread count),
+ * 3 with the schedule kernel in front (larger batches); 0 for batch 0, -1 on invalid arguments. For launch accounting;
+ * the reference's launcher (nvfp4_mla/csrc/mla_decode.cu:1042-1069) launches its split and merge kernels likewise. */
+NVFP4_MLA_API int nvfp4_mla_decode_launches(int batch, int heads, int max_kv_len, int num_splits, int precision);
+
 /* Bytes of scratch nvfp4_mla_decode needs for this problem on the current device. `num_splits` as in the decode
  * call. Replaces the torch::empty of o_part / lse_part inside the reference launcher
  * (nvfp4_mla/csrc/mla_decode.cu:1042-1047). Returns -1 on invalid arguments. */

@@ -15,6 +15,7 @@ SIGNATURES = {
     "nvfp4_mla_version": (_i32, []),
     "nvfp4_mla_last_error": (ctypes.c_char_p, []),
     "nvfp4_mla_decode_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "nvfp4_mla_decode_launches": (_i32, [_i32, _i32, _i32, _i32, _i32]),
     "nvfp4_mla_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i32, _i32, _f32, _f32, _f32,
                                 _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "nvfp4_mla_decode_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i32, _i32, _f32, _f32, _f32,

@@ -217,6 +217,14 @@ int nvfp4_mla_version(void) { return 100; }
 
 const char* nvfp4_mla_last_error(void) { return g_error; }
 
+// Whether the decode kernel derives the schedule by itself (one thread per (request, split) pair, 32-bit tile counts)
+// or reads the output of a schedule kernel launched in front of it.
+static bool schedules_itself(const mla::Problem& pb, int precision, int hpc) {
+  const long long bz = (long long)pb.batch * pb.splits;
+  return bz <= (long long)decode_threads(precision, hpc) &&
+         bz * ((pb.chunk + mla::TILE - 1) / mla::TILE + 1) * pb.head_groups < (1ll << 31);
+}
+
 // workspace of one precision mode (the modes may group the heads differently); negative on error
 static int64_t workspace_bytes_of(int batch, int heads, int num_splits, int precision, int hpc_limit = 128) {
   DeviceInfo* d;
@@ -225,6 +233,21 @@ static int64_t workspace_bytes_of(int batch, int heads, int num_splits, int prec
   const int hpc = heads_per_cta(heads, precision, *d, hpc_limit);
   if (problem_of(batch, heads, 1, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
   return int64_t(mla::ws_layout(pb.n_cta, pb.items(), pb.heads_per_cta).total);
+}
+
+int nvfp4_mla_decode_launches(int batch, int heads, int max_kv_len, int num_splits, int precision) {
+  g_error[0] = 0;
+  if (precision != NVFP4_MLA_PRECISION_BF16 && precision != NVFP4_MLA_PRECISION_FP8) {
+    fail("precision must be 0 (bf16) or 1 (fp8), got %d", precision);
+    return -1;
+  }
+  DeviceInfo* d;
+  if (device_info(&d)) return -1;
+  mla::Problem pb;
+  const int hpc = heads_per_cta(heads, precision, *d, 128);
+  if (problem_of(batch, heads, max_kv_len, num_splits, schedule_units(*d, hpc), hpc, &pb)) return -1;
+  if (batch == 0) return 0;
+  return schedules_itself(pb, precision, hpc) ? 2 : 3;
 }
 
 int64_t nvfp4_mla_decode_workspace_bytes(int batch, int heads, int num_splits) {
@@ -279,9 +302,7 @@ static int decode_impl(const void* q_nope, const void* q_pe, const uint8_t* ckv_
 
   // The decode kernels derive their schedule by themselves when one thread per (request, split) pair is enough; larger
   // batches read the output of the schedule kernel.
-  const long long bz = (long long)pb.batch * pb.splits;
-  const bool inline_sched = bz <= (long long)decode_threads(precision, hpc) &&
-                            bz * ((pb.chunk + mla::TILE - 1) / mla::TILE + 1) * pb.head_groups < (1ll << 31);  // its 32-bit arithmetic
+  const bool inline_sched = schedules_itself(pb, precision, hpc);
   if (!inline_sched) {
     mla::mla_schedule_kernel<<<1, mla::kSchedThreads, 0, st>>>(kv_lens, pb, header, cta_range, item_range, segs);
     MLA_CUDA(cudaGetLastError());

@@ -232,6 +232,39 @@ def test_query_with_outlier_channels(factor):
     check(c, out, lse2, f"outlier channels x{factor}")
 
 
+@pytest.mark.parametrize("precision", ["bf16", "fp8"])
+def test_schedule_inside_the_decode_kernel_and_in_front_of_it_agree(precision):
+    """Up to one (request, split) pair per thread of a decode CTA the decode kernel derives the schedule by itself (two
+    launches per call); beyond that a schedule kernel runs in front (three). Both must serve the same requests alike: a
+    batch of 700 short ragged requests (some empty) takes the second path, its first 40 requests alone the first."""
+    from nvfp4_mla_b200 import _lib
+    lib = _lib.load()
+    g = np.random.default_rng(11)
+    lens = [int(x) for x in g.integers(0, 700, size=700)]
+    lens[3] = lens[17] = 0
+    c = SyntheticCache(lens, 64, 16, 0.5, 2.0, seed=4, device="cuda")
+    prec = 0 if precision == "bf16" else 1
+    assert lib.nvfp4_mla_decode_launches(700, 16, max(lens), 0, prec) == 3
+    assert lib.nvfp4_mla_decode_launches(40, 16, max(lens), 0, prec) == 2
+    assert lib.nvfp4_mla_decode_launches(0, 16, 128, 0, prec) == 0
+    big = mla.decode(*c.args(SM_SCALE), max_kv_len=max(lens), precision=precision)
+    a = list(c.args(SM_SCALE))
+    n = 40
+    small = mla.decode(a[0][:n].contiguous(), a[1][:n].contiguous(), a[2], a[3], a[4], a[5][:n].contiguous(), a[6][:n].contiguous(),
+                       *a[7:], max_kv_len=max(lens), precision=precision)
+    torch.cuda.synchronize()
+    assert mla.workspace_status() == 0
+    assert float(big[3].abs().max()) == 0.0 and float(big[17].abs().max()) == 0.0
+    want, _ = oracle_reference(c)
+    tol = 4e-3 if precision == "bf16" else 0.08  # rel-L2 bounds of the two modes, as in the tests above
+    for got, m in ((big.float().cpu().numpy(), 700), (small.float().cpu().numpy(), n)):
+        assert not np.isnan(got).any()
+        nz = [b for b in range(m) if lens[b] > 0]
+        assert O.rel_l2(got[nz], want[nz]) < tol
+    # the two schedules cut the requests at different tiles, so the results agree to rounding, not bit for bit
+    assert float((big[:n].float() - small.float()).abs().max()) <= (2e-2 if precision == "bf16" else 0.2)
+
+
 @pytest.mark.parametrize("seed", [1, 2, 3])
 def test_random_shapes_are_deterministic_and_clean(seed):
     """A dozen random (batch, heads, page size, lengths, splits) per seed, both modes: repeated calls give identical
