@@ -493,7 +493,7 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
         sync_all()
         return sum(a.elapsed_time(b) for a, b in pairs), o
 
-    # Pass 1, the reported step time: the call as a user makes it (its three kernels chained by programmatic dependent
+    # Pass 1, the reported step time: the call as a user makes it (its kernels chained by programmatic dependent
     # launch). Pass 2, the same K steps with the library's own event pair around the decode kernel (the roofline's
     # duration): those events sit between the kernels and undo the chaining, so this pass is not the one reported.
     total_ms, out = timed_pass(lambda: decode_fn(*dargs, **kw))

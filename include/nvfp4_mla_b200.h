@@ -98,7 +98,8 @@ NVFP4_MLA_API int nvfp4_mla_decode(const void* q_nope, const void* q_pe, const u
  *     replayed concurrently) race on it and corrupt each other's results: serialise them, or give the concurrent
  *     ones their own workspace through nvfp4_mla_decode.
  *   - The array keeps what the previous call wrote. Nothing in it has to be cleared between calls: every record the
- *     kernels read is rewritten by the call's own schedule kernel first. The device-side status word is zero when the
+ *     kernels read is rewritten by the call itself first (by its schedule kernel, or by the decode CTAs that derive
+ *     the schedule themselves). The device-side status word is zero when the
  *     library is loaded and sticky afterwards: nvfp4_mla_decode_static_status(stream) synchronises `stream`, returns
  *     the status of all static calls since it last reported a non-zero one (same codes as nvfp4_mla_workspace_status)
  *     and, if it was non-zero, clears the word. */
