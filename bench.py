@@ -9,8 +9,9 @@ value is the bytes all ranks streamed divided by the slowest rank's time (weak s
   value      KV-cache bandwidth, 352 bytes per cached token / device time per step (CUDA events on the launching
              stream, inputs resident in HBM; the cache is far larger than L2, so no flush is needed)
   e2e        the same through the Python API with the per-step inputs (queries, page table, lengths) coming from
-             pinned host memory and the output copied back to the host inside the timed region. The KV cache itself
-             is device-resident state written by earlier steps of a serving engine, not a per-step input.
+             pinned host memory (one packed buffer, one copy per step) and the output copied back to the host inside
+             the timed region. The KV cache itself is device-resident state written by earlier steps of a serving
+             engine, not a per-step input.
   roofline   the decode kernel alone (timed by the library's own event pair around it) against the measured HBM peak
   cpu_baseline / --impl reference
              the reference's CPU path (dequantize, then fp32 attention: its own torch functions from the unmodified
@@ -536,15 +537,28 @@ def measure(args, workload, precision, steps, warmup, rank, world, dev, sampler,
 
     if want_e2e:
         # ---- end to end through the public API, per-step inputs from pinned host memory ------------------------
-        host = [t.cpu().pin_memory() for t in (cache.q_nope, cache.q_pe, cache.page_table, cache.kv_lens)]
-        devbuf = [torch.empty_like(t, device=dev) for t in host]
+        # The step's inputs sit back to back in ONE pinned host buffer (256-byte aligned pieces) and cross in one copy;
+        # the tensors the decode call gets are views of the device copy.
+        srcs = (cache.q_nope, cache.q_pe, cache.page_table, cache.kv_lens)
+        offs, total = [], 0
+        for t in srcs:
+            offs.append(total)
+            total += (t.numel() * t.element_size() + 255) // 256 * 256
+        host_buf = torch.empty(total, dtype=torch.uint8).pin_memory()
+        dev_buf = torch.empty(total, dtype=torch.uint8, device=dev)
+
+        def views(buf):
+            return [buf[o:o + t.numel() * t.element_size()].view(t.dtype).view(t.shape) for o, t in zip(offs, srcs)]
+
+        for h, t in zip(views(host_buf), srcs):
+            h.copy_(t.cpu())
+        devbuf = views(dev_buf)
         out_host = torch.empty(B, H, 512, dtype=torch.bfloat16).pin_memory()
-        res["h2d"] = sum(t.numel() * t.element_size() for t in host)
+        res["h2d"] = sum(t.numel() * t.element_size() for t in srcs)
         res["d2h"] = out_host.numel() * out_host.element_size()
 
         def e2e_step():
-            for d, h in zip(devbuf, host):
-                d.copy_(h, non_blocking=True)
+            dev_buf.copy_(host_buf, non_blocking=True)
             o = decode_fn(devbuf[0], devbuf[1], cache.ckv_cache, cache.ckv_sf_cache, cache.kpe_cache, devbuf[2], devbuf[3],
                           SM_SCALE, cache.ckv_scale, cache.kpe_scale, **kw)
             out_host.copy_(o, non_blocking=True)
