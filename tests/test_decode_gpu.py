@@ -249,15 +249,24 @@ def test_schedule_inside_the_decode_kernel_and_in_front_of_it_agree(precision):
     assert lib.nvfp4_mla_decode_launches(0, 16, 128, 0, prec) == 0
     big = mla.decode(*c.args(SM_SCALE), max_kv_len=max(lens), precision=precision)
     a = list(c.args(SM_SCALE))
+
+    def first(m):
+        return mla.decode(a[0][:m].contiguous(), a[1][:m].contiguous(), a[2], a[3], a[4], a[5][:m].contiguous(),
+                          a[6][:m].contiguous(), *a[7:], max_kv_len=max(lens), precision=precision)
+
     n = 40
-    small = mla.decode(a[0][:n].contiguous(), a[1][:n].contiguous(), a[2], a[3], a[4], a[5][:n].contiguous(), a[6][:n].contiguous(),
-                       *a[7:], max_kv_len=max(lens), precision=precision)
+    small = first(n)
+    edge = 640 if precision == "bf16" else 512  # one pair per thread of the decode CTA: the largest batch of the first path
+    assert lib.nvfp4_mla_decode_launches(edge, 16, max(lens), 0, prec) == 2
+    assert lib.nvfp4_mla_decode_launches(edge + 1, 16, max(lens), 0, prec) == 3
+    at_edge, past_edge = first(edge), first(edge + 1)
     torch.cuda.synchronize()
     assert mla.workspace_status() == 0
     assert float(big[3].abs().max()) == 0.0 and float(big[17].abs().max()) == 0.0
     want, _ = oracle_reference(c)
     tol = 4e-3 if precision == "bf16" else 0.08  # rel-L2 bounds of the two modes, as in the tests above
-    for got, m in ((big.float().cpu().numpy(), 700), (small.float().cpu().numpy(), n)):
+    for got, m in ((big.float().cpu().numpy(), 700), (small.float().cpu().numpy(), n),
+                   (at_edge.float().cpu().numpy(), edge), (past_edge.float().cpu().numpy(), edge + 1)):
         assert not np.isnan(got).any()
         nz = [b for b in range(m) if lens[b] > 0]
         assert O.rel_l2(got[nz], want[nz]) < tol
